@@ -1,0 +1,31 @@
+"""ctypes binding of the CUDA library.  There is no fallback: if the library is missing or does not
+load, importing this module raises."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import _build
+
+_LIB = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) ``_lib/liblethe_gdn.so``.  The library is built by ``_build.build()``; a missing
+    file is an error, never a reason to compute elsewhere."""
+    global _LIB
+    if _LIB is None:
+        path = _build.LIB
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m lethe_b200._build` (needs nvcc)")
+        _LIB = ctypes.CDLL(path)
+        _declare(_LIB)
+    return _LIB
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    c_int, c_void_p = ctypes.c_int, ctypes.c_void_p
+    L.lethe_probe_umma.restype = c_int
+    L.lethe_probe_umma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]
