@@ -1,0 +1,101 @@
+/* C interface of liblethe_gdn.so: the chunked gated-delta-rule (GDN family) forward and backward on
+ * NVIDIA B200 (sm_100a).
+ *
+ * It replaces, behind one pair of calls, what the reference project (RishiShah99/lethe) spreads over
+ * its autograd op and its kernel plug-ins:
+ *   - forward:  src/lethe/kernels/ops/gdn_layer.py:17-67 (_GDN2Function.forward, which today runs the
+ *               token-serial src/lethe/kernels/references/gdn_backward.py:13-55 or the chunkwise
+ *               restage src/lethe/kernels/references/gdn2_chunkwise_cw.py:213-314);
+ *   - backward: src/lethe/kernels/ops/gdn_backward.py:16-57 -> src/lethe/kernels/cute/gdn2_backward.py:77-134
+ *               -> src/lethe/kernels/cute/gdn2_assemble.py:242-314 / :601-696 / :711-775, i.e. the
+ *               forward recompute, the reverse state scan K#1 (K1Fn, gdn2_assemble.py:29-32), the
+ *               closed Stage B (:521-585) and the WY / triangular-inverse VJP K#2 (K2Fn, :33-44).
+ *
+ * Ownership: the caller allocates every buffer (inputs, outputs, the two workspaces and the status
+ * word) on the current device; the library allocates nothing and keeps no state between calls.
+ * Threading: re-entrant; all work is enqueued on the given stream; no call synchronises.
+ * Errors: a non-zero return means nothing was launched (see lethe_gdn_strerror).  Device-side waits
+ * are bounded; a wait that gave up leaves a non-zero code in *status, readable once the stream has
+ * been synchronised (results are then invalid).  The caller zeroes *status before the first call.
+ *
+ * Layouts (all row-major, innermost dimension contiguous):
+ *   q, k        [B, L, H, K]  bf16          v, o, do, dv [B, L, H, V]  bf16     dq, dk [B, L, H, K] bf16
+ *   g           [B, L, H] (gate = 1) or [B, L, H, K] (gate = 2), fp32, natural-log decay (<= 0)
+ *   beta        [B, L, H] fp32 (delta = 1)
+ *   h0, hT, dhT, dh0   [B, H, K, V] fp32
+ *   dg          like g, fp32;   dbeta like beta, fp32
+ * Sizes: K = 128, V in {64, 128}, L a multiple of 64 (the chunk length).
+ */
+#ifndef LETHE_GDN_H_
+#define LETHE_GDN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { LETHE_GATE_NONE = 0, LETHE_GATE_SCALAR = 1, LETHE_GATE_CHANNEL = 2 };
+
+typedef struct LetheGdnDims {
+  int32_t B, H, L, K, V;
+  int32_t gate;   /* LETHE_GATE_*                                                        */
+  int32_t delta;  /* 1: erase and write gates are beta (gated delta rule, KDA)            */
+                  /* 0: no erase term, write gate one (linear attention, GLA, SSD)        */
+} LetheGdnDims;
+
+typedef struct LetheGdnArgs {
+  LetheGdnDims dims;
+  float scale;            /* multiplies q; the reference default is K^-0.5                  */
+  /* forward inputs */
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* g;         /* NULL when gate == LETHE_GATE_NONE                              */
+  const float* beta;      /* NULL when delta == 0                                           */
+  const float* h0;        /* NULL: zero initial state                                       */
+  /* forward outputs */
+  void* o;
+  float* hT;              /* NULL: final state not wanted                                   */
+  /* backward inputs */
+  const void* d_o;
+  const float* dhT;       /* NULL: zero                                                     */
+  /* backward outputs */
+  void* dq;
+  void* dk;
+  void* dv;
+  float* dg;              /* NULL when gate == LETHE_GATE_NONE                              */
+  float* dbeta;           /* NULL when delta == 0                                           */
+  float* dh0;             /* NULL: not wanted                                               */
+  /* caller-owned scratch */
+  void* saved;            /* written by forward, read by backward; lethe_gdn_saved_bytes     */
+  size_t saved_bytes;
+  void* scratch;          /* backward only; lethe_gdn_scratch_bytes                          */
+  size_t scratch_bytes;
+  int32_t* status;        /* device word, see above                                         */
+} LetheGdnArgs;
+
+/* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */
+size_t lethe_gdn_saved_bytes(const LetheGdnDims* dims);
+size_t lethe_gdn_scratch_bytes(const LetheGdnDims* dims);
+
+/* Forward: o (and hT) from q, k, v, g, beta, h0.  Replaces gdn_layer.py:17-67 of the reference. */
+int lethe_gdn_forward(const LetheGdnArgs* args, void* cuda_stream);
+
+/* Backward: dq, dk, dv, dg, dbeta, dh0 from the forward inputs, d_o, dhT and `saved`.
+ * Replaces gdn_backward.py:16-57 / gdn2_assemble.py:242-314,601-696,711-775 of the reference. */
+int lethe_gdn_backward(const LetheGdnArgs* args, void* cuda_stream);
+
+/* Text for a return code of the calls above or for a device status code. */
+const char* lethe_gdn_strerror(int code);
+
+/* Test hook (not part of the GDN interface): one tcgen05 product on one CTA, used by the toolkit
+ * self-test.  No counterpart in the reference. */
+int lethe_probe_umma(const void* A, const void* B, float* D, int* status, int a_mn, int b_mn, int N,
+                     int kc, int fill, int a_neg, int twice, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LETHE_GDN_H_ */

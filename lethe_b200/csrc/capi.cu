@@ -1,0 +1,137 @@
+// C-ABI entry points: argument checks, tensor maps, kernel sequence.  See include/lethe_gdn.h.
+#include <string.h>
+
+#include "gdn_common.cuh"
+#include "host_util.h"
+
+namespace lg {
+int launch_prepare(const Problem&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_output(const Problem&, const CUtensorMap&, cudaStream_t);
+int launch_scan(const Problem&, bool adjoint, cudaStream_t);
+int launch_bwd_pre(const Problem&, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t);
+int launch_bwd_main(const Problem&, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                    const CUtensorMap& mdo, cudaStream_t);
+
+static bool dims_ok(const LetheGdnDims& d) {
+  if (d.B <= 0 || d.H <= 0 || d.L <= 0) return false;
+  if (d.K != kK || (d.V != 64 && d.V != 128)) return false;
+  if (d.L % kC) return false;
+  if (d.gate < LETHE_GATE_NONE || d.gate > LETHE_GATE_CHANNEL) return false;
+  if (d.delta != 0 && d.delta != 1) return false;
+  return true;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Tensor map of a token-major [B, L, H, D] 16-bit tensor; one box = 64 tokens x 64 channels of one head.
+static int token_map(CUtensorMap* m, const void* ptr, const LetheGdnDims& d, int D) {
+  uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(d.H), static_cast<uint64_t>(d.L),
+                      static_cast<uint64_t>(d.B)};
+  uint64_t str[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(d.H) * D * 2,
+                     static_cast<uint64_t>(d.L) * d.H * D * 2};
+  uint32_t box[4] = {64, 1, 64, 1};
+  return make_tmap_16bit(m, ptr, 4, dims, str, box);
+}
+
+static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
+  if (!a) return kErrNull;
+  const LetheGdnDims& d = a->dims;
+  if (!dims_ok(d)) return kErrDims;
+  if (d.gate == LETHE_GATE_CHANNEL) return kErrFlags;   // channel-wise gate: not built yet
+  if (!a->q || !a->k || !a->v || !a->saved || !a->status) return kErrNull;
+  if (d.gate != LETHE_GATE_NONE && !a->g) return kErrNull;
+  if (d.delta && !a->beta) return kErrNull;
+  if (!backward && !a->o) return kErrNull;
+  if (backward) {
+    if (!a->d_o || !a->dq || !a->dk || !a->dv || !a->scratch) return kErrNull;
+    if (d.gate != LETHE_GATE_NONE && !a->dg) return kErrNull;
+    if (d.delta && !a->dbeta) return kErrNull;
+  }
+  const void* ptrs[] = {a->q, a->k, a->v, a->o, a->d_o, a->dq, a->dk, a->dv, a->h0, a->hT, a->dhT, a->dh0,
+                        a->saved, a->scratch};
+  for (const void* x : ptrs)
+    if (x && !aligned16(x)) return kErrAlign;
+  Layout lay = make_layout(d);
+  if (a->saved_bytes < lay.saved_total) return kErrWorkspace;
+  if (backward && a->scratch_bytes < lay.scratch_total) return kErrWorkspace;
+  if (!aligned16(a->saved) || (reinterpret_cast<uintptr_t>(a->saved) & 1023u)) return kErrAlign;
+  if (backward && (reinterpret_cast<uintptr_t>(a->scratch) & 1023u)) return kErrAlign;
+  p->B = d.B; p->H = d.H; p->L = d.L; p->NT = d.L / kC; p->V = d.V; p->gate = d.gate; p->delta = d.delta;
+  p->scale = a->scale;
+  p->q = static_cast<const __nv_bfloat16*>(a->q);
+  p->k = static_cast<const __nv_bfloat16*>(a->k);
+  p->v = static_cast<const __nv_bfloat16*>(a->v);
+  p->d_o = static_cast<const __nv_bfloat16*>(a->d_o);
+  p->g = a->g; p->beta = a->beta; p->h0 = a->h0; p->dhT = a->dhT;
+  p->o = static_cast<__nv_bfloat16*>(a->o);
+  p->dq = static_cast<__nv_bfloat16*>(a->dq);
+  p->dk = static_cast<__nv_bfloat16*>(a->dk);
+  p->dv = static_cast<__nv_bfloat16*>(a->dv);
+  p->hT = a->hT; p->dg = a->dg; p->dbeta = a->dbeta; p->dh0 = a->dh0;
+  p->saved = static_cast<unsigned char*>(a->saved);
+  p->scratch = static_cast<unsigned char*>(a->scratch);
+  p->lay = lay;
+  p->status = a->status;
+  return kOk;
+}
+
+}  // namespace lg
+
+using namespace lg;
+
+extern "C" size_t lethe_gdn_saved_bytes(const LetheGdnDims* d) {
+  if (!d || !dims_ok(*d)) return 0;
+  return make_layout(*d).saved_total;
+}
+extern "C" size_t lethe_gdn_scratch_bytes(const LetheGdnDims* d) {
+  if (!d || !dims_ok(*d)) return 0;
+  return make_layout(*d).scratch_total;
+}
+
+extern "C" int lethe_gdn_forward(const LetheGdnArgs* a, void* stream) {
+  Problem p;
+  memset(&p, 0, sizeof(p));
+  int e = fill_problem(a, &p, false);
+  if (e) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap mq, mk, mv;
+  if ((e = token_map(&mq, a->q, a->dims, kK))) return e;
+  if ((e = token_map(&mk, a->k, a->dims, kK))) return e;
+  if ((e = token_map(&mv, a->v, a->dims, a->dims.V))) return e;
+  if ((e = launch_prepare(p, mq, mk, mv, st))) return e;
+  if ((e = launch_scan(p, false, st))) return e;
+  return launch_output(p, mq, st);
+}
+
+extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
+  Problem p;
+  memset(&p, 0, sizeof(p));
+  int e = fill_problem(a, &p, true);
+  if (e) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap mq, mk, mv, mdo;
+  if ((e = token_map(&mq, a->q, a->dims, kK))) return e;
+  if ((e = token_map(&mk, a->k, a->dims, kK))) return e;
+  if ((e = token_map(&mv, a->v, a->dims, a->dims.V))) return e;
+  if ((e = token_map(&mdo, a->d_o, a->dims, a->dims.V))) return e;
+  if ((e = launch_bwd_pre(p, mq, mdo, st))) return e;
+  if ((e = launch_scan(p, true, st))) return e;
+  return launch_bwd_main(p, mq, mk, mv, mdo, st);
+}
+
+extern "C" const char* lethe_gdn_strerror(int code) {
+  switch (code) {
+    case kOk: return "ok";
+    case kErrNull: return "a required pointer is null";
+    case kErrDims: return "unsupported sizes (need K = 128, V in {64, 128}, L a multiple of 64)";
+    case kErrAlign: return "a pointer is not aligned (16 bytes for tensors, 1024 for workspaces)";
+    case kErrWorkspace: return "workspace too small";
+    case kErrDriver: return "tensor-map encoding failed";
+    case kErrLaunch: return "kernel launch failed";
+    case kErrFlags: return "unsupported gate / delta combination";
+    case kErrTooLarge: return "problem exceeds the capacity of this entry point";
+    default: break;
+  }
+  if (code >= 100) return "device-side wait timed out (status word holds the wait site)";
+  return "unknown error";
+}

@@ -1,0 +1,115 @@
+// Shared definitions of the GDN kernels: problem description, workspace layout, small device helpers.
+//
+// Work decomposition.  A "chunk" is 64 consecutive tokens of one (batch, head) pair; chunks are
+// numbered z = (b*H + h)*NT + c.  Chunk-parallel kernels run one CTA of 128 threads per chunk;
+// the scan kernel runs one CTA per (b, h, 16-column slice of V) and walks the chunks in order.
+//
+// Per-chunk records in the workspaces ("image" = the SW128 shared-memory tile image, so that a
+// record moves between global and shared memory with one contiguous bulk copy):
+//   saved (forward -> backward)
+//     TA    16 KB   image, 128 rows x 64: rows 0-63 T = (I + strict_lower(M))^-1, rows 64-127 A
+//     W     16 KB   image, 64 x 128: WY factor w = T (beta gamma k)
+//     U     64 x V  image: u = T (beta v)
+//     P     32 KB   image, 128 x 128: kd^T w           (state transition, without the decay)
+//     R     128 x V fp16 row-major: kd^T u            (state input)
+//     Hc    128 x V image: state entering the chunk
+//     VN    64 x V  image: v_new = u - w h
+//     AD    128 fp32: exp(G_last) per key channel     (the decay of the chunk)
+//   scratch (backward only)
+//     RB    128 x V fp16 row-major: (q gamma)^T do - w^T (A^T do)
+//     DH    128 x V image: adjoint of the state leaving the chunk
+//     DV2   64 x V  image: adjoint of v_new
+//     DW    64 x 128 image: adjoint of w
+//     DKB   64 x 128 fp32: key gradient of Stage B
+//     DGB   64 x 128 fp32 (channel-wise) or 64 fp32 (scalar): gate-gradient of Stage B before the cumsum
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/lethe_gdn.h"
+#include "tiles.cuh"
+
+namespace lg {
+
+constexpr int kC = 64;    // chunk length
+constexpr int kK = 128;   // key dimension
+
+struct Layout {
+  // byte offsets of the record arrays inside `saved` / `scratch`, and record sizes
+  size_t ta, w, u, p, r, hc, vn, ad, saved_total;
+  size_t rb, dh, dv2, dw, dkb, dgb, scratch_total;
+  size_t sz_ta, sz_w, sz_u, sz_p, sz_r, sz_hc, sz_vn, sz_ad;
+  size_t sz_rb, sz_dh, sz_dv2, sz_dw, sz_dkb, sz_dgb;
+};
+
+__host__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ inline Layout make_layout(const LetheGdnDims& d) {
+  Layout l{};
+  const size_t Z = static_cast<size_t>(d.B) * d.H * (d.L / kC);
+  const size_t V = d.V;
+  l.sz_ta = 16384; l.sz_w = 16384; l.sz_u = kC * V * 2; l.sz_p = 32768; l.sz_r = kK * V * 2;
+  l.sz_hc = kK * V * 2; l.sz_vn = kC * V * 2; l.sz_ad = kK * 4;
+  size_t o = 0;
+  l.ta = o; o = align_up(o + Z * l.sz_ta, 1024);
+  l.w = o;  o = align_up(o + Z * l.sz_w, 1024);
+  l.u = o;  o = align_up(o + Z * l.sz_u, 1024);
+  l.p = o;  o = align_up(o + Z * l.sz_p, 1024);
+  l.r = o;  o = align_up(o + Z * l.sz_r, 1024);
+  l.hc = o; o = align_up(o + Z * l.sz_hc, 1024);
+  l.vn = o; o = align_up(o + Z * l.sz_vn, 1024);
+  l.ad = o; o = align_up(o + Z * l.sz_ad, 1024);
+  l.saved_total = o;
+  l.sz_rb = kK * V * 2; l.sz_dh = kK * V * 2; l.sz_dv2 = kC * V * 2; l.sz_dw = 16384;
+  l.sz_dkb = kC * kK * 4; l.sz_dgb = (d.gate == LETHE_GATE_CHANNEL ? kC * kK : kC) * 4;
+  o = 0;
+  l.rb = o;  o = align_up(o + Z * l.sz_rb, 1024);
+  l.dh = o;  o = align_up(o + Z * l.sz_dh, 1024);
+  l.dv2 = o; o = align_up(o + Z * l.sz_dv2, 1024);
+  l.dw = o;  o = align_up(o + Z * l.sz_dw, 1024);
+  l.dkb = o; o = align_up(o + Z * l.sz_dkb, 1024);
+  l.dgb = o; o = align_up(o + Z * l.sz_dgb, 1024);
+  l.scratch_total = o;
+  return l;
+}
+
+// Everything a kernel needs besides its tensor maps.
+struct Problem {
+  int B, H, L, NT, V, gate, delta;
+  float scale;
+  const __nv_bfloat16 *q, *k, *v, *d_o;
+  const float *g, *beta, *h0, *dhT;
+  __nv_bfloat16 *o, *dq, *dk, *dv;
+  float *hT, *dg, *dbeta, *dh0;
+  unsigned char* saved;
+  unsigned char* scratch;
+  Layout lay;
+  int* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------------------------
+// Inclusive prefix sum of one value per thread over threads 0..63 (two warps); every thread of the
+// CTA must call it (it contains __syncthreads).  `tmp` is a shared float[2].
+__device__ __forceinline__ float chunk_cumsum(float x, int tid, float* tmp) {
+  const int lane = tid & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (tid == 31) tmp[0] = x;
+  __syncthreads();
+  if (tid >= 32 && tid < 64) x += tmp[0];
+  return x;
+}
+
+// Control block at the start of every kernel: barriers, TMEM slot, abort flag.
+struct CtaShared {
+  uint64_t bar[8];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+}  // namespace lg

@@ -27,5 +27,15 @@ def lib() -> ctypes.CDLL:
 
 def _declare(L: ctypes.CDLL) -> None:
     c_int, c_void_p = ctypes.c_int, ctypes.c_void_p
+    L.lethe_gdn_saved_bytes.restype = ctypes.c_size_t
+    L.lethe_gdn_saved_bytes.argtypes = [c_void_p]
+    L.lethe_gdn_scratch_bytes.restype = ctypes.c_size_t
+    L.lethe_gdn_scratch_bytes.argtypes = [c_void_p]
+    L.lethe_gdn_forward.restype = c_int
+    L.lethe_gdn_forward.argtypes = [c_void_p, c_void_p]
+    L.lethe_gdn_backward.restype = c_int
+    L.lethe_gdn_backward.argtypes = [c_void_p, c_void_p]
+    L.lethe_gdn_strerror.restype = ctypes.c_char_p
+    L.lethe_gdn_strerror.argtypes = [c_int]
     L.lethe_probe_umma.restype = c_int
     L.lethe_probe_umma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]

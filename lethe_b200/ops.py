@@ -1,0 +1,186 @@
+"""PyTorch surface of the B200 chunked gated-delta-rule path.
+
+``gdn_chunk`` is the differentiable op.  It keeps the argument meaning of the reference project's op
+(``gdn2_op``, ``src/lethe/kernels/ops/gdn_layer.py:99-111``: token-major ``[B, L, H, D]`` tensors,
+``scale`` applied to q, optional L2 normalisation of q and k) and adds what the reference only has in
+its chunkwise references: an initial state in and the final state out
+(``src/lethe/kernels/references/gdn2_chunkwise.py:77,157-158``).
+
+PyTorch supplies device memory, the stream and autograd bookkeeping; every number is computed by the
+CUDA library behind ``lethe_b200.native`` (there is no other path: a missing library raises).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+from torch import Tensor
+
+from . import native
+
+GATE_NONE, GATE_SCALAR, GATE_CHANNEL = 0, 1, 2
+
+
+class _Dims(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "H", "L", "K", "V", "gate", "delta")]
+
+
+class _Args(ctypes.Structure):
+    _fields_ = [
+        ("dims", _Dims), ("scale", ctypes.c_float),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("g", ctypes.c_void_p), ("beta", ctypes.c_void_p), ("h0", ctypes.c_void_p),
+        ("o", ctypes.c_void_p), ("hT", ctypes.c_void_p),
+        ("d_o", ctypes.c_void_p), ("dhT", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+        ("dg", ctypes.c_void_p), ("dbeta", ctypes.c_void_p), ("dh0", ctypes.c_void_p),
+        ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("status", ctypes.c_void_p),
+    ]
+
+
+def _ptr(t: Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+class GdnError(RuntimeError):
+    pass
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        msg = native.lib().lethe_gdn_strerror(rc).decode()
+        raise GdnError(f"lethe_gdn: {msg} (code {rc})")
+
+
+def check_status(status: Tensor) -> None:
+    """Raise if a device-side wait of an earlier call gave up (synchronises)."""
+    code = int(status.item())
+    if code != 0:
+        raise GdnError(f"lethe_gdn: device-side wait timed out at site {code}; results are invalid")
+
+
+def _dims(q: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | None) -> _Dims:
+    B, L, H, K = q.shape
+    gate = GATE_NONE if g is None else (GATE_SCALAR if g.dim() == 3 else GATE_CHANNEL)
+    return _Dims(B, H, L, K, v.shape[-1], gate, 0 if beta is None else 1)
+
+
+def _prep16(t: Tensor) -> Tensor:
+    return t.to(torch.bfloat16).contiguous()
+
+
+def _prep32(t: Tensor | None) -> Tensor | None:
+    return None if t is None else t.to(torch.float32).contiguous()
+
+
+def gdn_forward_raw(q, k, v, g, beta, h0, scale: float, want_final: bool = True):
+    """One forward call of the library.  Inputs must be CUDA tensors: q, k, v bf16 contiguous
+    ``[B, L, H, D]``; g, beta, h0 fp32.  Returns ``(o, hT, saved, status)``."""
+    L_ = native.lib()
+    d = _dims(q, v, g, beta)
+    nsaved = L_.lethe_gdn_saved_bytes(ctypes.byref(d))
+    if nsaved == 0:
+        raise GdnError(f"lethe_gdn: unsupported sizes B={d.B} H={d.H} L={d.L} K={d.K} V={d.V} "
+                       "(need K = 128, V in {64, 128}, L a multiple of 64)")
+    dev = q.device
+    saved = torch.empty(nsaved, dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    o = torch.empty_like(v)
+    hT = torch.empty(d.B, d.H, d.K, d.V, dtype=torch.float32, device=dev) if want_final else None
+    a = _Args(dims=d, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
+              h0=_ptr(h0), o=_ptr(o), hT=_ptr(hT), saved=_ptr(saved), saved_bytes=nsaved,
+              status=_ptr(status))
+    _check(L_.lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(dev).cuda_stream))
+    return o, hT, saved, status
+
+
+def gdn_backward_raw(q, k, v, g, beta, h0, do, dhT, saved, status, scale: float):
+    """One backward call of the library.  Returns ``(dq, dk, dv, dg, dbeta, dh0)``."""
+    L_ = native.lib()
+    d = _dims(q, v, g, beta)
+    nscr = L_.lethe_gdn_scratch_bytes(ctypes.byref(d))
+    dev = q.device
+    scratch = torch.empty(nscr, dtype=torch.uint8, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dg = None if g is None else torch.empty_like(g)
+    dbeta = None if beta is None else torch.empty_like(beta)
+    dh0 = torch.empty(d.B, d.H, d.K, d.V, dtype=torch.float32, device=dev)
+    a = _Args(dims=d, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
+              h0=_ptr(h0), d_o=_ptr(do), dhT=_ptr(dhT), dq=_ptr(dq), dk=_ptr(dk), dv=_ptr(dv),
+              dg=_ptr(dg), dbeta=_ptr(dbeta), dh0=_ptr(dh0), saved=_ptr(saved),
+              saved_bytes=saved.numel(), scratch=_ptr(scratch), scratch_bytes=nscr,
+              status=_ptr(status))
+    _check(L_.lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(dev).cuda_stream))
+    return dq, dk, dv, dg, dbeta, dh0, scratch
+
+
+def _l2norm(x: Tensor, eps: float = 1e-6) -> Tensor:
+    # same epsilon placement as the reference (gdn_backward.py:9-10)
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+class _GdnChunk(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, h0, scale):
+        if not q.is_cuda:
+            raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+        K = q.shape[-1]
+        ctx.in_dtypes = tuple(None if t is None else t.dtype for t in (q, k, v, g, beta, h0))
+        ctx.pad_k = 0
+        q16, k16, v16 = _prep16(q), _prep16(k), _prep16(v)
+        g32, b32, h32 = _prep32(g), _prep32(beta), _prep32(h0)
+        if K == 64:
+            # the kernels are built for 128 key channels: pad with zero channels (exact)
+            ctx.pad_k = 64
+            q16 = torch.nn.functional.pad(q16, (0, 64))
+            k16 = torch.nn.functional.pad(k16, (0, 64))
+            if g32 is not None and g32.dim() == 4:
+                g32 = torch.nn.functional.pad(g32, (0, 64))
+            if h32 is not None:
+                h32 = torch.nn.functional.pad(h32, (0, 0, 0, 64))
+        o, hT, saved, status = gdn_forward_raw(q16, k16, v16, g32, b32, h32, scale)
+        ctx.save_for_backward(q16, k16, v16, g32, b32, h32, saved, status)
+        ctx.scale = scale
+        if ctx.pad_k:
+            hT = hT[:, :, :K].contiguous()
+        return o.to(v.dtype), hT
+
+    @staticmethod
+    def backward(ctx, do, dhT):
+        q16, k16, v16, g32, b32, h32, saved, status = ctx.saved_tensors
+        do16 = _prep16(do)
+        dhT32 = _prep32(dhT)
+        if ctx.pad_k and dhT32 is not None:
+            dhT32 = torch.nn.functional.pad(dhT32, (0, 0, 0, ctx.pad_k))
+        dq, dk, dv, dg, dbeta, dh0, _ = gdn_backward_raw(q16, k16, v16, g32, b32, h32, do16, dhT32,
+                                                        saved, status, ctx.scale)
+        if ctx.pad_k:
+            K = q16.shape[-1] - ctx.pad_k
+            dq, dk, dh0 = dq[..., :K], dk[..., :K], dh0[:, :, :K]
+            if dg is not None and dg.dim() == 4:
+                dg = dg[..., :K]
+        dts = ctx.in_dtypes
+        outs = [dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]),
+                None if dg is None else dg.to(dts[3]),
+                None if dbeta is None else dbeta.to(dts[4]),
+                None if dts[5] is None else dh0.to(dts[5]), None]
+        return tuple(outs)
+
+
+def gdn_chunk(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | None,
+              h0: Tensor | None = None, *, scale: float | None = None,
+              use_qk_l2norm: bool = False) -> tuple[Tensor, Tensor]:
+    """Chunked gated delta rule, differentiable.  Returns ``(o [B,L,H,V], h_T [B,H,K,V] fp32)``.
+
+    ``g``: per-token log decay, ``[B,L,H]`` (scalar gate), ``[B,L,H,K]`` (channel-wise) or None.
+    ``beta``: ``[B,L,H]`` (erase and write gate) or None for the variants without the delta term
+    (linear attention, GLA, SSD).  Gradients flow to q, k, v, g, beta and h0.
+    """
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    if use_qk_l2norm:
+        q, k = _l2norm(q.float()).to(q.dtype), _l2norm(k.float()).to(k.dtype)
+    return _GdnChunk.apply(q, k, v, g, beta, h0, float(scale))
