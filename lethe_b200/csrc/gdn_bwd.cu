@@ -1,8 +1,685 @@
-// Chunk-parallel backward kernels (placeholder while the forward is brought up).
+// Chunk-parallel backward kernels.  One CTA of 128 threads per chunk, tcgen05 products with
+// M = 128 and stacked 64-row operands as in the forward kernels.
+//
+//   bwd_pre    : Rb = (scale gamma q)^T do - w^T (A^T do)          input of the adjoint state scan
+//   bwd_stageb : dv2, dq, the Stage-B part of dk and of the gate gradient, dw
+//   bwd_wy     : the WY / triangular-inverse VJP: dv, dbeta, the rest of dk, and dg
+//
+// Reference (file:line in the reference project): reverse scan K#1 gdn2_assemble.py:71-99, closed
+// Stage B gdn2_assemble.py:521-585 (scalar-gate form: gate broadcast over channels, dg summed),
+// K#2 gdn2_assemble.py:102-147.
+//
+// Scalar-gate identities used to avoid per-channel work (i, s index tokens of the chunk):
+//   sum_d q~[i,d] dq_intra[i,d] = sum_s dA[i,s] A[i,s]            (row sums of E = dA . A)
+//   sum_d k[s,d] dk_intra[s,d]  = <v_new[s,:], (A^T do)[s,:]>     (column sums of E)
+//   sum_d dde[s,d]              = <v_new[s,:], (kd dh)[s,:]>
+// The gate gradient is a reverse cumulative sum in which large terms cancel (every -dde_i of a row
+// against the +sum_i dde_i of the chunk's last row, row sums of E against its column sums); each
+// such pair is therefore formed from the same fp32 numbers, as the reference's closed form does.
 #include "gdn_common.cuh"
 #include "host_util.h"
+
 namespace lg {
-int launch_bwd_pre(const Problem&, const CUtensorMap&, const CUtensorMap&, cudaStream_t) { return kErrFlags; }
-int launch_bwd_main(const Problem&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
-                    const CUtensorMap&, cudaStream_t) { return kErrFlags; }
+
+// ---------------------------------------------------------------------------------------------
+template <int V, bool DELTA>
+__global__ void __launch_bounds__(128)
+bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mdo) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* QG = sm;                    // 16 KB: scale gamma q (64 x 128)
+  unsigned char* Wt = QG + 16384;            // 16 KB: w
+  unsigned char* DO = Wt + 16384;            // do (64 x V)
+  unsigned char* TAt = DO + V * 128;         // 16 KB: [T | A]
+  unsigned char* DVL = TAt + 16384;          // A^T do (64 x V)
+  float* fs = reinterpret_cast<float*>(DVL + V * 128);
+  float* Gs = fs;
+  float* tmp = fs + 64;
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 256);
+    tmem_relinquish();
+  }
+  float gval = 0.f;
+  if (tid < 64 && p.gate == LETHE_GATE_SCALAR) gval = p.g[(static_cast<size_t>(b) * p.L + c * kC + tid) * p.H + h];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u));
+    for (int a = 0; a < 2; ++a) tma_load_4d(QG + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(DO + a * 8192, &mdo, bar_load, a * 64, h, c * kC, b);
+    if (DELTA) {
+      bulk_g2s(Wt, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, 16384, bar_load);
+      bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    }
+  }
+  const float G = chunk_cumsum(gval, tid, tmp);
+  if (tid < 64) Gs[tid] = G;
+  __syncthreads();
+  mbar_wait_warp(bar_load, 0, ctl, 401);
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15;
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(QG, r, ch, 64), x);
+    const float sg = p.scale * __expf(Gs[r]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] *= sg;
+    tile_st_chunk(QG, r, ch, 64, pack8_f16(x));
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(DO, r, ch, 64), x);
+    tile_st_chunk(DO, r, ch, 64, pack8_f16(x));
+  }
+  sync_for_issue();
+  uint32_t ph = 0;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  if (DELTA) {
+    // rows 64-127: A^T do
+    if (tid == 0) {
+      tc_fence_after();
+      issue_product(tmem, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+      issue_product(tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+      umma_commit(bar_mma);
+    }
+    wait_products(bar_mma, ph, ctl, 402);
+    if (tid >= 64) {
+#pragma unroll
+      for (int jb = 0; jb < V / 32; ++jb) {
+        float d[32];
+        tmem_ld32(tmem + lane_base + jb * 32, d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tile_st_chunk(DVL, tid - 64, jb * 4 + i, 64, pack8_f16(d + 8 * i));
+      }
+    }
+    sync_for_issue();
+    if (tid == 0) {
+      tc_fence_after();
+      issue_product(tmem + 128, Tile{smem_u32(Wt), 64, true}, Tile{smem_u32(DVL), 64, true}, V, 64, 1u, true);
+      umma_commit(bar_mma);
+    }
+  } else if (tid == 0) {
+    tc_fence_after();
+    issue_product(tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 403);
+  {
+    __half* Rg = reinterpret_cast<__half*>(p.scratch + p.lay.rb + static_cast<size_t>(z) * p.lay.sz_rb) +
+                 static_cast<size_t>(tid) * V;
+#pragma unroll
+    for (int jb = 0; jb < V / 32; ++jb) {
+      float d[32];
+      tmem_ld32(tmem + 128 + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Rg + jb * 32 + 8 * i) = pack8_f16(d + 8 * i);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stage B.  Accumulator regions (TMEM columns): cA [0,128) dv2 then dq_intra; cB [128,256)
+// [do; dv2] h^T; cC [256,320) do v_new^T; cD [320,448) Stage-B dk.
+// ---------------------------------------------------------------------------------------------
+template <int V, bool DELTA>
+__global__ void __launch_bounds__(128)
+bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mdo) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* X1 = sm;                       // 32 KB: rows 0-63 k, rows 64-127 kd
+  unsigned char* QT = X1 + 32768;               // 16 KB: q (64 x 128)
+  unsigned char* DD = QT + 16384;               // V*256: rows 0-63 do, rows 64-127 dv2
+  unsigned char* TAt = DD + V * 256;            // 16 KB: [T | A]
+  unsigned char* VNt = TAt + 16384;             // V*256: rows 0-63 v_new, rows 64-127 dec_end * v_new
+  unsigned char* Ht = VNt + V * 256;            // V*256: h entering the chunk
+  unsigned char* DHt = Ht + V * 256;            // V*256: dh
+  unsigned char* DS = DHt + V * 256;            // 16 KB: rows 0-63 scale*dA*ratio, rows 64-127 zero
+  float* fs = reinterpret_cast<float*>(DS + 16384);
+  float* Gs = fs;          // [64]
+  float* t3s = fs + 64;    // [64] column sum of E plus dde row sum
+  float* dde_s = fs + 208; // [64] dde row sums
+  float* dGs = fs + 128;   // [64]
+  float* tmp = fs + 192;   // [8]
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 272);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;   // token index of row 0 (stride H)
+  float gval = 0.f;
+  if (tid < 64 && p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
+
+  const unsigned char* dh_g = p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    }
+    for (int a = 0; a < V / 64; ++a) {
+      tma_load_4d(DD + a * 16384, &mdo, bar_load, a * 64, h, c * kC, b);
+      bulk_g2s(VNt + a * 16384, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn + a * 8192, 8192, bar_load);
+    }
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
+    bulk_g2s(DHt, dh_g, V * 256, bar_load);
+  }
+  const float G = chunk_cumsum(gval, tid, tmp);
+  if (tid < 64) Gs[tid] = G;
+  __syncthreads();
+  const float Glast = Gs[63];
+
+  mbar_wait_warp(bar_load, 0, ctl, 411);
+  // exp(G_last) <dh, h>: the two tile images share the swizzle, so the product is elementwise
+  float dhh = 0.f;
+  for (int idx = tid; idx < kK * V / 8; idx += 128) {
+    float x[8], y[8];
+    unpack8_f16(*reinterpret_cast<const uint4*>(DHt + idx * 16), x);
+    unpack8_f16(*reinterpret_cast<const uint4*>(Ht + idx * 16), y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dhh += x[i] * y[i];
+  }
+  dhh = cta_sum128(dhh, tid, tmp + 2) * __expf(Glast);
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15;
+    float x[8], y[8];
+    unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
+    tile_st_chunk(X1, r, ch, 128, pack8_f16(x));
+    const float de = __expf(Glast - Gs[r]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = x[i] * de;
+    tile_st_chunk(X1, 64 + r, ch, 128, pack8_f16(y));
+    unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
+    tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
+    if (ch < 8) tile_st_chunk(DS, 64 + r, ch, 128, make_uint4(0, 0, 0, 0));
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(DD, r, ch, 128), x);
+    tile_st_chunk(DD, r, ch, 128, pack8_f16(x));
+    unpack8_f16(tile_ld_chunk(VNt, r, ch, 128), x);
+    const float de = __expf(Glast - Gs[r]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] *= de;
+    tile_st_chunk(VNt, 64 + r, ch, 128, pack8_f16(x));
+  }
+  sync_for_issue();
+
+  uint32_t ph = 0;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  // ---- group 1: kd dh (rows 64-127 of cD), A^T do (rows 64-127 of cA), dA = do v_new^T (rows 0-63 of cC)
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(cD, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
+    issue_product(cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
+    issue_product(cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 128, false}, 64, V, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 412);
+  float t2 = 0.f;
+  if (tid >= 64) {
+    const int r = tid - 64;
+    float t3 = 0.f, dde = 0.f;
+    unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
+    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
+#pragma unroll
+    for (int jb = 0; jb < V / 32; ++jb) {
+      float d[32], d1[32];
+      tmem_ld32(cA + lane_base + jb * 32, d);
+      tmem_ld32(cD + lane_base + jb * 32, d1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float vn[8];
+        unpack8_f16(tile_ld_chunk(VNt, r, jb * 4 + i, 128), vn);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          t3 += vn[e] * d[8 * i + e];
+          dde += vn[e] * d1[8 * i + e];
+          d[8 * i + e] += d1[8 * i + e];
+        }
+        const uint4 pk = pack8_f16(d + 8 * i);
+        tile_st_chunk(DD, 64 + r, jb * 4 + i, 128, pk);
+        if (DELTA) *reinterpret_cast<uint4*>(dv2_g + sw128_chunk(r, jb * 4 + i, 64)) = pk;
+        else *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(d + 8 * i);
+      }
+    }
+    t3s[r] = t3 + dde;
+    dde_s[r] = dde;
+  } else {
+    const int r = tid;
+    float d[64];
+    tmem_ld32(cC + lane_base, d);
+    tmem_ld32(cC + lane_base + 32, d + 32);
+    tmem_ld_wait();
+    const float Gr = Gs[r];
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      float a[8], y[8];
+      unpack8_f16(tile_ld_chunk(TAt, 64 + r, s8, 128), a);   // A[r, s] (already holds scale * ratio)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int s = s8 * 8 + i;
+        const float da = (s <= r) ? d[s] : 0.f;
+        t2 += da * a[i];
+        y[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * da : 0.f;
+      }
+      tile_st_chunk(DS, r, s8, 128, pack8_f16(y));
+    }
+  }
+  sync_for_issue();
+
+  // ---- group 2: cB = [do; dv2] h^T;  cA = dAr k (rows 0-63 dq_intra);  cD = dAr^T q + (dec v_new) dh^T
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
+    issue_product(cA, Tile{smem_u32(DS), 128, false}, Tile{smem_u32(X1), 128, true}, 128, 64, 0u);
+    issue_product(cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
+    issue_product(cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 413);
+  float t1 = 0.f;
+  if (tid < 64) {
+    const int r = tid;
+    const float sg = p.scale * __expf(Gs[r]);
+    __nv_bfloat16* dq_g = p.dq + (tok0 + static_cast<size_t>(r) * p.H) * kK;
+    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(r) * p.H) * kK;
+    float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb) + r * kK;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float dqg[32], dqi[32];
+      tmem_ld32(cB + lane_base + jb * 32, dqg);
+      tmem_ld32(cA + lane_base + jb * 32, dqi);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float qv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(QT, r, jb * 4 + i, 64), qv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float a = sg * dqg[8 * i + e];
+          t1 += a * qv[e];
+          o8[e] = a + dqi[8 * i + e];
+        }
+        *reinterpret_cast<uint4*>(dq_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+      }
+      float dkv[32];
+      tmem_ld32(cD + lane_base + jb * 32, dkv);
+      tmem_ld_wait();
+      if (DELTA) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<float4*>(dkb_g + jb * 32 + 4 * i) =
+              make_float4(dkv[4 * i], dkv[4 * i + 1], dkv[4 * i + 2], dkv[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(dkv + 8 * i);
+      }
+    }
+  } else if (DELTA) {
+    const int r = tid - 64;
+    unsigned char* dw_g = p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float d[32];
+      tmem_ld32(cB + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) d[e] = -d[e];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(dw_g + sw128_chunk(r, jb * 4 + i, 64)) = pack8_f16(d + 8 * i);
+    }
+  }
+  __syncthreads();
+  // ---- Stage-B gate gradient of the chunk (before the reverse cumulative sum)
+  if (tid < 64) {
+    float dG = t1 + t2 - t3s[tid];
+    if (tid == 63) {
+      float sdde = 0.f;
+      for (int j = 0; j < 64; ++j) sdde += dde_s[j];
+      dG += dhh + sdde;
+    }
+    dGs[tid] = dG;
+    if (DELTA) reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid] = dG;
+  }
+  __syncthreads();
+  if (!DELTA && tid < 64 && p.gate == LETHE_GATE_SCALAR) {
+    float acc = 0.f;
+    for (int j = 63; j >= tid; --j) acc += dGs[j];
+    p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
+// WY / triangular-inverse VJP (delta variants only).  Accumulator regions: c0 [0,64) KK;
+// c1 [64,128) dT; c2 [128,192) X = dT T^T, later [128,256) sym k; c3 [192,256) dM;
+// c4 [256, 256+V+128) [dbv | dbgk].
+// ---------------------------------------------------------------------------------------------
+template <int V>
+__global__ void __launch_bounds__(128)
+bwd_wy_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* KB = sm;                       // 32 KB: rows 0-63 k, rows 64-127 beta gamma k
+  unsigned char* VT = KB + 32768;               // v (64 x V)
+  unsigned char* BVt = VT + V * 128;            // beta v
+  unsigned char* TAt = BVt + V * 128;           // 16 KB [T | A]
+  unsigned char* DV2t = TAt + 16384;            // dv2 (64 x V)
+  unsigned char* DWt = DV2t + V * 128;          // 16 KB dw (64 x 128), directly behind dv2
+  unsigned char* DTt = DWt + 16384;             // 8 KB dT (64 x 64)
+  unsigned char* XT = DTt + 8192;               // 8 KB X
+  unsigned char* SY = XT + 8192;                // 8 KB dkk + dkk^T, followed by 8 KB of padding
+  float* DK = reinterpret_cast<float*>(SY + 16384);   // fp32 [64][65]
+  float* fs = DK + 64 * 65;
+  float* Gs = fs;
+  float* dGs = fs + 64;
+  float* tmp = fs + 128;
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 136);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  float gval = 0.f, bval = 0.f;
+  if (tid < 64) {
+    if (p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
+    bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  const uint32_t c0 = tmem, c1 = tmem + 64, c2 = tmem + 128, c3 = tmem + 192, c4 = tmem + 256;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u);
+    for (int a = 0; a < 2; ++a) tma_load_4d(KB + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
+    bulk_g2s(DWt, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, 16384, bar_load);
+  }
+  const float G = chunk_cumsum(gval, tid, tmp);
+  if (tid < 64) {
+    Gs[tid] = G;
+    dGs[tid] = bval;   // reused below as the beta table until the gate gradient is formed
+  }
+  __syncthreads();
+  mbar_wait_warp(bar_load, 0, ctl, 421);
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15;
+    float x[8], y[8];
+    unpack8_bf16(tile_ld_chunk(KB, r, ch, 128), x);
+    tile_st_chunk(KB, r, ch, 128, pack8_f16(x));
+    const float bg = dGs[r] * __expf(Gs[r]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = x[i] * bg;
+    tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
+    tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
+    const float be = dGs[r];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] *= be;
+    tile_st_chunk(BVt, r, ch, 64, pack8_f16(x));
+  }
+  sync_for_issue();
+
+  uint32_t ph = 0;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  // ---- group 1: KK, dT = dv2 (beta v)^T + dw (beta gamma k)^T, [dbv | dbgk] = T^T [dv2 | dw]
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c0, Tile{smem_u32(KB), 128, false}, Tile{smem_u32(KB), 128, false}, 64, 128, 0u);
+    issue_product(c1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(BVt), 64, false}, 64, V, 0u);
+    issue_product(c1, Tile{smem_u32(DWt), 64, false}, Tile{smem_u32(KB) + 8192, 128, false}, 64, 128, 1u);
+    issue_product(c4, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V + 128, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 422);
+  if (tid < 64) {
+    float d[64];
+    tmem_ld32(c1 + lane_base, d);
+    tmem_ld32(c1 + lane_base + 32, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(DTt, tid, s8, 64, pack8_f16(d + 8 * s8));
+  }
+  sync_for_issue();
+  // ---- group 2: X = dT T^T
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c2, Tile{smem_u32(DTt), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 423);
+  if (tid < 64) {
+    float d[64];
+    tmem_ld32(c2 + lane_base, d);
+    tmem_ld32(c2 + lane_base + 32, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(XT, tid, s8, 64, pack8_f16(d + 8 * s8));
+  }
+  sync_for_issue();
+  // ---- group 3: dM = -T^T X
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c3, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(XT), 64, true}, 64, 64, 0u, true);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 424);
+  float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f;
+  float kk[64];
+  if (tid < 64) {
+    const int r = tid;
+    float dm[64];
+    tmem_ld32(c3 + lane_base, dm);
+    tmem_ld32(c3 + lane_base + 32, dm + 32);
+    tmem_ld32(c0 + lane_base, kk);
+    tmem_ld32(c0 + lane_base + 32, kk + 32);
+    tmem_ld_wait();
+    const float Gr = Gs[r];
+#pragma unroll
+    for (int s = 0; s < 64; ++s) {
+      const float ra = (s < r) ? __expf(Gr - Gs[s]) : 0.f;
+      const float x = (s < r) ? dm[s] * ra : 0.f;      // dM * ratio, strict lower
+      dbeta_m += x * kk[s];
+      const float dkk = x * bval;
+      rowsum_e += dkk * kk[s];
+      DK[r * 65 + s] = dkk;
+    }
+  }
+  __syncthreads();
+  if (tid < 64) {
+    const int r = tid;
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int s = s8 * 8 + i;
+        const float up = DK[s * 65 + r];          // dkk[s, r], non-zero for s > r
+        y[i] = DK[r * 65 + s] + up;
+        colsum_e += up * kk[s];                   // KK is symmetric
+      }
+      tile_st_chunk(SY, r, s8, 64, pack8_f16(y));
+    }
+  }
+  sync_for_issue();
+  // ---- group 4: (dkk + dkk^T) k
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c2, Tile{smem_u32(SY), 64, false}, Tile{smem_u32(KB), 128, true}, 128, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 425);
+  if (tid < 64) {
+    const int r = tid;
+    const float gam = __expf(Gs[r]);
+    const float bg = bval * gam;
+    // dv = beta * dbv,  r_i = <dbv, v>
+    float rv = 0.f;
+    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
+#pragma unroll
+    for (int jb = 0; jb < V / 32; ++jb) {
+      float d[32];
+      tmem_ld32(c4 + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float vv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(VT, r, jb * 4 + i, 64), vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          rv += d[8 * i + e] * vv[e];
+          o8[e] = bval * d[8 * i + e];
+        }
+        *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+      }
+    }
+    // dk = Stage-B part + sym k + beta gamma dbgk,  p_i = <dbgk, k>
+    float pk = 0.f;
+    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(r) * p.H) * kK;
+    const float* dkb_g = reinterpret_cast<const float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb) + r * kK;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float dbgk[32], sk[32];
+      tmem_ld32(c4 + V + lane_base + jb * 32, dbgk);
+      tmem_ld32(c2 + lane_base + jb * 32, sk);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float kv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(KB, r, jb * 4 + i, 128), kv);
+        const float4 b0 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i);
+        const float4 b1 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i + 4);
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          pk += dbgk[8 * i + e] * kv[e];
+          o8[e] = bb[e] + sk[8 * i + e] + bg * dbgk[8 * i + e];
+        }
+        *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+      }
+    }
+    p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
+    const float dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[r];
+    dGs[r] = dgb + rowsum_e - colsum_e + bval * pk * gam;
+  }
+  __syncthreads();
+  if (tid < 64 && p.gate == LETHE_GATE_SCALAR) {
+    float acc = 0.f;
+    for (int j = 63; j >= tid; --j) acc += dGs[j];
+    p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <typename Kern>
+static int set_smem(Kern kern, int smem) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess ? kOk : kErrLaunch;
+}
+
+template <int V, bool DELTA>
+static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
+  const int smem = 16384 * 3 + V * 256 + 72 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (set_smem(bwd_pre_kernel<V, DELTA>, smem)) return kErrLaunch;
+  bwd_pre_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mdo);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+template <int V, bool DELTA>
+static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo,
+                           cudaStream_t st) {
+  const int smem = 32768 + 16384 + V * 256 * 4 + 16384 * 2 + 272 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (set_smem(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
+  bwd_stageb_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mdo);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+template <int V>
+static int launch_wy_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
+  const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 * 2 + 16384 + 64 * 65 * 4 + 136 * 4 +
+                   static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (set_smem(bwd_wy_kernel<V>, smem)) return kErrLaunch;
+  bwd_wy_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
+  if (p.V == 64) return p.delta ? launch_pre_t<64, true>(p, mq, mdo, st) : launch_pre_t<64, false>(p, mq, mdo, st);
+  return p.delta ? launch_pre_t<128, true>(p, mq, mdo, st) : launch_pre_t<128, false>(p, mq, mdo, st);
+}
+
+int launch_bwd_main(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                    const CUtensorMap& mdo, cudaStream_t st) {
+  int e;
+  if (p.V == 64) e = p.delta ? launch_stageb_t<64, true>(p, mq, mk, mdo, st) : launch_stageb_t<64, false>(p, mq, mk, mdo, st);
+  else e = p.delta ? launch_stageb_t<128, true>(p, mq, mk, mdo, st) : launch_stageb_t<128, false>(p, mq, mk, mdo, st);
+  if (e || !p.delta) return e;
+  return p.V == 64 ? launch_wy_t<64>(p, mk, mv, st) : launch_wy_t<128>(p, mk, mv, st);
+}
+
 }  // namespace lg

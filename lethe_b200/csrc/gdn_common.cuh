@@ -12,7 +12,8 @@
 //     U     64 x V  image: u = T (beta v)
 //     P     32 KB   image, 128 x 128: kd^T w           (state transition, without the decay)
 //     R     128 x V fp16 row-major: kd^T u            (state input)
-//     Hc    128 x V image: state entering the chunk
+//     Hc    128 x V image: state entering the chunk; NT + 1 records per (b, h), the last one being
+//           the final state, so record index is (b*H + h)*(NT + 1) + c
 //     VN    64 x V  image: v_new = u - w h
 //     AD    128 fp32: exp(G_last) per key channel     (the decay of the chunk)
 //   scratch (backward only)
@@ -56,7 +57,7 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
   l.u = o;  o = align_up(o + Z * l.sz_u, 1024);
   l.p = o;  o = align_up(o + Z * l.sz_p, 1024);
   l.r = o;  o = align_up(o + Z * l.sz_r, 1024);
-  l.hc = o; o = align_up(o + Z * l.sz_hc, 1024);
+  l.hc = o; o = align_up(o + (Z + static_cast<size_t>(d.B) * d.H) * l.sz_hc, 1024);
   l.vn = o; o = align_up(o + Z * l.sz_vn, 1024);
   l.ad = o; o = align_up(o + Z * l.sz_ad, 1024);
   l.saved_total = o;
@@ -111,5 +112,36 @@ struct CtaShared {
   uint32_t tmem_slot;
   int abort_flag;
 };
+
+
+__device__ __forceinline__ unsigned char* align1024(unsigned char* p) {
+  return reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+
+// Called by all threads before one thread issues products that read tiles written by this CTA's
+// threads and / or overwrite accumulators that this CTA's threads have been reading.
+__device__ __forceinline__ void sync_for_issue() {
+  tc_fence_before();
+  fence_proxy_async();
+  __syncthreads();
+}
+
+// Called by all threads after the issuing thread committed to `bar`: waits for the products.
+__device__ __forceinline__ void wait_products(uint64_t* bar, uint32_t& phase, const CtaCtl& ctl, int code) {
+  __syncwarp();
+  mbar_wait_warp(bar, phase, ctl, code);
+  phase ^= 1u;
+  tc_fence_after();
+}
+
+// Deterministic sum over the 128 threads of a CTA (fixed tree).  `red` is a shared float[4].
+__device__ __forceinline__ float cta_sum128(float x, int tid, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = x;
+  __syncthreads();
+  return (red[0] + red[1]) + (red[2] + red[3]);
+}
 
 }  // namespace lg

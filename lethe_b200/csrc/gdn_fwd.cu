@@ -12,10 +12,6 @@ namespace lg {
 
 constexpr int kMs = 68;  // row stride (floats) of the fp32 copy of M used by the inverse
 
-__device__ __forceinline__ unsigned char* align1024(unsigned char* p) {
-  return reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
-}
-
 // ---------------------------------------------------------------------------------------------
 // prepare: per chunk
 //   G = cumsum(g), ratio[i,s] = exp(G_i - G_s) (s <= i)
@@ -330,7 +326,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
         bulk_g2s(WQ + a * 16384, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w + a * 8192, 8192, bar_load);
     }
     if (!DELTA) bulk_g2s(VN, Ug, V * 128, bar_load);   // v_new = u = v
-    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z) * p.lay.sz_hc, V * 256, bar_load);
+    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
   }
   // u row of this thread (threads 0-63), kept packed

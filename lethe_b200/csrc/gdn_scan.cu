@@ -96,7 +96,7 @@ scan_kernel(const Problem p) {
     }
     // state seen by this chunk: image record for the chunk-parallel kernels
     {
-      unsigned char* rec = Xg + z * szx;
+      unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
     }
@@ -131,6 +131,11 @@ scan_kernel(const Problem p) {
 #pragma unroll
       for (int j = 0; j < kVs; ++j) x[j] = a * x[j] + rr[j];
     }
+  }
+  if (!ADJOINT) {   // the final state as one more record (the adjoint of the gate needs it)
+    unsigned char* rec = Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx;
+    *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
+    *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
   }
   float* xT = ADJOINT ? p.dh0 : p.hT;
   if (xT) {

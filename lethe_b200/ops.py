@@ -41,6 +41,13 @@ class _Args(ctypes.Structure):
     ]
 
 
+def _workspace(nbytes: int, dev) -> Tensor:
+    """Byte buffer whose first element is 1024-byte aligned (the tile images inside need it)."""
+    raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
+    off = (-raw.data_ptr()) % 1024
+    return raw[off:off + nbytes]
+
+
 def _ptr(t: Tensor | None):
     return None if t is None else t.data_ptr()
 
@@ -86,7 +93,7 @@ def gdn_forward_raw(q, k, v, g, beta, h0, scale: float, want_final: bool = True)
         raise GdnError(f"lethe_gdn: unsupported sizes B={d.B} H={d.H} L={d.L} K={d.K} V={d.V} "
                        "(need K = 128, V in {64, 128}, L a multiple of 64)")
     dev = q.device
-    saved = torch.empty(nsaved, dtype=torch.uint8, device=dev)
+    saved = _workspace(nsaved, dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     o = torch.empty_like(v)
     hT = torch.empty(d.B, d.H, d.K, d.V, dtype=torch.float32, device=dev) if want_final else None
@@ -103,7 +110,7 @@ def gdn_backward_raw(q, k, v, g, beta, h0, do, dhT, saved, status, scale: float)
     d = _dims(q, v, g, beta)
     nscr = L_.lethe_gdn_scratch_bytes(ctypes.byref(d))
     dev = q.device
-    scratch = torch.empty(nscr, dtype=torch.uint8, device=dev)
+    scratch = _workspace(nscr, dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dg = None if g is None else torch.empty_like(g)
     dbeta = None if beta is None else torch.empty_like(beta)

@@ -44,8 +44,8 @@ def test_forward_records(V, delta, mild):
     ad = records(saved, off["ad"], sz["ad"], Z, torch.float32).reshape(*shp, 128).double()
     errs["ad"] = float((ad - st.a).abs().max())
     errs["R"] = scale_rel(records(saved, off["r"], sz["r"], Z).reshape(*shp, 128, V).double(), st.R)
-    errs["h"] = scale_rel(unswizzle(records(saved, off["hc"], sz["hc"], Z), 128, V).reshape(*shp, 128, V).double(),
-                          st.h[:, :, :-1])
+    errs["h"] = scale_rel(unswizzle(records(saved, off["hc"], sz["hc"], Z + B * H), 128, V)
+                          .reshape(B, H, NT + 1, 128, V).double(), st.h)
     errs["vn"] = scale_rel(unswizzle(records(saved, off["vn"], sz["vn"], Z), 64, V).reshape(*shp, 64, V).double(),
                            st.v_new)
     errs["u"] = scale_rel(unswizzle(records(saved, off["u"], sz["u"], Z), 64, V).reshape(*shp, 64, V).double(), st.u)

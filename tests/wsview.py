@@ -29,7 +29,7 @@ def layout(B, H, L, V, gate=1, delta=1):
     off, o = {}, 0
     for n in ("ta", "w", "u", "p", "r", "hc", "vn", "ad"):
         off[n] = o
-        o = al(o + Z * sz[n])
+        o = al(o + (Z + B * H if n == "hc" else Z) * sz[n])   # states: NT + 1 records per (b, h)
     sz2 = dict(rb=128 * V * 2, dh=128 * V * 2, dv2=64 * V * 2, dw=16384, dkb=64 * 128 * 4,
                dgb=(64 * 128 if gate == 2 else 64) * 4)
     off2, o = {}, 0
