@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Benchmark of the chunked gated-delta-rule training step (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one forward + backward of the op over one batch of seeded synthetic inputs.  Per GPU the
+workload is the configuration the metric is quoted on: scalar-gate gated delta rule, B=2, H=8,
+L=2048, d_k=128, d_v=64, chunk 64, bf16 inputs, initial state.  With N > 1 every rank runs that
+workload on its own (batch x head) shard -- the path shards without communication -- so scaling is
+"weak" and `value` is the whole job's tokens (B*L per rank) per second.
+
+Prints ONE JSON line (rank 0).  `value`: inputs resident in HBM, CUDA events around every step, L2
+flushed between steps, max over ranks.  `e2e`: the same step through the public op
+(`lethe_b200.ops.gdn_chunk` + autograd) with pinned host buffers, host->device copies of all inputs
+and device->host copies of all results inside the timed region.  `roofline`: the dominant kernel,
+timed alone with CUDA events.  `cpu_baseline`: the CPU oracle (a port of the reference's PyTorch CPU
+chunkwise path) timed on this machine's host cores on a bounded sample.
+`--impl reference` times that CPU path only (rank 0; other ranks exit).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, L, H, K, V, gate, delta)
+    "gdn_scalar_B2_H8_L2048_dk128_dv64": (2, 2048, 8, 128, 64, "scalar", True),
+    "gdn_scalar_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "scalar", True),
+    "ssd_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "scalar", False),
+    "la_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "none", False),
+}
+DEFAULT = "gdn_scalar_B2_H8_L2048_dk128_dv64"
+METRIC = "GDN fwd+bwd tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": reasons}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline (oracle port of the reference's PyTorch CPU chunkwise path)
+# ------------------------------------------------------------------------------------------------
+def cpu_baseline(workload: str, budget_s: float = 20.0):
+    """Times oracle.chunk_fwd_bwd (fp32, all host threads) on a head-subset of the workload and
+    scales to the full head count (heads are independent).  Returns the cpu_baseline object."""
+    from lethe_b200.synth import make_inputs
+    from oracle.gdn_oracle import chunk_fwd_bwd
+
+    B, L, H, K, V, gate, delta = WORKLOADS[workload]
+    hs = 1
+    inp = make_inputs(1, L, hs, K, V, gate=gate, delta=delta, seed=0)
+    f = {k: (None if t is None else t.float()) for k, t in inp.items()}
+
+    def run():
+        t0 = time.perf_counter()
+        chunk_fwd_bwd(f["q"], f["k"], f["v"], f["g"], f["beta"], f["h0"], f["do"], scale=K ** -0.5)
+        return time.perf_counter() - t0
+
+    run()                                    # warm
+    reps, spent, ts = 0, 0.0, []
+    while reps < 3 or (spent < budget_s * 0.5 and reps < 20):
+        t = run()
+        ts.append(t)
+        spent += t
+        reps += 1
+    t1 = statistics.median(ts)               # seconds for 1 batch row x 1 head
+    tokens_per_s = L / (t1 * H)              # a token spans all H heads
+    return {"value": tokens_per_s, "unit": "tokens/s", "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": f"oracle.chunk_fwd_bwd fp32 on B=1,H={hs},L={L} of {workload}, median of {reps} "
+                      f"runs of {t1:.2f}s, scaled linearly to H={H} heads"}
+
+
+# ------------------------------------------------------------------------------------------------
+def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool) -> int:
+    """Bytes one launch of `kernel` must move: each input tile and each record read once, each
+    result written once (Z chunks, 64 tokens each; K = 128)."""
+    qk, vv, img = 64 * 128 * 2, 64 * V * 2, 128 * V * 2
+    ta, w, p_, r, f32k = 16384, 16384, 32768, 128 * V * 2, 64 * 128 * 4
+    per = {
+        "prepare": 2 * qk + vv + ta + vv + r + ((w + p_) if delta else 0) + 512,
+        "scan_fwd": (p_ if delta else 0) + r + img + 512,
+        "output": qk + ta + img + vv + vv + vv + (w if delta else 0),
+        "bwd_pre": qk + vv + r + ((w + ta) if delta else 0),
+        "scan_bwd": (p_ if delta else 0) + r + img + 512,
+        "stageb": 2 * qk + vv + ta + vv + 2 * img + qk + (vv + w + f32k if delta else qk + vv),
+        "wy": qk + vv + ta + vv + w + f32k + qk + vv,
+    }[kernel]
+    return per * Z
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    B, L, H, K, V, gate, delta = WORKLOADS[args.workload]
+    config = {"workload": args.workload, "B_per_gpu": B, "H": H, "L": L, "d_k": K, "d_v": V, "chunk": 64,
+              "gate": gate, "delta": delta, "sharding": "batch x head, no collective",
+              "l2": "flushed between steps (256 MiB write)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb = cpu_baseline(args.workload)
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": 1e3 * B * L / cb["value"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "config": config,
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0},
+                "note": "the reference's CPU chunkwise path is Python and does not travel; this is the "
+                        "CPU oracle port of it, timed on this machine's host cores"}
+        print(json.dumps(line))
+        return
+
+    import torch.distributed as dist
+    from lethe_b200 import ops
+    from lethe_b200.synth import make_inputs
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=1 + rank)
+    host = {k: t.pin_memory() for k, t in inp.items() if t is not None}
+    d = {k: t.to(dev) for k, t in host.items()}
+    g, beta, h0 = d.get("g"), d.get("beta"), d.get("h0")
+    scale = K ** -0.5
+    gate_code = {"none": 0, "scalar": 1, "channel": 2}[gate]
+    buf = ops.GdnBuffers(B, L, H, K, V, gate_code, delta, dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(mask_f=0, mask_b=0):
+        ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, mask_f)
+        ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale, mask_b)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            flush.zero_()
+            fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        barrier()
+        for a, b in evs:
+            flush.zero_()
+            a.record()
+            fn()
+            b.record()
+        barrier()
+        return sum(a.elapsed_time(b) for a, b in evs) / steps     # ms per step
+
+    # the clock sampler runs over the whole measured part of the program (timed steps, per-kernel
+    # timing and the end-to-end leg): the timed steps alone last only a few milliseconds
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed(step, args.steps, max(args.warmup, 3))
+    ops.check_status(buf.status)
+
+    # ---- per-kernel timing (each kernel alone, same records in place), for the roofline
+    kern = {}
+    names_f = [("prepare", 1), ("scan_fwd", 2), ("output", 4)]
+    names_b = [("bwd_pre", 1), ("scan_bwd", 2), ("stageb", 4)] + ([("wy", 8)] if delta else [])
+    step()
+    for name, m in names_f:
+        kern[name] = timed(lambda m=m: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, m),
+                           max(args.steps, 10), 3)
+    for name, m in names_b:
+        kern[name] = timed(lambda m=m: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"],
+                                                         None, scale, m), max(args.steps, 10), 3)
+    fwd_ms = timed(lambda: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale), args.steps, 3)
+    bwd_ms = timed(lambda: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale),
+                   args.steps, 3)
+
+    # ---- end to end through the public op, host buffers in, host buffers out
+    outs_host = {}
+
+    def e2e_step():
+        leaves = {}
+        for n in ("q", "k", "v", "g", "beta", "h0"):
+            leaves[n] = host[n].to(dev, non_blocking=True).requires_grad_(True) if n in host else None
+        do_d = host["do"].to(dev, non_blocking=True)
+        o, hT = ops.gdn_chunk(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], leaves["h0"],
+                              scale=scale)
+        names = [n for n in leaves if leaves[n] is not None]
+        grads = torch.autograd.grad(o, [leaves[n] for n in names], do_d)
+        res = [("o", o.detach()), ("hT", hT.detach())] + [("d" + n, t) for n, t in zip(names, grads)]
+        for n, t in res:
+            if n not in outs_host:
+                outs_host[n] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            outs_host[n].copy_(t, non_blocking=True)
+
+    e2e_ms = timed(e2e_step, max(3, args.steps // 2), 3)
+    clocks = sampler.stop()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in outs_host.values())
+
+    vals = torch.tensor([ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, fwd_ms, bwd_ms = (float(x) for x in vals.tolist())
+    tokens = B * L * world
+
+    if rank == 0:
+        hbm, tf, which = peaks()
+        Z, BH = B * H * (L // 64), B * H
+        top = max(kern, key=kern.get)
+        ab = algorithmic_bytes(top, Z, BH, V, delta)
+        achieved = ab / (kern[top] * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate (bf16 in/out)",
+            "data": "synthetic", "config": config,
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "kernel_ms": kern,
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * (7 if delta else 6),
+            "clocks": clocks,
+            "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                         "frac": achieved / hbm, "peak_source": which, "traffic": None,
+                         "launch_ms": kern[top], "algorithmic_bytes": ab},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.workload)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -74,6 +74,10 @@ typedef struct LetheGdnArgs {
   void* scratch;          /* backward only; lethe_gdn_scratch_bytes                          */
   size_t scratch_bytes;
   int32_t* status;        /* device word, see above                                         */
+  /* Profiling aid: 0 runs every kernel of the call.  Otherwise bit i selects kernel i of the call  */
+  /* (forward: 1 prepare, 2 state scan, 4 output; backward: 1 scan input, 2 adjoint scan,           */
+  /* 4 Stage B, 8 WY VJP); a partial call relies on the records left by an earlier full call.       */
+  uint32_t kernel_mask;
 } LetheGdnArgs;
 
 /* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */

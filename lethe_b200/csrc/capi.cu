@@ -10,7 +10,7 @@ int launch_output(const Problem&, const CUtensorMap&, cudaStream_t);
 int launch_scan(const Problem&, bool adjoint, cudaStream_t);
 int launch_bwd_pre(const Problem&, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t);
 int launch_bwd_main(const Problem&, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                    const CUtensorMap& mdo, cudaStream_t);
+                    const CUtensorMap& mdo, cudaStream_t, uint32_t mask);
 
 static bool dims_ok(const LetheGdnDims& d) {
   if (d.B <= 0 || d.H <= 0 || d.L <= 0) return false;
@@ -98,9 +98,11 @@ extern "C" int lethe_gdn_forward(const LetheGdnArgs* a, void* stream) {
   if ((e = token_map(&mq, a->q, a->dims, kK))) return e;
   if ((e = token_map(&mk, a->k, a->dims, kK))) return e;
   if ((e = token_map(&mv, a->v, a->dims, a->dims.V))) return e;
-  if ((e = launch_prepare(p, mq, mk, mv, st))) return e;
-  if ((e = launch_scan(p, false, st))) return e;
-  return launch_output(p, mq, st);
+  const uint32_t m = a->kernel_mask ? a->kernel_mask : 7u;
+  if ((m & 1u) && (e = launch_prepare(p, mq, mk, mv, st))) return e;
+  if ((m & 2u) && (e = launch_scan(p, false, st))) return e;
+  if ((m & 4u) && (e = launch_output(p, mq, st))) return e;
+  return kOk;
 }
 
 extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
@@ -114,9 +116,11 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
   if ((e = token_map(&mk, a->k, a->dims, kK))) return e;
   if ((e = token_map(&mv, a->v, a->dims, a->dims.V))) return e;
   if ((e = token_map(&mdo, a->d_o, a->dims, a->dims.V))) return e;
-  if ((e = launch_bwd_pre(p, mq, mdo, st))) return e;
-  if ((e = launch_scan(p, true, st))) return e;
-  return launch_bwd_main(p, mq, mk, mv, mdo, st);
+  const uint32_t m = a->kernel_mask ? a->kernel_mask : 15u;
+  if ((m & 1u) && (e = launch_bwd_pre(p, mq, mdo, st))) return e;
+  if ((m & 2u) && (e = launch_scan(p, true, st))) return e;
+  if ((m & 12u) && (e = launch_bwd_main(p, mq, mk, mv, mdo, st, m))) return e;
+  return kOk;
 }
 
 extern "C" const char* lethe_gdn_strerror(int code) {

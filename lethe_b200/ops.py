@@ -37,7 +37,7 @@ class _Args(ctypes.Structure):
         ("dg", ctypes.c_void_p), ("dbeta", ctypes.c_void_p), ("dh0", ctypes.c_void_p),
         ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
-        ("status", ctypes.c_void_p),
+        ("status", ctypes.c_void_p), ("kernel_mask", ctypes.c_uint32),
     ]
 
 
@@ -69,12 +69,6 @@ def check_status(status: Tensor) -> None:
         raise GdnError(f"lethe_gdn: device-side wait timed out at site {code}; results are invalid")
 
 
-def _dims(q: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | None) -> _Dims:
-    B, L, H, K = q.shape
-    gate = GATE_NONE if g is None else (GATE_SCALAR if g.dim() == 3 else GATE_CHANNEL)
-    return _Dims(B, H, L, K, v.shape[-1], gate, 0 if beta is None else 1)
-
-
 def _prep16(t: Tensor) -> Tensor:
     return t.to(torch.bfloat16).contiguous()
 
@@ -83,45 +77,74 @@ def _prep32(t: Tensor | None) -> Tensor | None:
     return None if t is None else t.to(torch.float32).contiguous()
 
 
-def gdn_forward_raw(q, k, v, g, beta, h0, scale: float, want_final: bool = True):
+class GdnBuffers:
+    """Every buffer one forward + backward of a fixed problem size needs, allocated once.  The C
+    library allocates nothing: callers that must not allocate per step (a training loop, the
+    benchmark) keep one of these and call ``forward_into`` / ``backward_into``."""
+
+    def __init__(self, B, L, H, K, V, gate: int, delta: bool, device, backward: bool = True,
+                 saved: Tensor | None = None, status: Tensor | None = None):
+        L_ = native.lib()
+        self.dims = _Dims(B, H, L, K, V, gate, 1 if delta else 0)
+        nsaved = L_.lethe_gdn_saved_bytes(ctypes.byref(self.dims))
+        if nsaved == 0:
+            raise GdnError(f"lethe_gdn: unsupported sizes B={B} H={H} L={L} K={K} V={V} "
+                           "(need K = 128, V in {64, 128}, L a multiple of 64)")
+        bf, f32 = torch.bfloat16, torch.float32
+        self.saved = _workspace(nsaved, device) if saved is None else saved
+        self.status = torch.zeros(1, dtype=torch.int32, device=device) if status is None else status
+        self.o = torch.empty(B, L, H, V, dtype=bf, device=device)
+        self.hT = torch.empty(B, H, K, V, dtype=f32, device=device)
+        self.scratch = None
+        if backward:
+            self.scratch = _workspace(L_.lethe_gdn_scratch_bytes(ctypes.byref(self.dims)), device)
+            self.dq = torch.empty(B, L, H, K, dtype=bf, device=device)
+            self.dk = torch.empty(B, L, H, K, dtype=bf, device=device)
+            self.dv = torch.empty(B, L, H, V, dtype=bf, device=device)
+            gshape = (B, L, H, K) if gate == GATE_CHANNEL else (B, L, H)
+            self.dg = torch.empty(gshape, dtype=f32, device=device) if gate != GATE_NONE else None
+            self.dbeta = torch.empty(B, L, H, dtype=f32, device=device) if delta else None
+            self.dh0 = torch.empty(B, H, K, V, dtype=f32, device=device)
+
+
+def forward_into(buf: GdnBuffers, q, k, v, g, beta, h0, scale: float, kernel_mask: int = 0) -> None:
+    """Enqueue the forward kernels on the current stream; results land in ``buf.o`` / ``buf.hT``."""
+    a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
+              h0=_ptr(h0), o=_ptr(buf.o), hT=_ptr(buf.hT), saved=_ptr(buf.saved),
+              saved_bytes=buf.saved.numel(), status=_ptr(buf.status), kernel_mask=kernel_mask)
+    _check(native.lib().lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
+
+
+def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, kernel_mask: int = 0) -> None:
+    """Enqueue the backward kernels; gradients land in ``buf.dq`` ... ``buf.dh0``."""
+    a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
+              h0=_ptr(h0), d_o=_ptr(do), dhT=_ptr(dhT), dq=_ptr(buf.dq), dk=_ptr(buf.dk), dv=_ptr(buf.dv),
+              dg=_ptr(buf.dg), dbeta=_ptr(buf.dbeta), dh0=_ptr(buf.dh0), saved=_ptr(buf.saved),
+              saved_bytes=buf.saved.numel(), scratch=_ptr(buf.scratch), scratch_bytes=buf.scratch.numel(),
+              status=_ptr(buf.status), kernel_mask=kernel_mask)
+    _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
+
+
+def _gate_code(g: Tensor | None) -> int:
+    return GATE_NONE if g is None else (GATE_SCALAR if g.dim() == 3 else GATE_CHANNEL)
+
+
+def gdn_forward_raw(q, k, v, g, beta, h0, scale: float):
     """One forward call of the library.  Inputs must be CUDA tensors: q, k, v bf16 contiguous
-    ``[B, L, H, D]``; g, beta, h0 fp32.  Returns ``(o, hT, saved, status)``."""
-    L_ = native.lib()
-    d = _dims(q, v, g, beta)
-    nsaved = L_.lethe_gdn_saved_bytes(ctypes.byref(d))
-    if nsaved == 0:
-        raise GdnError(f"lethe_gdn: unsupported sizes B={d.B} H={d.H} L={d.L} K={d.K} V={d.V} "
-                       "(need K = 128, V in {64, 128}, L a multiple of 64)")
-    dev = q.device
-    saved = _workspace(nsaved, dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    o = torch.empty_like(v)
-    hT = torch.empty(d.B, d.H, d.K, d.V, dtype=torch.float32, device=dev) if want_final else None
-    a = _Args(dims=d, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
-              h0=_ptr(h0), o=_ptr(o), hT=_ptr(hT), saved=_ptr(saved), saved_bytes=nsaved,
-              status=_ptr(status))
-    _check(L_.lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(dev).cuda_stream))
-    return o, hT, saved, status
+    ``[B, L, H, D]``; g, beta, h0 fp32.  Returns ``(o, hT, saved, status)`` in fresh buffers."""
+    B, L, H, K = q.shape
+    buf = GdnBuffers(B, L, H, K, v.shape[-1], _gate_code(g), beta is not None, q.device, backward=False)
+    forward_into(buf, q, k, v, g, beta, h0, scale)
+    return buf.o, buf.hT, buf.saved, buf.status
 
 
 def gdn_backward_raw(q, k, v, g, beta, h0, do, dhT, saved, status, scale: float):
-    """One backward call of the library.  Returns ``(dq, dk, dv, dg, dbeta, dh0)``."""
-    L_ = native.lib()
-    d = _dims(q, v, g, beta)
-    nscr = L_.lethe_gdn_scratch_bytes(ctypes.byref(d))
-    dev = q.device
-    scratch = _workspace(nscr, dev)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    dg = None if g is None else torch.empty_like(g)
-    dbeta = None if beta is None else torch.empty_like(beta)
-    dh0 = torch.empty(d.B, d.H, d.K, d.V, dtype=torch.float32, device=dev)
-    a = _Args(dims=d, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
-              h0=_ptr(h0), d_o=_ptr(do), dhT=_ptr(dhT), dq=_ptr(dq), dk=_ptr(dk), dv=_ptr(dv),
-              dg=_ptr(dg), dbeta=_ptr(dbeta), dh0=_ptr(dh0), saved=_ptr(saved),
-              saved_bytes=saved.numel(), scratch=_ptr(scratch), scratch_bytes=nscr,
-              status=_ptr(status))
-    _check(L_.lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(dev).cuda_stream))
-    return dq, dk, dv, dg, dbeta, dh0, scratch
+    """One backward call of the library.  Returns ``(dq, dk, dv, dg, dbeta, dh0, scratch)``."""
+    B, L, H, K = q.shape
+    buf = GdnBuffers(B, L, H, K, v.shape[-1], _gate_code(g), beta is not None, q.device,
+                     saved=saved, status=status)
+    backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale)
+    return buf.dq, buf.dk, buf.dv, buf.dg, buf.dbeta, buf.dh0, buf.scratch
 
 
 def _l2norm(x: Tensor, eps: float = 1e-6) -> Tensor:

@@ -53,8 +53,10 @@ def test_forward_records(V, delta, mild):
         errs["T"] = scale_rel(ta[..., :64, :], st.T)
         errs["w"] = scale_rel(unswizzle(records(saved, off["w"], sz["w"], Z), 64, 128).reshape(*shp, 64, 128).double(),
                               st.w)
-        errs["P"] = scale_rel(unswizzle(records(saved, off["p"], sz["p"], Z), 128, 128).reshape(*shp, 128, 128).double(),
-                              st.P)
+        # P = kd^T w carries the chunk's whole decay: ~1e-80 under the strong draw, zero in fp16, so
+        # it is compared on an absolute floor (entries of h, which P multiplies, are O(1))
+        Pg = unswizzle(records(saved, off["p"], sz["p"], Z), 128, 128).reshape(*shp, 128, 128).double()
+        errs["P"] = float((Pg - st.P).abs().max()) / max(float(st.P.abs().max()), 1e-3)
     errs["hT"] = scale_rel(hT.double(), st.h[:, :, -1])
     errs["o"] = scale_rel(o.double(), st.o)
     report(f"fwd V={V} delta={delta} mild={mild}", errs)
