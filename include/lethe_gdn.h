@@ -91,6 +91,22 @@ int lethe_gdn_forward(const LetheGdnArgs* args, void* cuda_stream);
  * Replaces gdn_backward.py:16-57 / gdn2_assemble.py:242-314,601-696,711-775 of the reference. */
 int lethe_gdn_backward(const LetheGdnArgs* args, void* cuda_stream);
 
+/* Forward without a caller-supplied workspace, for hosts that cannot allocate device memory (a
+ * plug-in inside a runtime whose memory pool is off limits, a server that fixed its memory budget
+ * at start-up).  It has no counterpart in the reference.  Same arguments and results as
+ * lethe_gdn_forward, except that args->saved / saved_bytes are ignored: the per-chunk records go
+ * through a 16 MiB array built into the library (lethe_gdn_forward_static_capacity()), so
+ *   - the problem must satisfy lethe_gdn_saved_bytes(dims) <= 16 MiB, else the call returns the
+ *     "needs more workspace" error and launches nothing;
+ *   - the records are not kept for a backward pass (inference / evaluation only);
+ *   - all calls on one GPU share the array: calls that could overlap on the GPU must be put on one
+ *     stream; nothing needs clearing between calls;
+ *   - the first call on each GPU looks up the array's device address; make that call before any
+ *     stream capture starts.
+ * The call itself allocates nothing (no cudaMalloc, no cudaFree, no library that would). */
+int lethe_gdn_forward_static(const LetheGdnArgs* args, void* cuda_stream);
+size_t lethe_gdn_forward_static_capacity(void);
+
 /* Text for a return code of the calls above or for a device status code. */
 const char* lethe_gdn_strerror(int code);
 

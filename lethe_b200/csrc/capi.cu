@@ -1,6 +1,8 @@
 // C-ABI entry points: argument checks, tensor maps, kernel sequence.  See include/lethe_gdn.h.
 #include <string.h>
 
+#include <mutex>
+
 #include "gdn_common.cuh"
 #include "host_util.h"
 
@@ -123,6 +125,61 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
   return kOk;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no allocator to offer: a plug-in that is handed tensors by a
+// runtime whose memory pool it may not touch, an inference server that has pinned its whole memory
+// budget at start-up, a caller inside a region where cudaMalloc is forbidden.  They cannot supply
+// the `saved` workspace the forward kernels pass their per-chunk records through.  For them the
+// workspace lives in the array below, which is part of the library image: every GPU that loads the
+// library holds these 16 MiB (+1 KiB for alignment) until the process exits.
+//
+// The array is shared by every call on a device and keeps whatever the last call wrote.  Nothing
+// in it has to start at zero: each forward kernel writes every record of a chunk before a later
+// kernel of the same call reads it, and no record of an earlier call is read.  Two calls whose
+// kernels overlap on the GPU (different streams, or different threads on different streams) would
+// race on it; callers serialise them on one stream.
+//
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, looked up once per device by the first call on that device (with that
+// device current).  That first call should therefore happen before any stream capture begins.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kStaticSavedBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_static_saved[kStaticSavedBytes + 1024];
+static unsigned char* g_static_saved_ptr[64] = {};
+static std::mutex g_static_saved_mu;
+
+static int static_saved_address(unsigned char** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kErrDriver;
+  std::lock_guard<std::mutex> lock(g_static_saved_mu);
+  if (!g_static_saved_ptr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_saved) != cudaSuccess || !ptr) return kErrDriver;
+    const uintptr_t a = (reinterpret_cast<uintptr_t>(ptr) + 1023) & ~static_cast<uintptr_t>(1023);
+    g_static_saved_ptr[dev] = reinterpret_cast<unsigned char*>(a);   // the records want 1 KiB alignment
+  }
+  *out = g_static_saved_ptr[dev];
+  return kOk;
+}
+
+extern "C" size_t lethe_gdn_forward_static_capacity(void) { return kStaticSavedBytes; }
+
+extern "C" int lethe_gdn_forward_static(const LetheGdnArgs* a, void* stream) {
+  if (!a) return kErrNull;
+  if (!dims_ok(a->dims)) return kErrDims;
+  if (make_layout(a->dims).saved_total > kStaticSavedBytes) return kErrTooLarge;
+  unsigned char* ws = nullptr;
+  const int e = static_saved_address(&ws);
+  if (e) return e;
+  LetheGdnArgs b = *a;
+  b.saved = ws;
+  b.saved_bytes = kStaticSavedBytes;
+  b.kernel_mask = 0;
+  return lethe_gdn_forward(&b, stream);
+}
+
 extern "C" const char* lethe_gdn_strerror(int code) {
   switch (code) {
     case kOk: return "ok";
@@ -133,7 +190,7 @@ extern "C" const char* lethe_gdn_strerror(int code) {
     case kErrDriver: return "tensor-map encoding failed";
     case kErrLaunch: return "kernel launch failed";
     case kErrFlags: return "unsupported gate / delta combination";
-    case kErrTooLarge: return "problem exceeds the capacity of this entry point";
+    case kErrTooLarge: return "problem needs more workspace than the library's built-in 16 MiB (use lethe_gdn_forward)";
     default: break;
   }
   if (code >= 100) return "device-side wait timed out (status word holds the wait site)";
