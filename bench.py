@@ -38,6 +38,7 @@ WORKLOADS = {
     # name: (B, L, H, K, V, gate, delta)
     "gdn_scalar_B2_H8_L2048_dk128_dv64": (2, 2048, 8, 128, 64, "scalar", True),
     "gdn_scalar_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "scalar", True),
+    "gdn_scalar_B4_H8_L4096_dk128_dv64": (4, 4096, 8, 128, 64, "scalar", True),     # > L2: for ncu DRAM figures
     "ssd_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "scalar", False),
     "la_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "none", False),
 }

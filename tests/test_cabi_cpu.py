@@ -1,0 +1,71 @@
+"""CPU checks of the C-ABI library: it loads, exports every symbol the header declares, sizes its
+workspaces as documented and rejects bad arguments before touching a GPU."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from lethe_b200 import _build, native, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _build.build()
+    return native.lib()
+
+
+def test_exports_every_declared_symbol(lib):
+    hdr = open(os.path.join(ROOT, "include", "lethe_gdn.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    names = set(re.findall(r"\b(lethe_[a-z0-9_]+)\s*\(", hdr))
+    assert {"lethe_gdn_forward", "lethe_gdn_backward", "lethe_gdn_saved_bytes", "lethe_gdn_scratch_bytes",
+            "lethe_gdn_strerror", "lethe_gdn_forward_static", "lethe_probe_umma"} <= names
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_workspace_sizes(lib):
+    d = ops._Dims(2, 8, 2048, 128, 64, 1, 1)
+    saved = lib.lethe_gdn_saved_bytes(ctypes.byref(d))
+    scratch = lib.lethe_gdn_scratch_bytes(ctypes.byref(d))
+    Z = 2 * 8 * 32
+    per_saved = 16384 + 16384 + 8192 + 32768 + 16384 + 16384 + 8192 + 512
+    assert Z * per_saved <= saved <= Z * per_saved + 16 * 16384 + 8 * 1024
+    assert scratch >= Z * (16384 + 16384 + 8192 + 16384 + 32768 + 256)
+    for bad in (ops._Dims(2, 8, 2000, 128, 64, 1, 1), ops._Dims(2, 8, 2048, 96, 64, 1, 1),
+                ops._Dims(2, 8, 2048, 128, 32, 1, 1), ops._Dims(0, 8, 2048, 128, 64, 1, 1),
+                ops._Dims(2, 8, 2048, 128, 64, 5, 1)):
+        assert lib.lethe_gdn_saved_bytes(ctypes.byref(bad)) == 0
+
+
+def test_argument_errors_come_before_any_launch(lib):
+    d = ops._Dims(1, 1, 64, 128, 64, 1, 1)
+    a = ops._Args(dims=d, scale=1.0)                      # all pointers null
+    rc = lib.lethe_gdn_forward(ctypes.byref(a), None)
+    assert rc != 0 and b"null" in lib.lethe_gdn_strerror(rc)
+    a = ops._Args(dims=ops._Dims(1, 1, 65, 128, 64, 1, 1), scale=1.0)
+    rc = lib.lethe_gdn_forward(ctypes.byref(a), None)
+    assert rc != 0 and b"sizes" in lib.lethe_gdn_strerror(rc)
+    # misaligned tensor pointer (fake host addresses: nothing is dereferenced before the checks)
+    a = ops._Args(dims=d, scale=1.0, q=0x1008, k=0x2000, v=0x3000, g=0x4000, beta=0x5000, o=0x6000,
+                  saved=0x100000, saved_bytes=1 << 30, status=0x7000)
+    rc = lib.lethe_gdn_forward(ctypes.byref(a), None)
+    assert rc != 0 and b"aligned" in lib.lethe_gdn_strerror(rc)
+    a.q = 0x1000
+    a.saved_bytes = 1024                                   # workspace too small
+    rc = lib.lethe_gdn_forward(ctypes.byref(a), None)
+    assert rc != 0 and b"workspace" in lib.lethe_gdn_strerror(rc)
+    assert lib.lethe_gdn_strerror(0) == b"ok"
+    assert b"timed out" in lib.lethe_gdn_strerror(412)
+
+
+def test_op_refuses_cpu_tensors():
+    import torch
+
+    q = torch.zeros(1, 64, 1, 128)
+    with pytest.raises(ops.GdnError):
+        ops.gdn_chunk(q, q, torch.zeros(1, 64, 1, 64), None, None)
