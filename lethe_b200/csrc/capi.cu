@@ -8,6 +8,7 @@
 
 namespace lg {
 int launch_prepare(const Problem&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_prepare_cw(const Problem&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
 int launch_output(const Problem&, const CUtensorMap&, cudaStream_t);
 int launch_scan(const Problem&, bool adjoint, cudaStream_t);
 int launch_bwd_pre(const Problem&, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t);
@@ -39,7 +40,7 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   if (!a) return kErrNull;
   const LetheGdnDims& d = a->dims;
   if (!dims_ok(d)) return kErrDims;
-  if (d.gate == LETHE_GATE_CHANNEL) return kErrFlags;   // channel-wise gate: not built yet
+  if (d.gate == LETHE_GATE_CHANNEL && backward) return kErrFlags;   // channel-wise backward: not built yet
   if (!a->q || !a->k || !a->v || !a->saved || !a->status) return kErrNull;
   if (d.gate != LETHE_GATE_NONE && !a->g) return kErrNull;
   if (d.delta && !a->beta) return kErrNull;
@@ -101,7 +102,8 @@ extern "C" int lethe_gdn_forward(const LetheGdnArgs* a, void* stream) {
   if ((e = token_map(&mk, a->k, a->dims, kK))) return e;
   if ((e = token_map(&mv, a->v, a->dims, a->dims.V))) return e;
   const uint32_t m = a->kernel_mask ? a->kernel_mask : 7u;
-  if ((m & 1u) && (e = launch_prepare(p, mq, mk, mv, st))) return e;
+  if ((m & 1u) && (e = (p.gate == LETHE_GATE_CHANNEL ? launch_prepare_cw(p, mq, mk, mv, st)
+                                                     : launch_prepare(p, mq, mk, mv, st)))) return e;
   if ((m & 2u) && (e = launch_scan(p, false, st))) return e;
   if ((m & 4u) && (e = launch_output(p, mq, st))) return e;
   return kOk;

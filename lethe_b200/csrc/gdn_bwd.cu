@@ -22,7 +22,7 @@
 namespace lg {
 
 // ---------------------------------------------------------------------------------------------
-template <int V, bool DELTA>
+template <int V, bool DELTA, bool CW>
 __global__ void __launch_bounds__(128)
 bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mdo) {
   extern __shared__ unsigned char smem_raw[];
@@ -36,6 +36,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   float* Gs = fs;
   float* tmp = fs + 64;
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
+  float* Gt = fs + 128;     // channel-wise gate only
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
@@ -69,15 +70,21 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
+  if (CW) gate_tile_cw(p.g, (static_cast<size_t>(b) * p.L + c * kC) * p.H + h, p.H, tid, Gt);
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 401);
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8];
     unpack8_bf16(tile_ld_chunk(QG, r, ch, 64), x);
-    const float sg = p.scale * __expf(Gs[r]);
+    if (CW) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] *= sg;
+      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[r * kK + ch * 8 + i]);
+    } else {
+      const float sg = p.scale * __expf(Gs[r]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] *= sg;
+    }
     tile_st_chunk(QG, r, ch, 64, pack8_f16(x));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
@@ -644,11 +651,11 @@ static int set_smem(Kern kern, int smem) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess ? kOk : kErrLaunch;
 }
 
-template <int V, bool DELTA>
+template <int V, bool DELTA, bool CW>
 static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
-  const int smem = 16384 * 3 + V * 256 + 72 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (set_smem(bwd_pre_kernel<V, DELTA>, smem)) return kErrLaunch;
-  bwd_pre_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mdo);
+  const int smem = 16384 * 3 + V * 256 + 128 * 4 + (CW ? 32768 : 0) + 1024;
+  if (set_smem(bwd_pre_kernel<V, DELTA, CW>, smem)) return kErrLaunch;
+  bwd_pre_kernel<V, DELTA, CW><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mdo);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V, bool DELTA>
@@ -669,8 +676,12 @@ static int launch_wy_t(const Problem& p, const CUtensorMap& mk, const CUtensorMa
 }
 
 int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
-  if (p.V == 64) return p.delta ? launch_pre_t<64, true>(p, mq, mdo, st) : launch_pre_t<64, false>(p, mq, mdo, st);
-  return p.delta ? launch_pre_t<128, true>(p, mq, mdo, st) : launch_pre_t<128, false>(p, mq, mdo, st);
+  if (p.gate == LETHE_GATE_CHANNEL) {
+    if (p.V == 64) return p.delta ? launch_pre_t<64, true, true>(p, mq, mdo, st) : launch_pre_t<64, false, true>(p, mq, mdo, st);
+    return p.delta ? launch_pre_t<128, true, true>(p, mq, mdo, st) : launch_pre_t<128, false, true>(p, mq, mdo, st);
+  }
+  if (p.V == 64) return p.delta ? launch_pre_t<64, true, false>(p, mq, mdo, st) : launch_pre_t<64, false, false>(p, mq, mdo, st);
+  return p.delta ? launch_pre_t<128, true, false>(p, mq, mdo, st) : launch_pre_t<128, false, false>(p, mq, mdo, st);
 }
 
 // mask bit 4: Stage B, bit 8: WY VJP (delta variants only)

@@ -106,6 +106,17 @@ __device__ __forceinline__ float chunk_cumsum(float x, int tid, float* tmp) {
   return x;
 }
 
+// Channel-wise gate: cumulative log decay of the chunk, Gt[i * 128 + d]; thread d owns channel d.
+// `tok0` is the token index of the chunk's first row for this head (tokens of a head are H apart).
+__device__ __forceinline__ void gate_tile_cw(const float* g, size_t tok0, int H, int tid, float* Gt) {
+  float acc = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < kC; ++i) {
+    acc += g[(tok0 + static_cast<size_t>(i) * H) * kK + tid];
+    Gt[i * kK + tid] = acc;
+  }
+}
+
 // Control block at the start of every kernel: barriers, TMEM slot, abort flag.
 struct CtaShared {
   uint64_t bar[8];

@@ -1,0 +1,326 @@
+// Channel-wise gate (one log decay per token, head and key channel): the `prepare` kernel.
+//
+// With a per-channel decay the ratio exp(G_i,d - G_s,d) sits inside the contraction over d, so
+// M[i,s] = beta_i sum_d k[i,d] k[s,d] exp(G_i,d - G_s,d) and A[i,s] are not plain Gram products
+// (reference: gdn2_chunkwise_cw.py:155-157,168-169).  Splitting the ratio as exp(G_i - G_ref) *
+// exp(G_ref - G_s) is only safe when both exponents are <= 0, i.e. when s <= ref <= i.  The 64-token
+// chunk is therefore cut into four blocks of 16 rows:
+//   * row block I against earlier blocks (s < 16 I): reference row a_I = 16 I.  Left operand rows
+//     x[i] exp(G_i - G_{a_I}) (one tile serves all I: blocks are disjoint row ranges), right operand
+//     rows k[s] exp(G_{a_I} - G_s) for s < 16 I (three row ranges packed into one tile).  Three
+//     tcgen05 products with N = 16, 32, 48.
+//   * the four diagonal 16 x 16 blocks: exact per-pair exponentials on the CUDA cores, while the
+//     products run.
+// Everything after M and A (inverse, WY factors, state map) is the scalar-gate kernel's, with
+// per-channel decays in the operand scalings.
+#include "gdn_common.cuh"
+#include "host_util.h"
+
+namespace lg {
+
+constexpr int kMsC = 68;
+
+template <int V, bool DELTA>
+__global__ void __launch_bounds__(128)
+prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
+                  const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* KQ = sm;                      // 32 KB: rows 0-63 k, 64-127 q (fp16); later M (fp32), then [w | u]
+  unsigned char* LA = KQ + 32768;              // 32 KB: rows 0-63 k exp(G_i - G_a), rows 64-127 q exp(G_i - G_a)
+  unsigned char* KR = LA + 32768;              // 32 KB: rows [0,16) [16,48) [48,96): k exp(G_{a_I} - G_s), I = 1, 2, 3
+  float* Gt = reinterpret_cast<float*>(KR + 32768);   // 32 KB: cumulative log decay [64][128]
+  unsigned char* BGK = reinterpret_cast<unsigned char*>(Gt) + 32768;   // 16 KB
+  unsigned char* BV = BGK + 16384;             // V*128
+  unsigned char* KD = BV + V * 128;            // 16 KB
+  unsigned char* TA = KD + 16384;              // 16 KB
+  float* fs = reinterpret_cast<float*>(TA + 16384);
+  float* Adg = fs;              // [64][16] diagonal blocks of A
+  float* Mdg = fs + 1024;       // [64][16] diagonal blocks of M
+  float* betas = fs + 2048;     // [64]
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 2112);
+  float* Msm = reinterpret_cast<float*>(KQ);
+  unsigned char* WU = KQ;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 256);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  if (DELTA && tid < 64) betas[tid] = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 32768u + V * 128u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(KQ + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(KQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    }
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
+  }
+  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+  reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[63 * kK + tid]);
+  __syncthreads();
+
+  // ---- operand tiles
+  mbar_wait_warp(bar_load, 0, ctl, 501);
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15, d0 = ch * 8;
+    const int blk = r >> 4;
+    float kx[8], qx[8], y[8], gr[8], ga[8], gl[8];
+    unpack8_bf16(tile_ld_chunk(KQ, r, ch, 128), kx);
+    unpack8_bf16(tile_ld_chunk(KQ, 64 + r, ch, 128), qx);
+    tile_st_chunk(KQ, r, ch, 128, pack8_f16(kx));
+    tile_st_chunk(KQ, 64 + r, ch, 128, pack8_f16(qx));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      gr[e] = Gt[r * kK + d0 + e];
+      ga[e] = Gt[(blk * 16) * kK + d0 + e];
+      gl[e] = Gt[63 * kK + d0 + e];
+    }
+    float ea[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ea[e] = __expf(gr[e] - ga[e]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = kx[e] * ea[e];
+    tile_st_chunk(LA, r, ch, 128, pack8_f16(y));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = qx[e] * ea[e];
+    tile_st_chunk(LA, 64 + r, ch, 128, pack8_f16(y));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(gl[e] - gr[e]);
+    tile_st_chunk(KD, r, ch, 64, pack8_f16(y));
+    if (DELTA) {
+      const float be = betas[r];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * be * __expf(gr[e]);
+      tile_st_chunk(BGK, r, ch, 64, pack8_f16(y));
+    }
+    for (int I = blk + 1; I < 4; ++I) {     // row r is a source row for every later row block I
+      const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[(I * 16) * kK + d0 + e] - gr[e]);
+      tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
+    }
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(BV, r, ch, 64), x);
+    const float be = DELTA ? betas[r] : 1.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] *= be;
+    tile_st_chunk(BV, r, ch, 64, pack8_f16(x));
+  }
+  sync_for_issue();
+
+  // ---- off-diagonal blocks on the tensor cores: columns [0,16) I=1, [16,48) I=2, [48,96) I=3
+  uint32_t ph = 0;
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(tmem + 0, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR), 128, false}, 16, 128, 0u);
+    issue_product(tmem + 16, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 16 * 128, 128, false}, 32, 128, 0u);
+    issue_product(tmem + 48, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 48 * 128, 128, false}, 48, 128, 0u);
+    umma_commit(bar_mma);
+  }
+  __syncwarp();
+  // ---- diagonal blocks, exact: pair (i, s) of one block, s <= i
+  for (int pp = tid; pp < 4 * 136; pp += 128) {
+    const int blk = pp / 136, t = pp % 136;
+    int ii = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
+    while ((ii + 1) * (ii + 2) / 2 <= t) ++ii;
+    while (ii * (ii + 1) / 2 > t) --ii;
+    const int ss = t - ii * (ii + 1) / 2;
+    const int i = blk * 16 + ii, s = blk * 16 + ss;
+    float acc_a = 0.f, acc_m = 0.f;
+#pragma unroll 4
+    for (int ch = 0; ch < 16; ++ch) {
+      float qi[8], ki[8], ks[8];
+      unpack8_f16(tile_ld_chunk(KQ, 64 + i, ch, 128), qi);
+      unpack8_f16(tile_ld_chunk(KQ, i, ch, 128), ki);
+      unpack8_f16(tile_ld_chunk(KQ, s, ch, 128), ks);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ex = __expf(Gt[i * kK + ch * 8 + e] - Gt[s * kK + ch * 8 + e]);
+        const float kse = ks[e] * ex;
+        acc_a += qi[e] * kse;
+        acc_m += ki[e] * kse;
+      }
+    }
+    Adg[i * 16 + ss] = p.scale * acc_a;
+    Mdg[i * 16 + ss] = (DELTA && ss < ii) ? betas[i] * acc_m : 0.f;
+  }
+  __syncthreads();
+  wait_products(bar_mma, ph, ctl, 502);
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  {
+    float d[96];
+    tmem_ld32(tmem + lane_base, d);
+    tmem_ld32(tmem + lane_base + 32, d + 32);
+    tmem_ld32(tmem + lane_base + 64, d + 64);
+    tmem_ld_wait();
+    const int r = tid & 63, I = r >> 4;
+    float row[64];
+#pragma unroll
+    for (int s = 0; s < 64; ++s) row[s] = 0.f;
+    if (I == 1) {
+#pragma unroll
+      for (int s = 0; s < 16; ++s) row[s] = d[s];
+    } else if (I == 2) {
+#pragma unroll
+      for (int s = 0; s < 32; ++s) row[s] = d[16 + s];
+    } else if (I == 3) {
+#pragma unroll
+      for (int s = 0; s < 48; ++s) row[s] = d[48 + s];
+    }
+    if (tid < 64) {
+      if (DELTA) {
+        const float be = betas[r];
+#pragma unroll
+        for (int s = 0; s < 64; ++s) {
+          float m = row[s] * be;                               // off-diagonal blocks (zero beyond 16 I)
+          if ((s >> 4) == I) m = (s < r) ? Mdg[r * 16 + (s & 15)] : 0.f;
+          Msm[r * kMsC + s] = m;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int s8 = 0; s8 < 8; ++s8) {
+        float a[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int s = s8 * 8 + e;
+          float x = row[s] * p.scale;
+          if ((s >> 4) == I) x = (s <= r) ? Adg[r * 16 + (s & 15)] : 0.f;
+          a[e] = x;
+        }
+        tile_st_chunk(TA, 64 + r, s8, 128, pack8_f16(a));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- T = (I + M)^-1 (fp32, one column per thread)
+  if (tid < 64) {
+    float col[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) col[i] = 0.f;
+    if (DELTA) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float acc = (i == tid) ? 1.f : 0.f;
+#pragma unroll
+        for (int s4 = 0; s4 < (i + 3) / 4; ++s4) {
+          const float4 m = *reinterpret_cast<const float4*>(&Msm[i * kMsC + 4 * s4]);
+          acc -= m.x * col[4 * s4];
+          if (4 * s4 + 1 < i) acc -= m.y * col[4 * s4 + 1];
+          if (4 * s4 + 2 < i) acc -= m.z * col[4 * s4 + 2];
+          if (4 * s4 + 3 < i) acc -= m.w * col[4 * s4 + 3];
+        }
+        col[i] = acc;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      const float t = DELTA ? col[i] : ((i == tid) ? 1.f : 0.f);
+      *reinterpret_cast<__half*>(TA + sw128_off(i, tid, 128)) = __float2half_rn(t);
+    }
+  }
+  sync_for_issue();
+
+  if (DELTA) {
+    if (tid == 0) {
+      tc_fence_after();
+      issue_product(tmem, Tile{smem_u32(TA), 128, false}, Tile{smem_u32(BGK), 64, true}, 128 + V, 64, 0u);
+      umma_commit(bar_mma);
+      bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
+      bulk_commit();
+    }
+    wait_products(bar_mma, ph, ctl, 503);
+    if (tid < 64) {
+#pragma unroll 1
+      for (int jb = 0; jb < (128 + V) / 32; ++jb) {
+        float d[32];
+        tmem_ld32(tmem + lane_base + jb * 32, d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tile_st_chunk(WU, tid, jb * 4 + i, 64, pack8_f16(d + 8 * i));
+      }
+    }
+    sync_for_issue();
+  } else if (tid == 0) {
+    bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
+    bulk_commit();
+  }
+
+  constexpr int N3 = DELTA ? 128 + V : V;
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(tmem, Tile{smem_u32(KD), 64, true}, Tile{smem_u32(DELTA ? WU : BV), 64, true}, N3, 64, 0u);
+    umma_commit(bar_mma);
+    if (DELTA) {
+      bulk_s2g(p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, WU, 16384);
+      bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, WU + 16384, V * 128);
+    } else {
+      bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, BV, V * 128);
+    }
+    bulk_commit();
+  }
+  wait_products(bar_mma, ph, ctl, 504);
+  {
+    unsigned char* Pg = p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p;
+    __half* Rg = reinterpret_cast<__half*>(p.saved + p.lay.r + static_cast<size_t>(z) * p.lay.sz_r) +
+                 static_cast<size_t>(tid) * V;
+#pragma unroll 1
+    for (int jb = 0; jb < N3 / 32; ++jb) {
+      float d[32];
+      tmem_ld32(tmem + lane_base + jb * 32, d);
+      tmem_ld_wait();
+      if (DELTA && jb < 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(Pg + sw128_chunk(tid, jb * 4 + i, 128)) = pack8_f16(d + 8 * i);
+      } else {
+        const int c0 = (jb - (DELTA ? 4 : 0)) * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Rg + c0 + 8 * i) = pack8_f16(d + 8 * i);
+      }
+    }
+  }
+  if (tid == 0) bulk_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+template <int V, bool DELTA>
+static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
+                               const CUtensorMap& mv, cudaStream_t st) {
+  const int smem = 32768 * 4 + 16384 + V * 128 + 16384 + 16384 + 2112 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  auto kern = prepare_cw_kernel<V, DELTA>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
+  kern<<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mv);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+int launch_prepare_cw(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                      cudaStream_t st) {
+  if (p.V == 64) return p.delta ? launch_prepare_cw_t<64, true>(p, mq, mk, mv, st) : launch_prepare_cw_t<64, false>(p, mq, mk, mv, st);
+  return p.delta ? launch_prepare_cw_t<128, true>(p, mq, mk, mv, st) : launch_prepare_cw_t<128, false>(p, mq, mk, mv, st);
+}
+
+}  // namespace lg

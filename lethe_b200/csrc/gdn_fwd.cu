@@ -279,7 +279,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
 //   o = qg h + A v_new                                       (product 2 accumulates onto rows 64-127)
 // Reference: gdn2_chunkwise.py:146-153.
 // ---------------------------------------------------------------------------------------------
-template <int V, bool DELTA>
+template <int V, bool DELTA, bool CW>
 __global__ void __launch_bounds__(128)
 output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   extern __shared__ unsigned char smem_raw[];
@@ -292,6 +292,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   float* Gs = fs;
   float* tmp = fs + 64;
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
+  float* Gt = fs + 128;     // channel-wise gate only: cumulative log decay [64][128]
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
@@ -337,6 +338,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
+  if (CW) gate_tile_cw(p.g, (static_cast<size_t>(b) * p.L + c * kC) * p.H + h, p.H, tid, Gt);
   __syncthreads();
 
   mbar_wait_warp(bar_load, 0, ctl, 211);
@@ -344,9 +346,14 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8];
     unpack8_bf16(tile_ld_chunk(WQ, 64 + r, ch, 128), x);
-    const float sg = p.scale * __expf(Gs[r]);
+    if (CW) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] *= sg;
+      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[r * kK + ch * 8 + i]);
+    } else {
+      const float sg = p.scale * __expf(Gs[r]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] *= sg;
+    }
     tile_st_chunk(WQ, 64 + r, ch, 128, pack8_f16(x));
     if (!DELTA) tile_st_chunk(WQ, r, ch, 128, make_uint4(0, 0, 0, 0));
   }
@@ -424,10 +431,10 @@ static int launch_prepare_t(const Problem& p, const CUtensorMap& mq, const CUten
   kern<<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
-template <int V, bool DELTA>
+template <int V, bool DELTA, bool CW>
 static int launch_output_t(const Problem& p, const CUtensorMap& mq, cudaStream_t st) {
-  const int smem = 32768 + V * 256 + 16384 + V * 128 + 72 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
-  auto kern = output_kernel<V, DELTA>;
+  const int smem = 32768 + V * 256 + 16384 + V * 128 + 128 * 4 + (CW ? 32768 : 0) + 1024;
+  auto kern = output_kernel<V, DELTA, CW>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
   kern<<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
@@ -439,8 +446,12 @@ int launch_prepare(const Problem& p, const CUtensorMap& mq, const CUtensorMap& m
   return p.delta ? launch_prepare_t<128, true>(p, mq, mk, mv, st) : launch_prepare_t<128, false>(p, mq, mk, mv, st);
 }
 int launch_output(const Problem& p, const CUtensorMap& mq, cudaStream_t st) {
-  if (p.V == 64) return p.delta ? launch_output_t<64, true>(p, mq, st) : launch_output_t<64, false>(p, mq, st);
-  return p.delta ? launch_output_t<128, true>(p, mq, st) : launch_output_t<128, false>(p, mq, st);
+  if (p.gate == LETHE_GATE_CHANNEL) {
+    if (p.V == 64) return p.delta ? launch_output_t<64, true, true>(p, mq, st) : launch_output_t<64, false, true>(p, mq, st);
+    return p.delta ? launch_output_t<128, true, true>(p, mq, st) : launch_output_t<128, false, true>(p, mq, st);
+  }
+  if (p.V == 64) return p.delta ? launch_output_t<64, true, false>(p, mq, st) : launch_output_t<64, false, false>(p, mq, st);
+  return p.delta ? launch_output_t<128, true, false>(p, mq, st) : launch_output_t<128, false, false>(p, mq, st);
 }
 
 }  // namespace lg

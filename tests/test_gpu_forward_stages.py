@@ -27,12 +27,13 @@ def run_forward(B, L, H, V, delta=True, gate="scalar", mild=False, seed=0, with_
     return inp, o.cpu(), hT.cpu(), saved, st
 
 
+@pytest.mark.parametrize("gate", ["scalar", "channel"])
 @pytest.mark.parametrize("V", [64, 128])
 @pytest.mark.parametrize("delta", [True, False])
 @pytest.mark.parametrize("mild", [False, True])
-def test_forward_records(V, delta, mild):
+def test_forward_records(V, delta, mild, gate):
     B, L, H = 2, 256, 2
-    inp, o, hT, saved, st = run_forward(B, L, H, V, delta=delta, mild=mild)
+    inp, o, hT, saved, st = run_forward(B, L, H, V, delta=delta, mild=mild, gate=gate)
     Z, sz, off, _, _ = layout(B, H, L, V)
     NT = L // 64
     shp = (B, H, NT)
@@ -59,6 +60,6 @@ def test_forward_records(V, delta, mild):
         errs["P"] = float((Pg - st.P).abs().max()) / max(float(st.P.abs().max()), 1e-3)
     errs["hT"] = scale_rel(hT.double(), st.h[:, :, -1])
     errs["o"] = scale_rel(o.double(), st.o)
-    report(f"fwd V={V} delta={delta} mild={mild}", errs)
+    report(f"fwd gate={gate} V={V} delta={delta} mild={mild}", errs)
     for n, e in errs.items():
         assert e < (5e-3 if n == "o" else tol), (n, e, errs)
