@@ -14,6 +14,8 @@ int launch_scan(const Problem&, bool adjoint, cudaStream_t);
 int launch_bwd_pre(const Problem&, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t);
 int launch_bwd_main(const Problem&, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     const CUtensorMap& mdo, cudaStream_t, uint32_t mask);
+int launch_bwd_main_cw(const Problem&, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                       const CUtensorMap& mdo, cudaStream_t, uint32_t mask);
 
 static bool dims_ok(const LetheGdnDims& d) {
   if (d.B <= 0 || d.H <= 0 || d.L <= 0) return false;
@@ -40,7 +42,6 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   if (!a) return kErrNull;
   const LetheGdnDims& d = a->dims;
   if (!dims_ok(d)) return kErrDims;
-  if (d.gate == LETHE_GATE_CHANNEL && backward) return kErrFlags;   // channel-wise backward: not built yet
   if (!a->q || !a->k || !a->v || !a->saved || !a->status) return kErrNull;
   if (d.gate != LETHE_GATE_NONE && !a->g) return kErrNull;
   if (d.delta && !a->beta) return kErrNull;
@@ -123,7 +124,8 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
   const uint32_t m = a->kernel_mask ? a->kernel_mask : 15u;
   if ((m & 1u) && (e = launch_bwd_pre(p, mq, mdo, st))) return e;
   if ((m & 2u) && (e = launch_scan(p, true, st))) return e;
-  if ((m & 12u) && (e = launch_bwd_main(p, mq, mk, mv, mdo, st, m))) return e;
+  if ((m & 12u) && (e = (p.gate == LETHE_GATE_CHANNEL ? launch_bwd_main_cw(p, mq, mk, mv, mdo, st, m)
+                                                      : launch_bwd_main(p, mq, mk, mv, mdo, st, m)))) return e;
   return kOk;
 }
 

@@ -23,6 +23,10 @@
 //     DW    64 x 128 image: adjoint of w
 //     DKB   64 x 128 fp32: key gradient of Stage B
 //     DGB   64 x 128 fp32 (channel-wise) or 64 fp32 (scalar): gate-gradient of Stage B before the cumsum
+//   channel-wise gate only:
+//     DA    64 x 64 image: scale * tril(do v_new^T)         DM   64 x 64 image: strict_lower(-T^T dT T^T)
+//     DQP   64 x 128 fp32: the part of dq (Stage B), then of d(beta gamma k) (WY VJP), outside the
+//           decay-coupled sums
 #pragma once
 #include <stddef.h>
 #include <stdint.h>
@@ -38,7 +42,7 @@ constexpr int kK = 128;   // key dimension
 struct Layout {
   // byte offsets of the record arrays inside `saved` / `scratch`, and record sizes
   size_t ta, w, u, p, r, hc, vn, ad, saved_total;
-  size_t rb, dh, dv2, dw, dkb, dgb, scratch_total;
+  size_t rb, dh, dv2, dw, dkb, dgb, da, dm, dqp, scratch_total;
   size_t sz_ta, sz_w, sz_u, sz_p, sz_r, sz_hc, sz_vn, sz_ad;
   size_t sz_rb, sz_dh, sz_dv2, sz_dw, sz_dkb, sz_dgb;
 };
@@ -70,6 +74,11 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
   l.dw = o;  o = align_up(o + Z * l.sz_dw, 1024);
   l.dkb = o; o = align_up(o + Z * l.sz_dkb, 1024);
   l.dgb = o; o = align_up(o + Z * l.sz_dgb, 1024);
+  if (d.gate == LETHE_GATE_CHANNEL) {
+    l.da = o;  o = align_up(o + Z * 8192, 1024);
+    l.dm = o;  o = align_up(o + Z * 8192, 1024);
+    l.dqp = o; o = align_up(o + Z * static_cast<size_t>(kC * kK * 4), 1024);
+  }
   l.scratch_total = o;
   return l;
 }

@@ -1,0 +1,693 @@
+// Channel-wise gate: chunk-parallel backward kernels (after the adjoint state scan).
+//
+//   bwd_cw_sb1  : dv2, dA, dw and the parts of dq, dk and of the gate gradient that are plain
+//                 products followed by per-element decays
+//   bwd_cw_wy1  : WY / triangular-inverse VJP up to dM; dv, the value part of dbeta, d(beta gamma k)
+//   bwd_cw_pair : the decay-coupled pair sums
+//                     out1[i,d] = sum_{s<=i} C[i,s] k[s,d] exp(G_i,d - G_s,d)
+//                     out2[s,d] = sum_{i>=s} C[i,s] x[i,d] exp(G_i,d - G_s,d)
+//                 with (C, x) = (scale dA, q) for Stage B and (dM, beta k) for the WY VJP, and the
+//                 final assembly of dq / dk / dbeta / dg.
+//
+// Reference: closed channel-wise Stage B gdn2_assemble.py:521-585, channel-wise K#2
+// gdn2_assemble.py:407-473 (its two decay einsums are `out1` / `out2` here), the SIMT kernel
+// gdn2_sb_einsum.py:44-76 that the reference uses for them.
+//
+// The pair sums use the 16-row block scheme of the forward (gdn_cw_fwd.cu): blocks strictly below
+// the diagonal go through tcgen05 with both decay factors <= 1 (reference row 16 I for out1, last
+// row of the source block for out2), the four diagonal blocks are summed exactly on the CUDA cores.
+#include "gdn_common.cuh"
+#include "host_util.h"
+
+namespace lg {
+
+// fp32 exchange tile [64][128] with a column swizzle so that "thread d writes column d" and
+// "thread i reads row i" are both free of bank conflicts
+__device__ __forceinline__ int exi(int row, int col) { return row * kK + (col ^ (row & 31)); }
+
+// ---------------------------------------------------------------------------------------------
+// Stage B, part 1.  Accumulators: cA [0,128) dv2; cB [128,256) [do; dv2] h^T; cC [256,320) dA;
+// cD [320,448) v_new dh^T.
+// ---------------------------------------------------------------------------------------------
+template <int V, bool DELTA>
+__global__ void __launch_bounds__(128)
+bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mdo) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* X1 = sm;                       // 32 KB: rows 0-63 k, rows 64-127 kd
+  unsigned char* QT = X1 + 32768;               // 16 KB: q
+  unsigned char* DD = QT + 16384;               // V*256: rows 0-63 do, rows 64-127 dv2
+  unsigned char* TAt = DD + V * 256;            // 16 KB
+  unsigned char* VNt = TAt + 16384;             // V*128: v_new (64 rows); over-reads run into Ht
+  unsigned char* Ht = VNt + V * 128;            // V*256
+  unsigned char* DHt = Ht + V * 256;            // V*256
+  float* Gt = reinterpret_cast<float*>(DHt + V * 256);    // 32 KB
+  float* fs = Gt + 64 * kK;
+  float* hh = fs;                // [128] exp(G_last) <dh, h> per channel
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 128);
+  float* DDE = reinterpret_cast<float*>(Ht);   // [64][128] fp32 exchange tile, after the products are done
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    }
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(DD + a * 16384, &mdo, bar_load, a * 64, h, c * kC, b);
+    bulk_g2s(VNt, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn, V * 128, bar_load);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
+    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
+  }
+  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+  __syncthreads();
+  mbar_wait_warp(bar_load, 0, ctl, 601);
+  {  // exp(G_last,d) sum_v dh[d,v] h[d,v]: thread d owns row d of both images
+    float acc = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < V / 8; ++ch) {
+      float x[8], y[8];
+      unpack8_f16(tile_ld_chunk(DHt, tid, ch, 128), x);
+      unpack8_f16(tile_ld_chunk(Ht, tid, ch, 128), y);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += x[e] * y[e];
+    }
+    hh[tid] = acc * __expf(Gt[63 * kK + tid]);
+  }
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15;
+    float x[8], y[8];
+    unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
+    tile_st_chunk(X1, r, ch, 128, pack8_f16(x));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * __expf(Gt[63 * kK + ch * 8 + e] - Gt[r * kK + ch * 8 + e]);
+    tile_st_chunk(X1, 64 + r, ch, 128, pack8_f16(y));
+    unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
+    tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(DD, r, ch, 128), x);
+    tile_st_chunk(DD, r, ch, 128, pack8_f16(x));
+  }
+  sync_for_issue();
+
+  uint32_t ph = 0;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(cA, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
+    issue_product(cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 1u);
+    issue_product(cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 64, false}, 64, V, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 602);
+  if (tid >= 64) {
+    const int r = tid - 64;
+    unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
+    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
+#pragma unroll
+    for (int jb = 0; jb < V / 32; ++jb) {
+      float d[32];
+      tmem_ld32(cA + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 pk = pack8_f16(d + 8 * i);
+        tile_st_chunk(DD, 64 + r, jb * 4 + i, 128, pk);
+        if (DELTA) *reinterpret_cast<uint4*>(dv2_g + sw128_chunk(r, jb * 4 + i, 64)) = pk;
+        else *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(d + 8 * i);
+      }
+    }
+  } else {
+    const int r = tid;
+    float d[64];
+    tmem_ld32(cC + lane_base, d);
+    tmem_ld32(cC + lane_base + 32, d + 32);
+    tmem_ld_wait();
+    unsigned char* da_g = p.scratch + p.lay.da + static_cast<size_t>(z) * 8192;
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = (s8 * 8 + i <= r) ? p.scale * d[s8 * 8 + i] : 0.f;
+      *reinterpret_cast<uint4*>(da_g + sw128_chunk(r, s8, 64)) = pack8_f16(y);
+    }
+  }
+  sync_for_issue();
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
+    issue_product(cD, Tile{smem_u32(VNt), 64, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 603);
+  __syncthreads();          // every thread is past the products: Ht / DHt may be overwritten (DDE)
+  float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
+  float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
+  float* dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
+  if (tid < 64) {
+    const int r = tid;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float dqg[32], dkd[32];
+      tmem_ld32(cB + lane_base + jb * 32, dqg);
+      tmem_ld32(cD + lane_base + jb * 32, dkd);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float qv[8], kv[8];
+        unpack8_f16(tile_ld_chunk(QT, r, jb * 4 + i, 64), qv);
+        unpack8_f16(tile_ld_chunk(X1, r, jb * 4 + i, 128), kv);
+        float o1[8], o2[8], o3[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int d = jb * 32 + i * 8 + e;
+          const float g = Gt[r * kK + d];
+          const float sg = p.scale * __expf(g);
+          const float de = __expf(Gt[63 * kK + d] - g);
+          o1[e] = sg * dqg[8 * i + e];                       // part of dq
+          o2[e] = dkd[8 * i + e] * de;                       // part of dk
+          const float dde = o2[e] * kv[e];
+          DDE[exi(r, d)] = dde;
+          o3[e] = o1[e] * qv[e] - dde;                       // part of dG
+        }
+        const int c0 = jb * 32 + i * 8;
+        *reinterpret_cast<float4*>(dqp_g + r * kK + c0) = make_float4(o1[0], o1[1], o1[2], o1[3]);
+        *reinterpret_cast<float4*>(dqp_g + r * kK + c0 + 4) = make_float4(o1[4], o1[5], o1[6], o1[7]);
+        *reinterpret_cast<float4*>(dkb_g + r * kK + c0) = make_float4(o2[0], o2[1], o2[2], o2[3]);
+        *reinterpret_cast<float4*>(dkb_g + r * kK + c0 + 4) = make_float4(o2[4], o2[5], o2[6], o2[7]);
+        *reinterpret_cast<float4*>(dgb_g + r * kK + c0) = make_float4(o3[0], o3[1], o3[2], o3[3]);
+        *reinterpret_cast<float4*>(dgb_g + r * kK + c0 + 4) = make_float4(o3[4], o3[5], o3[6], o3[7]);
+      }
+    }
+  } else if (DELTA) {
+    const int r = tid - 64;
+    unsigned char* dw_g = p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float d[32];
+      tmem_ld32(cB + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) d[e] = -d[e];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(dw_g + sw128_chunk(r, jb * 4 + i, 64)) = pack8_f16(d + 8 * i);
+    }
+  }
+  __syncthreads();
+  {  // last row of the chunk: exp(G_last) <dh, h> + sum_i dde[i, d]   (thread d, column d)
+    float acc = hh[tid];
+    for (int i = 0; i < 64; ++i) acc += DDE[exi(i, tid)];
+    dgb_g[63 * kK + tid] += acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
+// WY VJP, part 1.  Accumulators: c1 [64,128) dT; c2 [128,192) X; c3 [192,256) dM;
+// c4 [256, 256+V+128) [dbv | d(beta gamma k)].
+// ---------------------------------------------------------------------------------------------
+template <int V>
+__global__ void __launch_bounds__(128)
+bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* KB = sm;                       // 32 KB: rows 0-63 k, rows 64-127 beta gamma k
+  unsigned char* VT = KB + 32768;               // v
+  unsigned char* BVt = VT + V * 128;            // beta v
+  unsigned char* TAt = BVt + V * 128;           // 16 KB
+  unsigned char* DV2t = TAt + 16384;            // dv2
+  unsigned char* DWt = DV2t + V * 128;          // 16 KB dw
+  unsigned char* DTt = DWt + 16384;             // 8 KB dT
+  unsigned char* XT = DTt + 8192;               // 8 KB X (+ 8 KB padding behind it)
+  float* Gt = reinterpret_cast<float*>(XT + 16384);
+  float* fs = Gt + 64 * kK;
+  float* betas = fs;
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 64);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  float bval = 0.f;
+  if (tid < 64) {
+    bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+    betas[tid] = bval;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  const uint32_t c1 = tmem + 64, c2 = tmem + 128, c3 = tmem + 192, c4 = tmem + 256;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u);
+    for (int a = 0; a < 2; ++a) tma_load_4d(KB + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
+    bulk_g2s(DWt, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, 16384, bar_load);
+  }
+  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+  __syncthreads();
+  mbar_wait_warp(bar_load, 0, ctl, 611);
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15;
+    float x[8], y[8];
+    unpack8_bf16(tile_ld_chunk(KB, r, ch, 128), x);
+    tile_st_chunk(KB, r, ch, 128, pack8_f16(x));
+    const float be = betas[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * be * __expf(Gt[r * kK + ch * 8 + e]);
+    tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
+    tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
+    const float be = betas[r];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] *= be;
+    tile_st_chunk(BVt, r, ch, 64, pack8_f16(x));
+  }
+  sync_for_issue();
+  uint32_t ph = 0;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(BVt), 64, false}, 64, V, 0u);
+    issue_product(c1, Tile{smem_u32(DWt), 64, false}, Tile{smem_u32(KB) + 8192, 128, false}, 64, 128, 1u);
+    issue_product(c4, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V + 128, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 612);
+  if (tid < 64) {
+    float d[64];
+    tmem_ld32(c1 + lane_base, d);
+    tmem_ld32(c1 + lane_base + 32, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(DTt, tid, s8, 64, pack8_f16(d + 8 * s8));
+  }
+  sync_for_issue();
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c2, Tile{smem_u32(DTt), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 613);
+  if (tid < 64) {
+    float d[64];
+    tmem_ld32(c2 + lane_base, d);
+    tmem_ld32(c2 + lane_base + 32, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(XT, tid, s8, 64, pack8_f16(d + 8 * s8));
+  }
+  sync_for_issue();
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(c3, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(XT), 64, true}, 64, 64, 0u, true);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 614);
+  if (tid < 64) {
+    const int r = tid;
+    {  // dM, strictly lower -> record
+      float dm[64];
+      tmem_ld32(c3 + lane_base, dm);
+      tmem_ld32(c3 + lane_base + 32, dm + 32);
+      tmem_ld_wait();
+      unsigned char* dm_g = p.scratch + p.lay.dm + static_cast<size_t>(z) * 8192;
+#pragma unroll
+      for (int s8 = 0; s8 < 8; ++s8) {
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = (s8 * 8 + i < r) ? dm[s8 * 8 + i] : 0.f;
+        *reinterpret_cast<uint4*>(dm_g + sw128_chunk(r, s8, 64)) = pack8_f16(y);
+      }
+    }
+    // dv = beta dbv; value part of dbeta
+    float rv = 0.f;
+    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
+#pragma unroll
+    for (int jb = 0; jb < V / 32; ++jb) {
+      float d[32];
+      tmem_ld32(c4 + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float vv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(VT, r, jb * 4 + i, 64), vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          rv += d[8 * i + e] * vv[e];
+          o8[e] = bval * d[8 * i + e];
+        }
+        *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+      }
+    }
+    p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv;
+    // d(beta gamma k) = T^T dw, fp32 -> record
+    float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4)) + r * kK;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float d[32];
+      tmem_ld32(c4 + V + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<float4*>(dqp_g + jb * 32 + 4 * i) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decay-coupled pair sums and final assembly.  MODE 0: Stage B (C = scale dA, x = q);
+// MODE 1: WY VJP (C = dM, x = beta k).  FINAL_G: this kernel closes the gate gradient (reverse
+// cumulative sum per channel); otherwise it leaves its contribution in the DGB record.
+// Accumulators: out1 rows 0-63 of [0,128); out2 rows 64-127 of [128,256).
+// ---------------------------------------------------------------------------------------------
+template <int MODE, bool FINAL_G>
+__global__ void __launch_bounds__(128)
+bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* KX = sm;                       // 32 KB: rows 0-63 k, rows 64-127 x
+  unsigned char* KR = KX + 32768;               // 32 KB: k exp(G_{16 I} - G_s), rows [0,16) [16,48) [48,96)
+  unsigned char* XE = KR + 32768;               // 32 KB: x exp(G_i - G_{16 J + 15}), rows [0,48) [48,80) [80,96)
+  unsigned char* CS = XE + 32768;               // 8 KB: C as loaded; doubles as the junk atom in front of MB_0
+  unsigned char* MB = CS + 8192;                // 3 x 8 KB: C restricted to column block J and rows >= 16 (J + 1)
+  unsigned char* MA = MB + 3 * 8192;            // 3 x 8 KB: C restricted to row block I and columns < 16 I
+  float* Gt = reinterpret_cast<float*>(MA + 4 * 8192);   // (one spare 8 KB tile behind MA_3 for over-reads)
+  float* fs = Gt + 64 * kK;
+  float* Cd = fs;                // [64][16] diagonal blocks of C
+  float* betas = fs + 1024;      // [64]
+  float* red = fs + 1088;        // [64] row sums for dbeta
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 1152);
+  float* EX1 = reinterpret_cast<float*>(KR);    // exchange tiles, once the products are done
+  float* EX2 = reinterpret_cast<float*>(XE);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 256);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  if (tid < 64) betas[tid] = (MODE == 1) ? p.beta[tok0 + static_cast<size_t>(tid) * p.H] : 1.f;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 32768u + 8192u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(KX + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(KX + a * 16384 + 8192, MODE == 0 ? &mq : &mk, bar_load, a * 64, h, c * kC, b);
+    }
+    bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_load);
+  }
+  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+  __syncthreads();
+  mbar_wait_warp(bar_load, 0, ctl, 621);
+  // ---- decayed operand rows
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15, d0 = ch * 8, blk = r >> 4;
+    float kx[8], xx[8], y[8], gr[8];
+    unpack8_bf16(tile_ld_chunk(KX, r, ch, 128), kx);
+    unpack8_bf16(tile_ld_chunk(KX, 64 + r, ch, 128), xx);
+    const float be = betas[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      xx[e] *= be;
+      gr[e] = Gt[r * kK + d0 + e];
+    }
+    tile_st_chunk(KX, r, ch, 128, pack8_f16(kx));
+    tile_st_chunk(KX, 64 + r, ch, 128, pack8_f16(xx));
+    for (int I = blk + 1; I < 4; ++I) {
+      const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[(I * 16) * kK + d0 + e] - gr[e]);
+      tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
+    }
+    for (int J = 0; J < blk; ++J) {
+      const int off = (J == 0) ? 0 : (J == 1 ? 48 : 80);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = xx[e] * __expf(gr[e] - Gt[(J * 16 + 15) * kK + d0 + e]);
+      tile_st_chunk(XE, off + (r - 16 * (J + 1)), ch, 128, pack8_f16(y));
+    }
+  }
+  // ---- masked copies of C and its diagonal blocks
+  for (int idx = tid; idx < 64 * 8; idx += 128) {
+    const int r = idx >> 3, s8 = idx & 7, blk = r >> 4, cb = s8 >> 1;
+    const uint4 cv = tile_ld_chunk(CS, r, s8, 64);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int I = 1; I < 4; ++I) tile_st_chunk(MA + (I - 1) * 8192, r, s8, 64, (I == blk && cb < I) ? cv : zero);
+#pragma unroll
+    for (int J = 0; J < 3; ++J) tile_st_chunk(MB + J * 8192, r, s8, 64, (cb == J && blk > J) ? cv : zero);
+    if (cb == blk) {
+      float cf[8];
+      unpack8_f16(cv, cf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) Cd[r * 16 + (s8 & 1) * 8 + e] = cf[e];
+    }
+  }
+  sync_for_issue();
+  uint32_t ph = 0;
+  if (tid == 0) {
+    tc_fence_after();
+    for (int I = 1; I < 4; ++I) {
+      const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
+      issue_product(tmem, Tile{smem_u32(MA + (I - 1) * 8192), 64, false},
+                    Tile{smem_u32(KR) + off * 128, 128, true}, 128, 16 * I, I > 1 ? 1u : 0u);
+    }
+    for (int J = 0; J < 3; ++J) {
+      const int off = (J == 0) ? 0 : (J == 1 ? 48 : 80);
+      const int r0 = 16 * (J + 1);
+      issue_product(tmem + 128, Tile{smem_u32(MB + J * 8192) - 8192 + r0 * 128, 64, true},
+                    Tile{smem_u32(XE) + off * 128, 128, true}, 128, 64 - r0, J > 0 ? 1u : 0u);
+    }
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 622);
+  __syncthreads();          // products done for every thread: KR / XE become the exchange tiles
+  // ---- diagonal blocks, exact; thread d owns channel d
+  {
+    const int d = tid;
+#pragma unroll 1
+    for (int blk = 0; blk < 4; ++blk) {
+      float g[16], kk[16], xv[16], a1[16], a2[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int r = blk * 16 + j;
+        g[j] = Gt[r * kK + d];
+        kk[j] = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(r, d, 128)));
+        xv[j] = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(64 + r, d, 128)));
+        a1[j] = 0.f;
+        a2[j] = 0.f;
+      }
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+#pragma unroll
+        for (int ss = 0; ss <= ii; ++ss) {
+          const float cv = Cd[(blk * 16 + ii) * 16 + ss];
+          const float e = cv * __expf(g[ii] - g[ss]);
+          a1[ii] += e * kk[ss];
+          a2[ss] += e * xv[ii];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        EX1[exi(blk * 16 + j, d)] = a1[j];
+        EX2[exi(blk * 16 + j, d)] = a2[j];
+      }
+    }
+  }
+  __syncthreads();
+  // ---- assembly
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
+  float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
+  float* dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
+  if (tid < 64) {
+    // out1 row i: decay from the block's reference row, plus the diagonal block
+    const int i = tid, a = (i >> 4) * 16;
+    const float be = betas[i];
+    __nv_bfloat16* dq_g = p.dq + (tok0 + static_cast<size_t>(i) * p.H) * kK;
+    float rsum = 0.f;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float acc[32];
+      tmem_ld32(tmem + lane_base + jb * 32, acc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int q8 = 0; q8 < 4; ++q8) {
+        float kv[8], xv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
+        unpack8_f16(tile_ld_chunk(KX, 64 + i, jb * 4 + q8, 128), xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int d = jb * 32 + q8 * 8 + e;
+          const float gi = Gt[i * kK + d];
+          const float o1 = acc[8 * q8 + e] * __expf(gi - Gt[a * kK + d]) + EX1[exi(i, d)];
+          const float part = dqp_g[i * kK + d];
+          if (MODE == 0) {
+            o8[e] = part + o1;                                        // dq
+            dgb_g[i * kK + d] += xv[e] * o1;       // + q~ . dq_intra (the scale already sits in C)
+          } else {
+            const float dbk = part * __expf(gi) + o1;                 // d(beta k)
+            rsum += dbk * kv[e];
+            dkb_g[i * kK + d] += dbk * be;
+            dgb_g[i * kK + d] += part * xv[e] * __expf(gi) + xv[e] * o1;   // dq_wy (b gamma k) + (b k) dbk_m
+          }
+        }
+        if (MODE == 0) *reinterpret_cast<uint4*>(dq_g + jb * 32 + q8 * 8) = pack8_bf16(o8);
+      }
+    }
+    if (MODE == 1) red[i] = rsum;
+  }
+  __syncthreads();
+  if (tid >= 64) {
+    // out2 row s: decay to the last row of its block, plus the diagonal block
+    const int s = tid - 64, el = (s >> 4) * 16 + 15;
+    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(s) * p.H) * kK;
+    constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float acc[32];
+      tmem_ld32(tmem + 128 + lane_base + jb * 32, acc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int q8 = 0; q8 < 4; ++q8) {
+        float kv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(KX, s, jb * 4 + q8, 128), kv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int d = jb * 32 + q8 * 8 + e;
+          const float o2 = acc[8 * q8 + e] * __expf(Gt[el * kK + d] - Gt[s * kK + d]) + EX2[exi(s, d)];
+          const float dk = dkb_g[s * kK + d] + o2;
+          o8[e] = dk;
+          if (!kFinalK) dkb_g[s * kK + d] = dk;
+          dgb_g[s * kK + d] -= kv[e] * o2;
+        }
+        if (kFinalK) *reinterpret_cast<uint4*>(dk_g + jb * 32 + q8 * 8) = pack8_bf16(o8);
+      }
+    }
+  } else if (MODE == 1) {
+    p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid];
+  }
+  __syncthreads();
+  if (FINAL_G) {   // dg[i, d] = sum_{j >= i} dG[j, d]; thread d walks its channel
+    float acc = 0.f;
+    for (int i = 63; i >= 0; --i) {
+      acc += dgb_g[i * kK + tid];
+      p.dg[(tok0 + static_cast<size_t>(i) * p.H) * kK + tid] = acc;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename Kern>
+static int set_smem_cw(Kern kern, int smem) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess ? kOk : kErrLaunch;
+}
+
+template <int V, bool DELTA>
+static int launch_sb1_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo,
+                        cudaStream_t st) {
+  const int smem = 32768 + 16384 + V * 256 + 16384 + V * 128 + V * 512 + 32768 + 128 * 4 +
+                   static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (set_smem_cw(bwd_cw_sb1_kernel<V, DELTA>, smem)) return kErrLaunch;
+  bwd_cw_sb1_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mdo);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+template <int V>
+static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
+  const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 + 16384 + 32768 + 64 * 4 +
+                   static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (set_smem_cw(bwd_cw_wy1_kernel<V>, smem)) return kErrLaunch;
+  bwd_cw_wy1_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+template <int MODE, bool FINAL_G>
+static int launch_pair_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, cudaStream_t st) {
+  const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1152 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (set_smem_cw(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
+  bwd_cw_pair_kernel<MODE, FINAL_G><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// mask bit 4: Stage B (two kernels), bit 8: WY VJP (two kernels, delta variants only)
+int launch_bwd_main_cw(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                       const CUtensorMap& mdo, cudaStream_t st, uint32_t mask) {
+  int e = kOk;
+  if (mask & 4u) {
+    if (p.V == 64) e = p.delta ? launch_sb1_t<64, true>(p, mq, mk, mdo, st) : launch_sb1_t<64, false>(p, mq, mk, mdo, st);
+    else e = p.delta ? launch_sb1_t<128, true>(p, mq, mk, mdo, st) : launch_sb1_t<128, false>(p, mq, mk, mdo, st);
+    if (e) return e;
+    e = p.delta ? launch_pair_t<0, false>(p, mq, mk, st) : launch_pair_t<0, true>(p, mq, mk, st);
+    if (e) return e;
+  }
+  if (!p.delta || !(mask & 8u)) return e;
+  e = p.V == 64 ? launch_wy1_t<64>(p, mk, mv, st) : launch_wy1_t<128>(p, mk, mv, st);
+  if (e) return e;
+  return launch_pair_t<1, true>(p, mq, mk, st);
+}
+
+}  // namespace lg

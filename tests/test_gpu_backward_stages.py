@@ -13,12 +13,13 @@ from .wsview import layout, records, report, unswizzle
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("gate", ["scalar", "channel"])
 @pytest.mark.parametrize("V", [64, 128])
 @pytest.mark.parametrize("delta", [True, False])
 @pytest.mark.parametrize("mild", [False, True])
-def test_backward_records(V, delta, mild):
+def test_backward_records(V, delta, mild, gate):
     B, L, H = 2, 256, 2
-    inp = make_inputs(B, L, H, 128, V, gate="scalar", delta=delta, seed=5, mild=mild)
+    inp = make_inputs(B, L, H, 128, V, gate=gate, delta=delta, seed=5, mild=mild)
     dev = {k: (None if t is None else t.cuda()) for k, t in inp.items()}
     scale = 128 ** -0.5
     gen = torch.Generator().manual_seed(9)
@@ -33,7 +34,7 @@ def test_backward_records(V, delta, mild):
     f64 = {k: (None if t is None else t.double()) for k, t in inp.items()}
     st = chunk_forward(f64["q"], f64["k"], f64["v"], f64["g"], f64["beta"], f64["h0"], scale=scale)
     gr, it = chunk_backward(st, f64["do"], dhT.double())
-    Z, _, _, sz2, off2 = layout(B, H, L, V)
+    Z, _, _, sz2, off2 = layout(B, H, L, V, gate=2 if gate == "channel" else 1)
     NT = L // 64
     shp = (B, H, NT)
     errs = {}
@@ -49,6 +50,6 @@ def test_backward_records(V, delta, mild):
         ref = getattr(gr, n)
         if ref is not None and got is not None:
             errs[n] = scale_rel(got.cpu().double(), ref)
-    report(f"bwd V={V} delta={delta} mild={mild}", errs)
+    report(f"bwd gate={gate} V={V} delta={delta} mild={mild}", errs)
     for n, e in errs.items():
         assert e < (5e-3 if n in ("dq", "dk", "dv") else 2e-3), (n, e, errs)

@@ -53,7 +53,7 @@ def compare(label, res, ref):
     return errs
 
 
-@pytest.mark.parametrize("name", ["gdn_scalar_k128"])
+@pytest.mark.parametrize("name", ["gdn_scalar_k128", "kda_k128"])
 def test_golden(name):
     z = np.load(os.path.join(GOLD, name + ".npz"))
     d = {k: torch.from_numpy(z[k]) for k in z.files if z[k].ndim}
@@ -83,6 +83,22 @@ def test_config1_scalar_gdn(mild):
     """B=2, H=8, L=2048, d_k=128, d_v=64, scalar gate, initial state (the headline configuration)."""
     _, res, ref = oracle_case(2, 2048, 8, 128, 64, "scalar", True, mild, seed=1)
     compare(f"config1 mild={mild}", res, ref)
+
+
+@pytest.mark.parametrize("mild", [False, True])
+def test_config2_channelwise_kda(mild):
+    """B=2, H=8, L=2048, d_k=128, d_v=128, channel-wise gate + beta (KDA)."""
+    _, res, ref = oracle_case(2, 2048, 8, 128, 128, "channel", True, mild, seed=2)
+    compare(f"config2 KDA mild={mild}", res, ref)
+
+
+@pytest.mark.parametrize("V", [64, 128])
+def test_gla(V):
+    """Channel-wise gate without the delta term (GLA), with initial state and final-state adjoint."""
+    _, res, ref = oracle_case(2, 512, 4, 128, V, "channel", False, True, seed=7, with_dhT=True)
+    compare(f"gla V={V}", res, ref)
+    _, res, ref = oracle_case(1, 256, 2, 128, V, "channel", False, False, seed=8)
+    compare(f"gla strong V={V}", res, ref)
 
 
 def test_config0_shape_d64():
