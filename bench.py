@@ -39,6 +39,10 @@ WORKLOADS = {
     "gdn_scalar_B2_H8_L2048_dk128_dv64": (2, 2048, 8, 128, 64, "scalar", True),
     "gdn_scalar_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "scalar", True),
     "gdn_scalar_B4_H8_L4096_dk128_dv64": (4, 4096, 8, 128, 64, "scalar", True),     # > L2: for ncu DRAM figures
+    "kda_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "channel", True),          # configuration 2
+    "gla_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "channel", False),       # configuration 3
+    "kda_B2_H32_L8192_dk128_dv128": (2, 8192, 32, 128, 128, "channel", True),        # configuration 4a, one GPU's share
+    "kda_B1_H32_L65536_dk128_dv128": (1, 65536, 32, 128, 128, "channel", True),      # configuration 4b (use --sp)
     "ssd_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "scalar", False),
     "la_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "none", False),
 }
@@ -130,11 +134,26 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 
 
 # ------------------------------------------------------------------------------------------------
-def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool) -> int:
+def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool, cw: bool = False) -> int:
     """Bytes one launch of `kernel` must move: each input tile and each record read once, each
-    result written once (Z chunks, 64 tokens each; K = 128)."""
+    result written once (Z chunks, 64 tokens each; K = 128).  With the channel-wise gate every kernel
+    also reads the chunk's 32 KB of gate values, "stageb" and "wy" are two launches each and pass
+    three fp32 64 x 128 records (dq / dk / dg parts) between them."""
     qk, vv, img = 64 * 128 * 2, 64 * V * 2, 128 * V * 2
     ta, w, p_, r, f32k = 16384, 16384, 32768, 128 * V * 2, 64 * 128 * 4
+    if cw:
+        g = f32k
+        per = {
+            "prepare": g + 2 * qk + vv + ta + vv + r + ((w + p_) if delta else 0) + 512,
+            "scan_fwd": (p_ if delta else 0) + r + img + 512,
+            "output": g + qk + ta + img + vv + vv + vv + (w if delta else 0),
+            "bwd_pre": g + qk + vv + r + ((w + ta) if delta else 0),
+            "scan_bwd": (p_ if delta else 0) + r + img + 512,
+            "stageb": (g + 2 * qk + vv + ta + vv + 2 * img + 8192 + 3 * f32k + (vv + w if delta else vv))
+                      + (g + 2 * qk + 8192 + 3 * f32k + qk + (2 * f32k if delta else qk + f32k)),
+            "wy": (g + qk + vv + ta + vv + w + 8192 + f32k + vv) + (g + qk + 8192 + 3 * f32k + qk + f32k),
+        }[kernel]
+        return per * Z
     per = {
         "prepare": 2 * qk + vv + ta + vv + r + ((w + p_) if delta else 0) + 512,
         "scan_fwd": (p_ if delta else 0) + r + img + 512,
@@ -147,6 +166,53 @@ def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool) -> int:
     return per * Z
 
 
+def sp_main(args, rank, world, dev, B, L, H, K, V, gate, delta, config):
+    """Sequence-parallel timing: rank r owns tokens [r L/N, (r+1) L/N) of every head; chunk-boundary
+    states (forward) and adjoint states (backward) travel rank to rank by NCCL point-to-point."""
+    import torch.distributed as dist
+    from lethe_b200 import ops
+    from lethe_b200.parallel import SequenceParallelGdn
+    from lethe_b200.synth import make_inputs
+
+    if world == 1:
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=dev)
+    Ll = L // world
+    inp = make_inputs(B, Ll, H, K, V, gate=gate, delta=delta, seed=1 + rank, with_h0=(rank == 0))
+    d = {k: t.to(dev) for k, t in inp.items() if t is not None}
+    gate_code = {"none": 0, "scalar": 1, "channel": 2}[gate]
+    sp = SequenceParallelGdn(B, Ll, H, K, V, gate_code, delta, dev)
+    scale = K ** -0.5
+
+    def step():
+        sp.forward(d["q"], d["k"], d["v"], d.get("g"), d.get("beta"), d.get("h0"), scale)
+        sp.backward(d["do"], None)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ops.check_status(sp.buf.status)
+    if rank == 0:
+        config = dict(config, mode="sequence parallel", L_per_gpu=Ll, l2="inputs and records exceed L2")
+        print(json.dumps({"metric": METRIC, "value": B * L / (float(ms) * 1e-3), "unit": "tokens/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                          "ms_per_step": float(ms), "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate (bf16 in/out)",
+                          "data": "synthetic", "config": config,
+                          "gpu_launches": args.steps * (9 if gate == "channel" and delta else 7)}))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -155,6 +221,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sp", action="store_true",
+                    help="sequence parallel: the workload's L is split over the ranks (strong scaling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -189,6 +257,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.sp:
+        sp_main(args, rank, world, dev, B, L, H, K, V, gate, delta, config)
+        return
     inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=1 + rank)
     host = {k: t.pin_memory() for k, t in inp.items() if t is not None}
     d = {k: t.to(dev) for k, t in host.items()}
@@ -277,7 +348,7 @@ def main():
         hbm, tf, which = peaks()
         Z, BH = B * H * (L // 64), B * H
         top = max(kern, key=kern.get)
-        ab = algorithmic_bytes(top, Z, BH, V, delta)
+        ab = algorithmic_bytes(top, Z, BH, V, delta, gate == "channel")
         achieved = ab / (kern[top] * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
@@ -287,7 +358,7 @@ def main():
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "kernel_ms": kern,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (7 if delta else 6),
+            "gpu_launches": args.steps * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
             "clocks": clocks,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "peak_source": which, "traffic": None,

@@ -78,6 +78,10 @@ typedef struct LetheGdnArgs {
   /* (forward: 1 prepare, 2 state scan, 4 output; backward: 1 scan input, 2 adjoint scan,           */
   /* 4 Stage B, 8 WY VJP); a partial call relies on the records left by an earlier full call.       */
   uint32_t kernel_mask;
+  /* Optional split of the beta gradient (delta = 1).  NULL: `dbeta` receives the whole gradient.     */
+  /* Non-NULL: `dbeta` receives the erase-gate part and `dbeta_write` the write-gate part, the two    */
+  /* gradients the reference returns separately (db_erase / dw_write, gdn2_assemble.py:150-181).      */
+  float* dbeta_write;
 } LetheGdnArgs;
 
 /* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */

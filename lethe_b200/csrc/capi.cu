@@ -71,13 +71,32 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   p->dq = static_cast<__nv_bfloat16*>(a->dq);
   p->dk = static_cast<__nv_bfloat16*>(a->dk);
   p->dv = static_cast<__nv_bfloat16*>(a->dv);
-  p->hT = a->hT; p->dg = a->dg; p->dbeta = a->dbeta; p->dh0 = a->dh0;
+  p->hT = a->hT; p->dg = a->dg; p->dbeta = a->dbeta; p->dh0 = a->dh0; p->dbeta_w = a->dbeta_write;
   p->saved = static_cast<unsigned char*>(a->saved);
   p->scratch = static_cast<unsigned char*>(a->scratch);
   p->lay = lay;
   p->status = a->status;
   return kOk;
 }
+
+// Makes the device that owns `ptr` current on the calling thread for the duration of a call and
+// binds its primary context.  A host framework may call from a worker thread that has never touched
+// CUDA (PyTorch's autograd thread when nothing else ran on it yet): without this the driver-level
+// tensor-map encoding fails with "invalid context".
+struct DeviceGuard {
+  int prev = -1, dev = -1;
+  bool ok = false;
+  explicit DeviceGuard(const void* ptr) {
+    cudaPointerAttributes at;
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    dev = prev;
+    if (ptr && cudaPointerGetAttributes(&at, ptr) == cudaSuccess && at.type == cudaMemoryTypeDevice) dev = at.device;
+    ok = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (ok && prev >= 0 && prev != dev) cudaSetDevice(prev);
+  }
+};
 
 }  // namespace lg
 
@@ -97,6 +116,8 @@ extern "C" int lethe_gdn_forward(const LetheGdnArgs* a, void* stream) {
   memset(&p, 0, sizeof(p));
   int e = fill_problem(a, &p, false);
   if (e) return e;
+  DeviceGuard guard(a->q);
+  if (!guard.ok) return kErrDriver;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap mq, mk, mv;
   if ((e = token_map(&mq, a->q, a->dims, kK))) return e;
@@ -115,6 +136,8 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
   memset(&p, 0, sizeof(p));
   int e = fill_problem(a, &p, true);
   if (e) return e;
+  DeviceGuard guard(a->q);
+  if (!guard.ok) return kErrDriver;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap mq, mk, mv, mdo;
   if ((e = token_map(&mq, a->q, a->dims, kK))) return e;

@@ -628,7 +628,12 @@ bwd_wy_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __g
         *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(o8);
       }
     }
-    p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
+    if (p.dbeta_w) {
+      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = gam * pk + dbeta_m;
+    } else {
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
+    }
     const float dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[r];
     dGs[r] = dgb + rowsum_e - colsum_e + bval * pk * gam;
   }

@@ -90,7 +90,7 @@ struct Problem {
   const __nv_bfloat16 *q, *k, *v, *d_o;
   const float *g, *beta, *h0, *dhT;
   __nv_bfloat16 *o, *dq, *dk, *dv;
-  float *hT, *dg, *dbeta, *dh0;
+  float *hT, *dg, *dbeta, *dh0, *dbeta_w;
   unsigned char* saved;
   unsigned char* scratch;
   Layout lay;

@@ -386,7 +386,12 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
         *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
       }
     }
-    p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv;
+    if (p.dbeta_w) {
+      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = 0.f;
+    } else {
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv;
+    }
     // d(beta gamma k) = T^T dw, fp32 -> record
     float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4)) + r * kK;
 #pragma unroll 1

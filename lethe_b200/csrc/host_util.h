@@ -3,6 +3,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 namespace lg {
 
@@ -57,6 +59,13 @@ inline int make_tmap_16bit(CUtensorMap* map, const void* ptr, int rank, const ui
                   const_cast<void*>(ptr), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("LETHE_GDN_DEBUG")) {
+    fprintf(stderr, "lethe_gdn: cuTensorMapEncodeTiled failed (%d): ptr %p rank %d dims", static_cast<int>(r), ptr, rank);
+    for (int i = 0; i < rank; ++i) fprintf(stderr, " %llu", static_cast<unsigned long long>(dims[i]));
+    fprintf(stderr, " strides");
+    for (int i = 0; i + 1 < rank; ++i) fprintf(stderr, " %llu", static_cast<unsigned long long>(strides_bytes[i]));
+    fprintf(stderr, "\n");
+  }
   return r == CUDA_SUCCESS ? kOk : kErrDriver;
 }
 

@@ -38,6 +38,7 @@ class _Args(ctypes.Structure):
         ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p), ("kernel_mask", ctypes.c_uint32),
+        ("dbeta_write", ctypes.c_void_p),
     ]
 
 
@@ -104,6 +105,7 @@ class GdnBuffers:
             gshape = (B, L, H, K) if gate == GATE_CHANNEL else (B, L, H)
             self.dg = torch.empty(gshape, dtype=f32, device=device) if gate != GATE_NONE else None
             self.dbeta = torch.empty(B, L, H, dtype=f32, device=device) if delta else None
+            self.dbeta_write = None      # set to a [B, L, H] fp32 tensor to get the erase / write split
             self.dh0 = torch.empty(B, H, K, V, dtype=f32, device=device)
 
 
@@ -121,7 +123,7 @@ def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, 
               h0=_ptr(h0), d_o=_ptr(do), dhT=_ptr(dhT), dq=_ptr(buf.dq), dk=_ptr(buf.dk), dv=_ptr(buf.dv),
               dg=_ptr(buf.dg), dbeta=_ptr(buf.dbeta), dh0=_ptr(buf.dh0), saved=_ptr(buf.saved),
               saved_bytes=buf.saved.numel(), scratch=_ptr(buf.scratch), scratch_bytes=buf.scratch.numel(),
-              status=_ptr(buf.status), kernel_mask=kernel_mask)
+              status=_ptr(buf.status), kernel_mask=kernel_mask, dbeta_write=_ptr(buf.dbeta_write))
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
@@ -214,3 +216,89 @@ def gdn_chunk(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | 
     if use_qk_l2norm:
         q, k = _l2norm(q.float()).to(q.dtype), _l2norm(k.float()).to(k.dtype)
     return _GdnChunk.apply(q, k, v, g, beta, h0, float(scale))
+
+
+# ------------------------------------------------------------------------------------------------
+# The reference's own six-input surface
+# ------------------------------------------------------------------------------------------------
+def _channel_constant(t: Tensor) -> bool:
+    return bool(torch.equal(t, t[..., :1].expand_as(t)))
+
+
+class _Gdn2Op(torch.autograd.Function):
+    """``gdn2_op`` of the reference (``src/lethe/kernels/ops/gdn_layer.py:15-111``) on the CUDA library.
+
+    The reference op takes a per-channel log decay ``g``, erase gate ``b`` (both ``[B,L,H,d_k]``) and
+    write gate ``w`` (``[B,L,H,d_v]``).  The kernels cover the regimes its native path covers
+    (``src/lethe/kernels/cute/gdn2_backward.py:53-60,102-134`` and ``cute/gdn2_family.py``):
+    ``b`` and ``w`` both equal to one beta per token-head broadcast over the channels (gated delta
+    rule / KDA), or ``b = 0, w = 1`` (no delta term); ``g`` either constant over the channels
+    (scalar gate) or not (channel-wise gate).  Any other ``b`` / ``w`` raises.
+
+    Gradients of broadcast inputs are spread evenly over the channels, as the reference's scalar
+    assembly does (``gdn2_assemble.py:343-345``); ``grad_b`` carries the erase part and ``grad_w`` the
+    write part of the beta gradient (``gdn2_assemble.py:150-181``).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, b, w, scale, use_qk_l2norm):
+        if not q.is_cuda:
+            raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+        K, V = q.shape[-1], v.shape[-1]
+        with torch.no_grad():
+            if _channel_constant(b) and _channel_constant(w) and bool(torch.equal(b[..., 0], w[..., 0])):
+                beta = b[..., 0].float().contiguous()
+            elif not bool(b.any()) and bool((w == 1).all()):
+                beta = None
+            else:
+                raise GdnError("lethe_gdn: per-channel erase / write gates are not supported: b and w must be "
+                               "one beta per token-head broadcast over the channels, or b = 0 and w = 1")
+            scalar_gate = _channel_constant(g)
+            g_in = (g[..., 0] if scalar_gate else g).float().contiguous()
+        ctx.meta = (q.dtype, k.dtype, v.dtype, g.dtype, b.dtype, w.dtype, K, V, scalar_gate, beta is not None,
+                    use_qk_l2norm)
+        qf, kf = q.float(), k.float()
+        if use_qk_l2norm:
+            qn, kn = _l2norm(qf), _l2norm(kf)
+        else:
+            qn, kn = qf, kf
+        q16, k16, v16 = _prep16(qn), _prep16(kn), _prep16(v)
+        o, _hT, saved, status = gdn_forward_raw(q16, k16, v16, g_in, beta, None, scale)
+        ctx.save_for_backward(q, k, q16, k16, v16, g_in, beta, saved, status)
+        ctx.scale = scale
+        return o.to(v.dtype)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, q16, k16, v16, g_in, beta, saved, status = ctx.saved_tensors
+        dq_t, dk_t, dv_t, dg_t, db_t, dw_t, K, V, scalar_gate, delta, l2 = ctx.meta
+        B, L, H, _ = q16.shape
+        buf = GdnBuffers(B, L, H, K, V, _gate_code(g_in), delta, q16.device, saved=saved, status=status)
+        if delta:
+            buf.dbeta_write = torch.empty(B, L, H, dtype=torch.float32, device=q16.device)
+        backward_into(buf, q16, k16, v16, g_in, beta, None, _prep16(do), None, ctx.scale)
+        dq, dk = buf.dq.float(), buf.dk.float()
+        if l2:   # VJP of x / sqrt(|x|^2 + eps), done by autograd like the reference (gdn2_assemble.py:300-312)
+            with torch.enable_grad():
+                ql = q.detach().float().requires_grad_(True)
+                kl = k.detach().float().requires_grad_(True)
+                dq, dk = torch.autograd.grad((_l2norm(ql), _l2norm(kl)), (ql, kl), (dq, dk))
+        grad_g = (buf.dg.unsqueeze(-1).expand(B, L, H, K) / K) if scalar_gate else buf.dg
+        if delta:
+            grad_b = buf.dbeta.unsqueeze(-1).expand(B, L, H, K) / K
+            grad_w = buf.dbeta_write.unsqueeze(-1).expand(B, L, H, V) / V
+        else:
+            grad_b = torch.zeros(B, L, H, K, device=q16.device)
+            grad_w = torch.zeros(B, L, H, V, device=q16.device)
+        return (dq.to(dq_t), dk.to(dk_t), buf.dv.to(dv_t), grad_g.to(dg_t).contiguous(),
+                grad_b.to(db_t).contiguous(), grad_w.to(dw_t).contiguous(), None, None)
+
+
+def gdn2_op(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Tensor, *, scale: float | None = None,
+            use_qk_l2norm: bool = True) -> Tensor:
+    """Drop-in for the reference's ``gdn2_op`` (same argument list, same defaults, returns ``o``)."""
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    if q.shape[-1] != 128:
+        raise GdnError("lethe_gdn: gdn2_op needs d_k = 128 (use gdn_chunk for d_k = 64)")
+    return _Gdn2Op.apply(q, k, v, g, b, w, float(scale), bool(use_qk_l2norm))

@@ -1,0 +1,122 @@
+"""GPU: the reference's own call surface on the CUDA library -- the six-input ``gdn2_op`` with
+broadcast gates and L2-normalised q/k, the family wrappers, and a small training loop."""
+
+import pytest
+import torch
+
+from lethe_b200.family import gla_backward, kda_backward, la_backward, ssd_backward
+from lethe_b200.ops import GdnError, gdn2_op, gdn_chunk
+from lethe_b200.synth import make_inputs
+from oracle.gdn_oracle import scale_rel, serial_backward
+
+from .wsview import report
+
+pytestmark = pytest.mark.gpu
+
+
+def _l2(x, eps=1e-6):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+@pytest.mark.parametrize("gate", ["scalar", "channel"])
+def test_gdn2_op_six_inputs(gate):
+    """b = w = beta broadcast; g broadcast (scalar regime) or per channel; q, k normalised inside."""
+    B, L, H, K, V = 1, 128, 2, 128, 64
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(B, L, H, K, generator=gen).bfloat16()
+    k = torch.randn(B, L, H, K, generator=gen).bfloat16()
+    v = torch.randn(B, L, H, V, generator=gen).bfloat16()
+    beta = torch.randn(B, L, H, generator=gen).sigmoid()
+    gs = -0.1 * torch.rand(B, L, H, K if gate == "channel" else 1, generator=gen)
+    g = gs.expand(B, L, H, K).contiguous()
+    b = beta[..., None].expand(B, L, H, K).contiguous()
+    w = beta[..., None].expand(B, L, H, V).contiguous()
+    do = torch.randn(B, L, H, V, generator=gen).bfloat16()
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, g, b, w)]
+    o = gdn2_op(*leaves)
+    grads = torch.autograd.grad(o, leaves, do.cuda())
+    # oracle on the same inputs: normalise in fp64, token-serial recurrence, autograd
+    q64, k64 = q.double().requires_grad_(True), k.double().requires_grad_(True)
+    g64 = (gs[..., 0] if gate == "scalar" else g).double()
+    o_ref, _, gr = serial_backward(_l2(q64).detach(), _l2(k64).detach(), v.double(), g64, beta.double(), None,
+                                   do.double())
+    dq_ref, dk_ref = torch.autograd.grad((_l2(q64), _l2(k64)), (q64, k64), (gr.dq, gr.dk))
+    errs = {"o": scale_rel(o.detach().cpu(), o_ref), "dq": scale_rel(grads[0].cpu(), dq_ref),
+            "dk": scale_rel(grads[1].cpu(), dk_ref), "dv": scale_rel(grads[2].cpu(), gr.dv),
+            "dg": scale_rel(grads[3].cpu().sum(-1) if gate == "scalar" else grads[3].cpu(), gr.dg),
+            "dbeta": scale_rel(grads[4].cpu().sum(-1) + grads[5].cpu().sum(-1), gr.dbeta)}
+    report(f"gdn2_op gate={gate}", errs)
+    # q, k are rounded to bf16 after the normalisation: allow for that extra rounding
+    assert max(errs.values()) <= 8e-3, errs
+
+
+def test_gdn2_op_rejects_general_gates():
+    B, L, H, K, V = 1, 64, 1, 128, 64
+    x = torch.rand(B, L, H, K, device="cuda")
+    with pytest.raises(GdnError):
+        gdn2_op(x.bfloat16(), x.bfloat16(), torch.rand(B, L, H, V, device="cuda").bfloat16(), -x, x,
+                torch.rand(B, L, H, V, device="cuda"))
+
+
+def test_family_wrappers():
+    B, L, H, K, V = 1, 256, 2, 128, 64
+    inp = make_inputs(B, L, H, K, V, gate="channel", delta=True, seed=12, mild=True)
+    d = {n: (None if t is None else t.cuda()) for n, t in inp.items()}
+    f = {n: (None if t is None else t.double()) for n, t in inp.items()}
+    gsc = d["g"][..., 0].contiguous()
+    cases = {
+        "kda": (kda_backward(d["q"], d["k"], d["v"], d["g"], d["beta"], d["do"], use_qk_l2norm=False),
+                serial_backward(f["q"], f["k"], f["v"], f["g"], f["beta"], None, f["do"])[2]),
+        "gla": (gla_backward(d["q"], d["k"], d["v"], d["g"], d["do"], use_qk_l2norm=False),
+                serial_backward(f["q"], f["k"], f["v"], f["g"], None, None, f["do"])[2]),
+        "ssd": (ssd_backward(d["q"], d["k"], d["v"], gsc, d["do"], use_qk_l2norm=False),
+                serial_backward(f["q"], f["k"], f["v"], f["g"][..., 0], None, None, f["do"])[2]),
+        "la": (la_backward(d["q"], d["k"], d["v"], d["do"], use_qk_l2norm=False),
+               serial_backward(f["q"], f["k"], f["v"], None, None, None, f["do"])[2]),
+    }
+    for name, (got, ref) in cases.items():
+        errs = {"dq": scale_rel(got.grad_q.cpu(), ref.dq), "dk": scale_rel(got.grad_k.cpu(), ref.dk),
+                "dv": scale_rel(got.grad_v.cpu(), ref.dv)}
+        if hasattr(got, "grad_g"):
+            errs["dg"] = scale_rel(got.grad_g.cpu(), ref.dg)
+        if hasattr(got, "grad_beta"):
+            errs["dbeta"] = scale_rel(got.grad_beta.cpu(), ref.dbeta)
+        report(f"family {name}", errs)
+        assert max(errs.values()) <= 5e-3, (name, errs)
+
+
+def test_tiny_train_loop():
+    """Free q, k, v and gate logits are trained through the op to reproduce a teacher's output:
+    300 Adam steps at lr 0.01 on B=4, L=256, H=2, d_k=128, d_v=64 fp32 parameters (the shape of the
+    reference's tiny-train evidence, results/gdn2_tiny_train_native_sbe.json): no NaN and the
+    normalised loss falls by more than 20x."""
+    B, L, H, K, V = 4, 256, 2, 128, 64
+    dev = "cuda"
+
+    def params(seed):
+        gen = torch.Generator().manual_seed(seed)
+        return [torch.randn(B, L, H, K, generator=gen), torch.randn(B, L, H, K, generator=gen),
+                torch.randn(B, L, H, V, generator=gen), torch.randn(B, L, H, generator=gen),
+                torch.randn(B, L, H, generator=gen)]
+
+    def run(ps):
+        q, k, v, gl, bl = ps
+        g = -0.2 * torch.nn.functional.softplus(gl)
+        o, _ = gdn_chunk(q, k, v, g, torch.sigmoid(bl), None, use_qk_l2norm=True)
+        return o.float()
+
+    with torch.no_grad():
+        target = run([t.to(dev) for t in params(100)])
+    student = [t.to(dev).requires_grad_(True) for t in params(200)]
+    opt = torch.optim.Adam(student, lr=0.01)
+    var = float(target.var())
+    losses = []
+    for _ in range(300):
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(run(student), target) / var
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert all(l == l for l in losses), "NaN in the loss"
+    report("tiny-train", {"first": losses[0], "last": losses[-1]})
+    assert losses[-1] < losses[0] / 20, (losses[0], losses[-1])
