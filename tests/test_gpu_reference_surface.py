@@ -120,3 +120,43 @@ def test_tiny_train_loop():
     assert all(l == l for l in losses), "NaN in the loss"
     report("tiny-train", {"first": losses[0], "last": losses[-1]})
     assert losses[-1] < losses[0] / 20, (losses[0], losses[-1])
+
+
+def test_kernel_plugins_k1_k2():
+    """The K1Fn / K2Fn adapters against the oracle's intermediates (the reference's micro-gate level)."""
+    import math
+
+    from lethe_b200.plugins import k1_fn, k2_fn
+    from oracle.gdn_oracle import _chunks, chunk_backward, chunk_forward
+
+    B, L, H, K, V = 1, 256, 2, 128, 64
+    inp = make_inputs(B, L, H, K, V, gate="scalar", delta=True, seed=14, mild=True)
+    f = {n: (None if t is None else t.double()) for n, t in inp.items()}
+    st = chunk_forward(f["q"], f["k"], f["v"], f["g"], f["beta"], f["h0"])
+    dhT = 0.1 * torch.randn(B, H, K, V, dtype=torch.float64, generator=torch.Generator().manual_seed(15))
+    gr, it = chunk_backward(st, f["do"], dhT)
+    g2 = st.G[..., 0] / math.log(2.0)
+    cu = lambda t: t.float().cuda()  # noqa: E731
+    dh, dv2, dh0 = k1_fn(cu(st.qs), cu(st.k), cu(st.w), cu(g2), cu(g2[..., -1]), cu(_chunks(f["do"], 64)),
+                         cu(it["dv_local"]), cu(dhT))
+    errs = {"dh": scale_rel(dh.cpu(), it["dh"]), "dv2": scale_rel(dv2.cpu(), it["dv2"]),
+            "dh0": scale_rel(dh0.cpu(), gr.dh0)}
+    # K#2 on the oracle's dw, du; expected values from the closed form of the WY VJP
+    dk2, dv, db, dg = k2_fn(cu(st.k), cu(st.v), cu(st.beta), cu(g2), cu(st.T), cu(it["dw"]), cu(it["dv2"]))
+    bc, gam = st.beta[..., None], st.G.exp()
+    Tt = st.T.transpose(-1, -2)
+    ratio = st.ratio[..., 0]
+    KK = st.k @ st.k.transpose(-1, -2)
+    dbv, dbgk = Tt @ it["dv2"], Tt @ it["dw"]
+    dM = it["dM"]
+    dkk = dM * bc * ratio
+    dk2_ref = (dkk + dkk.transpose(-1, -2)) @ st.k + bc * gam * dbgk
+    p_, r_ = (dbgk * st.k).sum(-1), (dbv * st.v).sum(-1)
+    db_ref = r_ + gam[..., 0] * p_ + (dM * ratio * KK).sum(-1)
+    e = dkk * KK
+    dG = e.sum(-1) - e.sum(-2) + st.beta * p_ * gam[..., 0]
+    dg_ref = torch.flip(torch.cumsum(torch.flip(dG, [-1]), -1), [-1])
+    errs.update(dk2=scale_rel(dk2.cpu(), dk2_ref), dv=scale_rel(dv.cpu(), bc * dbv), db=scale_rel(db.cpu(), db_ref),
+                dg=scale_rel(dg.cpu(), dg_ref))
+    report("plugins k1/k2", errs)
+    assert max(errs.values()) <= 5e-3, errs
