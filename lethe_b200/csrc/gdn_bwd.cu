@@ -79,7 +79,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
     unpack8_bf16(tile_ld_chunk(QG, r, ch, 64), x);
     if (CW) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[r * kK + ch * 8 + i]);
+      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[gidx(r, ch * 8 + i)]);
     } else {
       const float sg = p.scale * __expf(Gs[r]);
 #pragma unroll

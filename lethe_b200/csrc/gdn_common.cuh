@@ -115,14 +115,22 @@ __device__ __forceinline__ float chunk_cumsum(float x, int tid, float* tmp) {
   return x;
 }
 
-// Channel-wise gate: cumulative log decay of the chunk, Gt[i * 128 + d]; thread d owns channel d.
-// `tok0` is the token index of the chunk's first row for this head (tokens of a head are H apart).
+// Channel-wise gate tile: cumulative log decay of the chunk, 64 rows x 128 channels of fp32 in
+// shared memory.  Element (row, col) lives at gidx(row, col): the column is XOR-ed with the low row
+// bits so that both "thread d walks column d" and "thread i walks row i" are free of bank conflicts.
+__device__ __forceinline__ int gidx(int row, int col) { return row * kK + (col ^ (row & 31)); }
+
+// Thread d owns channel d.  `tok0` is the token index of the chunk's first row for this head (tokens
+// of a head are H apart).  All 64 loads are issued before the first add so that they overlap.
 __device__ __forceinline__ void gate_tile_cw(const float* g, size_t tok0, int H, int tid, float* Gt) {
+  float x[kC];
+#pragma unroll
+  for (int i = 0; i < kC; ++i) x[i] = g[(tok0 + static_cast<size_t>(i) * H) * kK + tid];
   float acc = 0.f;
-#pragma unroll 8
+#pragma unroll
   for (int i = 0; i < kC; ++i) {
-    acc += g[(tok0 + static_cast<size_t>(i) * H) * kK + tid];
-    Gt[i * kK + tid] = acc;
+    acc += x[i];
+    Gt[gidx(i, tid)] = acc;
   }
 }
 

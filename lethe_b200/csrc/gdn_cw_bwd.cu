@@ -23,7 +23,16 @@ namespace lg {
 
 // fp32 exchange tile [64][128] with a column swizzle so that "thread d writes column d" and
 // "thread i reads row i" are both free of bank conflicts
-__device__ __forceinline__ int exi(int row, int col) { return row * kK + (col ^ (row & 31)); }
+__device__ __forceinline__ int exi(int row, int col) { return gidx(row, col); }
+
+__device__ __forceinline__ void ld8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void st8(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Stage B, part 1.  Accumulators: cA [0,128) dv2; cB [128,256) [do; dv2] h^T; cC [256,320) dA;
@@ -94,7 +103,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc += x[e] * y[e];
     }
-    hh[tid] = acc * __expf(Gt[63 * kK + tid]);
+    hh[tid] = acc * __expf(Gt[gidx(63, tid)]);
   }
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
@@ -102,7 +111,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
     tile_st_chunk(X1, r, ch, 128, pack8_f16(x));
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = x[e] * __expf(Gt[63 * kK + ch * 8 + e] - Gt[r * kK + ch * 8 + e]);
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * __expf(Gt[gidx(63, ch * 8 + e)] - Gt[gidx(r, ch * 8 + e)]);
     tile_st_chunk(X1, 64 + r, ch, 128, pack8_f16(y));
     unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
@@ -186,9 +195,9 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int d = jb * 32 + i * 8 + e;
-          const float g = Gt[r * kK + d];
+          const float g = Gt[gidx(r, d)];
           const float sg = p.scale * __expf(g);
-          const float de = __expf(Gt[63 * kK + d] - g);
+          const float de = __expf(Gt[gidx(63, d)] - g);
           o1[e] = sg * dqg[8 * i + e];                       // part of dq
           o2[e] = dkd[8 * i + e] * de;                       // part of dk
           const float dde = o2[e] * kv[e];
@@ -296,7 +305,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     tile_st_chunk(KB, r, ch, 128, pack8_f16(x));
     const float be = betas[r];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = x[e] * be * __expf(Gt[r * kK + ch * 8 + e]);
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * be * __expf(Gt[gidx(r, ch * 8 + e)]);
     tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
@@ -477,20 +486,20 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       xx[e] *= be;
-      gr[e] = Gt[r * kK + d0 + e];
+      gr[e] = Gt[gidx(r, d0 + e)];
     }
     tile_st_chunk(KX, r, ch, 128, pack8_f16(kx));
     tile_st_chunk(KX, 64 + r, ch, 128, pack8_f16(xx));
     for (int I = blk + 1; I < 4; ++I) {
       const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[(I * 16) * kK + d0 + e] - gr[e]);
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[gidx((I * 16), d0 + e)] - gr[e]);
       tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
     }
     for (int J = 0; J < blk; ++J) {
       const int off = (J == 0) ? 0 : (J == 1 ? 48 : 80);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = xx[e] * __expf(gr[e] - Gt[(J * 16 + 15) * kK + d0 + e]);
+      for (int e = 0; e < 8; ++e) y[e] = xx[e] * __expf(gr[e] - Gt[gidx((J * 16 + 15), d0 + e)]);
       tile_st_chunk(XE, off + (r - 16 * (J + 1)), ch, 128, pack8_f16(y));
     }
   }
@@ -538,7 +547,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int r = blk * 16 + j;
-        g[j] = Gt[r * kK + d];
+        g[j] = Gt[gidx(r, d)];
         kk[j] = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(r, d, 128)));
         xv[j] = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(64 + r, d, 128)));
         a1[j] = 0.f;
@@ -580,26 +589,32 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       tmem_ld_wait();
 #pragma unroll
       for (int q8 = 0; q8 < 4; ++q8) {
-        float kv[8], xv[8], o8[8];
+        const int c0 = jb * 32 + q8 * 8;
+        float kv[8], xv[8], o8[8], part[8], dg8[8], dk8[8];
         unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
         unpack8_f16(tile_ld_chunk(KX, 64 + i, jb * 4 + q8, 128), xv);
+        ld8(dqp_g + i * kK + c0, part);
+        ld8(dgb_g + i * kK + c0, dg8);
+        if (MODE == 1) ld8(dkb_g + i * kK + c0, dk8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int d = jb * 32 + q8 * 8 + e;
-          const float gi = Gt[i * kK + d];
-          const float o1 = acc[8 * q8 + e] * __expf(gi - Gt[a * kK + d]) + EX1[exi(i, d)];
-          const float part = dqp_g[i * kK + d];
+          const int d = c0 + e;
+          const float gi = Gt[gidx(i, d)];
+          const float o1 = acc[8 * q8 + e] * __expf(gi - Gt[gidx(a, d)]) + EX1[exi(i, d)];
           if (MODE == 0) {
-            o8[e] = part + o1;                                        // dq
-            dgb_g[i * kK + d] += xv[e] * o1;       // + q~ . dq_intra (the scale already sits in C)
+            o8[e] = part[e] + o1;                                     // dq
+            dg8[e] += xv[e] * o1;       // + q~ . dq_intra (the scale already sits in C)
           } else {
-            const float dbk = part * __expf(gi) + o1;                 // d(beta k)
+            const float eg = __expf(gi);
+            const float dbk = part[e] * eg + o1;                      // d(beta k)
             rsum += dbk * kv[e];
-            dkb_g[i * kK + d] += dbk * be;
-            dgb_g[i * kK + d] += part * xv[e] * __expf(gi) + xv[e] * o1;   // dq_wy (b gamma k) + (b k) dbk_m
+            dk8[e] += dbk * be;
+            dg8[e] += part[e] * xv[e] * eg + xv[e] * o1;              // dq_wy (b gamma k) + (b k) dbk_m
           }
         }
-        if (MODE == 0) *reinterpret_cast<uint4*>(dq_g + jb * 32 + q8 * 8) = pack8_bf16(o8);
+        st8(dgb_g + i * kK + c0, dg8);
+        if (MODE == 0) *reinterpret_cast<uint4*>(dq_g + c0) = pack8_bf16(o8);
+        else st8(dkb_g + i * kK + c0, dk8);
       }
     }
     if (MODE == 1) red[i] = rsum;
@@ -617,18 +632,21 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       tmem_ld_wait();
 #pragma unroll
       for (int q8 = 0; q8 < 4; ++q8) {
-        float kv[8], o8[8];
+        const int c0 = jb * 32 + q8 * 8;
+        float kv[8], dk8[8], dg8[8];
         unpack8_f16(tile_ld_chunk(KX, s, jb * 4 + q8, 128), kv);
+        ld8(dkb_g + s * kK + c0, dk8);
+        ld8(dgb_g + s * kK + c0, dg8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int d = jb * 32 + q8 * 8 + e;
-          const float o2 = acc[8 * q8 + e] * __expf(Gt[el * kK + d] - Gt[s * kK + d]) + EX2[exi(s, d)];
-          const float dk = dkb_g[s * kK + d] + o2;
-          o8[e] = dk;
-          if (!kFinalK) dkb_g[s * kK + d] = dk;
-          dgb_g[s * kK + d] -= kv[e] * o2;
+          const int d = c0 + e;
+          const float o2 = acc[8 * q8 + e] * __expf(Gt[gidx(el, d)] - Gt[gidx(s, d)]) + EX2[exi(s, d)];
+          dk8[e] += o2;
+          dg8[e] -= kv[e] * o2;
         }
-        if (kFinalK) *reinterpret_cast<uint4*>(dk_g + jb * 32 + q8 * 8) = pack8_bf16(o8);
+        st8(dgb_g + s * kK + c0, dg8);
+        if (kFinalK) *reinterpret_cast<uint4*>(dk_g + c0) = pack8_bf16(dk8);
+        else st8(dkb_g + s * kK + c0, dk8);
       }
     }
   } else if (MODE == 1) {

@@ -72,7 +72,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
   gate_tile_cw(p.g, tok0, p.H, tid, Gt);
-  reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[63 * kK + tid]);
+  reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
   __syncthreads();
 
   // ---- operand tiles
@@ -87,9 +87,9 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tile_st_chunk(KQ, 64 + r, ch, 128, pack8_f16(qx));
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      gr[e] = Gt[r * kK + d0 + e];
-      ga[e] = Gt[(blk * 16) * kK + d0 + e];
-      gl[e] = Gt[63 * kK + d0 + e];
+      gr[e] = Gt[gidx(r, d0 + e)];
+      ga[e] = Gt[gidx((blk * 16), d0 + e)];
+      gl[e] = Gt[gidx(63, d0 + e)];
     }
     float ea[8];
 #pragma unroll
@@ -112,7 +112,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     for (int I = blk + 1; I < 4; ++I) {     // row r is a source row for every later row block I
       const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[(I * 16) * kK + d0 + e] - gr[e]);
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[gidx((I * 16), d0 + e)] - gr[e]);
       tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
     }
   }
@@ -154,7 +154,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       unpack8_f16(tile_ld_chunk(KQ, s, ch, 128), ks);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float ex = __expf(Gt[i * kK + ch * 8 + e] - Gt[s * kK + ch * 8 + e]);
+        const float ex = __expf(Gt[gidx(i, ch * 8 + e)] - Gt[gidx(s, ch * 8 + e)]);
         const float kse = ks[e] * ex;
         acc_a += qi[e] * kse;
         acc_m += ki[e] * kse;

@@ -348,7 +348,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
     unpack8_bf16(tile_ld_chunk(WQ, 64 + r, ch, 128), x);
     if (CW) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[r * kK + ch * 8 + i]);
+      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[gidx(r, ch * 8 + i)]);
     } else {
       const float sg = p.scale * __expf(Gs[r]);
 #pragma unroll
