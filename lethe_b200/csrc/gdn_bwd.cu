@@ -689,6 +689,8 @@ int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& m
   return p.delta ? launch_pre_t<128, true, false>(p, mq, mdo, st) : launch_pre_t<128, false, false>(p, mq, mdo, st);
 }
 
+int launch_bwd_wy(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st);
+
 // mask bit 4: Stage B, bit 8: WY VJP (delta variants only)
 int launch_bwd_main(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     const CUtensorMap& mdo, cudaStream_t st, uint32_t mask) {
@@ -698,7 +700,7 @@ int launch_bwd_main(const Problem& p, const CUtensorMap& mq, const CUtensorMap& 
     else e = p.delta ? launch_stageb_t<128, true>(p, mq, mk, mdo, st) : launch_stageb_t<128, false>(p, mq, mk, mdo, st);
   }
   if (e || !p.delta || !(mask & 8u)) return e;
-  return p.V == 64 ? launch_wy_t<64>(p, mk, mv, st) : launch_wy_t<128>(p, mk, mv, st);
+  return launch_bwd_wy(p, mk, mv, st);
 }
 
 }  // namespace lg

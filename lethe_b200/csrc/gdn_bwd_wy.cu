@@ -1,0 +1,285 @@
+// WY / triangular-inverse VJP for the scalar gate (reference K#2: gdn2_assemble.py:102-147), laid out
+// so that two CTAs fit on one SM at d_v = 64 (256 TMEM columns, < 100 KB of shared memory).
+//
+// With T = (I + strict_lower(M))^-1, du = dv2, dw from Stage B:
+//   dT  = du (beta v)^T + dw (beta gamma k)^T = [du v^T + dw (gamma k)^T] . beta_s      (column scale)
+//   dM  = strict_lower(-T^T dT T^T),  dkk = dM . beta_i . ratio
+//   dk  = (dkk + dkk^T) k + beta gamma . (T^T dw) + Stage-B part
+//       = sym k + T'^T dw + DKB,     T'[l,i] = T[l,i] beta_i gamma_i     (one accumulator)
+//   p_i = <(T^T dw)[i,:], k[i,:]> = sum_l T[l,i] (k dw^T)[i,l]           (no d x d_k read-back)
+//   dv = beta . (T^T du),  dbeta = <T^T du, v> + gamma p + sum_s dM ratio KK,
+//   dG = rowsum(e) - colsum(e) + beta p gamma,  e = dkk . KK,  dg = reverse cumsum (+ Stage-B part)
+//
+// Accumulators (TMEM columns): R0 [0,128) = [KK | k dw^T] (rows 0-63), later the dk accumulator;
+// R1 [128,192) = dT, then X = dT T^T, then dM; R2 [192, 192+V) = T^T du.
+#include "gdn_common.cuh"
+#include "host_util.h"
+
+namespace lg {
+
+template <int V>
+__global__ void __launch_bounds__(128)
+bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = align1024(smem_raw);
+  unsigned char* T1 = sm;                       // 32 KB: rows 0-63 k, rows 64-127 dw
+  unsigned char* GK = T1 + 32768;               // 16 KB: gamma k (64 x 128); later the fp32 transpose buffer
+  unsigned char* TAt = GK + 16384;              // 16 KB: [T | A]
+  unsigned char* TP = TAt + 16384;              // 8 KB: T'   (its second atom is W8: junk rows)
+  unsigned char* W8 = TP + 8192;                // 8 KB: dT, then X, then dkk + dkk^T (over-reads run into DV2t)
+  unsigned char* DV2t = W8 + 8192;              // du (64 x V)
+  unsigned char* VT = DV2t + V * 128;           // v (64 x V) (+ 8 KB behind it for over-reads)
+  float* fs = reinterpret_cast<float*>(VT + V * 128 + 8192);
+  float* Gs = fs;          // [64]
+  float* betas = fs + 64;  // [64]
+  float* dGs = fs + 128;   // [64]
+  float* tmp = fs + 192;   // [8]
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 200);
+  float* DK = reinterpret_cast<float*>(GK);    // fp32 [64][64], column XOR swizzle
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  CtaCtl ctl{p.status, &cs->abort_flag};
+  uint64_t* bar_load = &cs->bar[0];
+  uint64_t* bar_mma = &cs->bar[1];
+  constexpr uint32_t kCols = (V == 64) ? 256u : 512u;
+  if (tid == 0) {
+    cs->abort_flag = 0;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, kCols);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  float gval = 0.f, bval = 0.f;
+  if (tid < 64) {
+    if (p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
+    bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  const uint32_t R0 = tmem, R1 = tmem + 128, R2 = tmem + 192;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(T1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
+               bar_load);
+    }
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
+  }
+  const float G = chunk_cumsum(gval, tid, tmp);
+  if (tid < 64) {
+    Gs[tid] = G;
+    betas[tid] = bval;
+  }
+  __syncthreads();
+  mbar_wait_warp(bar_load, 0, ctl, 421);
+  for (int idx = tid; idx < 64 * 16; idx += 128) {
+    const int r = idx >> 4, ch = idx & 15;
+    float x[8], y[8];
+    unpack8_bf16(tile_ld_chunk(T1, r, ch, 128), x);
+    tile_st_chunk(T1, r, ch, 128, pack8_f16(x));
+    const float ga = __expf(Gs[r]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = x[i] * ga;
+    tile_st_chunk(GK, r, ch, 64, pack8_f16(y));
+    if (ch < 8) {   // T'[l, i] = T[l, i] beta_i gamma_i  (row l = r, columns 8 ch .. 8 ch + 7)
+      float t[8];
+      unpack8_f16(tile_ld_chunk(TAt, r, ch, 128), t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t[i] *= betas[ch * 8 + i] * __expf(Gs[ch * 8 + i]);
+      tile_st_chunk(TP, r, ch, 64, pack8_f16(t));
+    }
+  }
+  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+    const int r = idx / (V / 8), ch = idx % (V / 8);
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
+    tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
+  }
+  sync_for_issue();
+
+  uint32_t ph = 0;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  // ---- group 1: [KK | k dw^T], dT / beta_s, T^T du
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(R0, Tile{smem_u32(T1), 128, false}, Tile{smem_u32(T1), 128, false}, 128, 128, 0u);
+    issue_product(R1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(VT), 64, false}, 64, V, 0u);
+    issue_product(R1, Tile{smem_u32(T1) + 8192, 128, false}, Tile{smem_u32(GK), 64, false}, 64, 128, 1u);
+    issue_product(R2, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 422);
+  float pk = 0.f;
+  if (tid < 64) {
+    float d[64];
+    tmem_ld32(R1 + lane_base, d);
+    tmem_ld32(R1 + lane_base + 32, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = d[s8 * 8 + i] * betas[s8 * 8 + i];
+      tile_st_chunk(W8, tid, s8, 64, pack8_f16(y));
+    }
+    // p_i = sum_l T[l, i] (k dw^T)[i, l]
+    tmem_ld32(R0 + 64 + lane_base, d);
+    tmem_ld32(R0 + 96 + lane_base, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int l = 0; l < 64; ++l)
+      pk += d[l] * __half2float(*reinterpret_cast<const __half*>(TAt + sw128_off(l, tid, 128)));
+  }
+  sync_for_issue();
+  // ---- group 2: X = dT T^T
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(R1, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 423);
+  if (tid < 64) {
+    float d[64];
+    tmem_ld32(R1 + lane_base, d);
+    tmem_ld32(R1 + lane_base + 32, d + 32);
+    tmem_ld_wait();
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(W8, tid, s8, 64, pack8_f16(d + 8 * s8));
+  }
+  sync_for_issue();
+  // ---- group 3: dM = -T^T X
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(R1, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(W8), 64, true}, 64, 64, 0u, true);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 424);
+  float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f;
+  float kk[64];
+  if (tid < 64) {
+    const int r = tid;
+    float dm[64];
+    tmem_ld32(R1 + lane_base, dm);
+    tmem_ld32(R1 + lane_base + 32, dm + 32);
+    tmem_ld32(R0 + lane_base, kk);
+    tmem_ld32(R0 + lane_base + 32, kk + 32);
+    tmem_ld_wait();
+    const float Gr = Gs[r];
+#pragma unroll
+    for (int s = 0; s < 64; ++s) {
+      const float x = (s < r) ? dm[s] * __expf(Gr - Gs[s]) : 0.f;      // dM * ratio, strictly lower
+      dbeta_m += x * kk[s];
+      const float dkk = x * bval;
+      rowsum_e += dkk * kk[s];
+      DK[r * 64 + (s ^ (r & 31))] = dkk;
+    }
+  }
+  __syncthreads();
+  if (tid < 64) {
+    const int r = tid;
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int s = s8 * 8 + i;
+        const float up = DK[s * 64 + (r ^ (s & 31))];          // dkk[s, r], non-zero for s > r
+        y[i] = DK[r * 64 + (s ^ (r & 31))] + up;
+        colsum_e += up * kk[s];                                // KK is symmetric
+      }
+      tile_st_chunk(W8, r, s8, 64, pack8_f16(y));
+    }
+  }
+  sync_for_issue();
+  // ---- group 4: dk accumulator = (dkk + dkk^T) k + T'^T dw
+  if (tid == 0) {
+    tc_fence_after();
+    issue_product(R0, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(T1), 128, true}, 128, 64, 0u);
+    issue_product(R0, Tile{smem_u32(TP), 64, true}, Tile{smem_u32(T1) + 8192, 128, true}, 128, 64, 1u);
+    umma_commit(bar_mma);
+  }
+  wait_products(bar_mma, ph, ctl, 425);
+  if (tid < 64) {
+    const int r = tid;
+    const float gam = __expf(Gs[r]);
+    float rv = 0.f;
+    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
+#pragma unroll
+    for (int jb = 0; jb < V / 32; ++jb) {
+      float d[32];
+      tmem_ld32(R2 + lane_base + jb * 32, d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float vv[8], o8[8];
+        unpack8_f16(tile_ld_chunk(VT, r, jb * 4 + i, 64), vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          rv += d[8 * i + e] * vv[e];
+          o8[e] = bval * d[8 * i + e];
+        }
+        *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+      }
+    }
+    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(r) * p.H) * kK;
+    const float* dkb_g = reinterpret_cast<const float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb) + r * kK;
+#pragma unroll 1
+    for (int jb = 0; jb < 4; ++jb) {
+      float sk[32];
+      tmem_ld32(R0 + lane_base + jb * 32, sk);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 b0 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i);
+        const float4 b1 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i + 4);
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float o8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o8[e] = bb[e] + sk[8 * i + e];
+        *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+      }
+    }
+    if (p.dbeta_w) {
+      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = gam * pk + dbeta_m;
+    } else {
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
+    }
+    const float dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[r];
+    dGs[r] = dgb + rowsum_e - colsum_e + bval * pk * gam;
+  }
+  __syncthreads();
+  if (tid < 64 && p.gate == LETHE_GATE_SCALAR) {
+    float acc = 0.f;
+    for (int j = 63; j >= tid; --j) acc += dGs[j];
+    p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kCols);
+}
+
+template <int V>
+static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
+  const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 200 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  if (cudaFuncSetAttribute(bwd_wy2_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return kErrLaunch;
+  bwd_wy2_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+int launch_bwd_wy(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
+  return p.V == 64 ? launch_wy2_t<64>(p, mk, mv, st) : launch_wy2_t<128>(p, mk, mv, st);
+}
+
+}  // namespace lg
