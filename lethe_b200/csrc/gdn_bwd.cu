@@ -3,7 +3,7 @@
 //
 //   bwd_pre    : Rb = (scale gamma q)^T do - w^T (A^T do)          input of the adjoint state scan
 //   bwd_stageb : dv2, dq, the Stage-B part of dk and of the gate gradient, dw
-//   bwd_wy     : the WY / triangular-inverse VJP: dv, dbeta, the rest of dk, and dg
+//   (the WY / triangular-inverse VJP, which closes dv, dbeta, dk and dg, lives in gdn_bwd_wy.cu)
 //
 // Reference (file:line in the reference project): reverse scan K#1 gdn2_assemble.py:71-99, closed
 // Stage B gdn2_assemble.py:521-585 (scalar-gate form: gate broadcast over channels, dg summed),
@@ -402,253 +402,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
 }
 
 // ---------------------------------------------------------------------------------------------
-// WY / triangular-inverse VJP (delta variants only).  Accumulator regions: c0 [0,64) KK;
-// c1 [64,128) dT; c2 [128,192) X = dT T^T, later [128,256) sym k; c3 [192,256) dM;
-// c4 [256, 256+V+128) [dbv | dbgk].
-// ---------------------------------------------------------------------------------------------
-template <int V>
-__global__ void __launch_bounds__(128)
-bwd_wy_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024(smem_raw);
-  unsigned char* KB = sm;                       // 32 KB: rows 0-63 k, rows 64-127 beta gamma k
-  unsigned char* VT = KB + 32768;               // v (64 x V)
-  unsigned char* BVt = VT + V * 128;            // beta v
-  unsigned char* TAt = BVt + V * 128;           // 16 KB [T | A]
-  unsigned char* DV2t = TAt + 16384;            // dv2 (64 x V)
-  unsigned char* DWt = DV2t + V * 128;          // 16 KB dw (64 x 128), directly behind dv2
-  unsigned char* DTt = DWt + 16384;             // 8 KB dT (64 x 64)
-  unsigned char* XT = DTt + 8192;               // 8 KB X
-  unsigned char* SY = XT + 8192;                // 8 KB dkk + dkk^T, followed by 8 KB of padding
-  float* DK = reinterpret_cast<float*>(SY + 16384);   // fp32 [64][65]
-  float* fs = DK + 64 * 65;
-  float* Gs = fs;
-  float* dGs = fs + 64;
-  float* tmp = fs + 128;
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 136);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
-  CtaCtl ctl{p.status, &cs->abort_flag};
-  uint64_t* bar_load = &cs->bar[0];
-  uint64_t* bar_mma = &cs->bar[1];
-  if (tid == 0) {
-    cs->abort_flag = 0;
-    mbar_init(bar_load, 1);
-    mbar_init(bar_mma, 1);
-    fence_mbar_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(&cs->tmem_slot, 512);
-    tmem_relinquish();
-  }
-  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
-  float gval = 0.f, bval = 0.f;
-  if (tid < 64) {
-    if (p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
-    bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = cs->tmem_slot;
-  const uint32_t c0 = tmem, c1 = tmem + 64, c2 = tmem + 128, c3 = tmem + 192, c4 = tmem + 256;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u);
-    for (int a = 0; a < 2; ++a) tma_load_4d(KB + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
-    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
-    bulk_g2s(DWt, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, 16384, bar_load);
-  }
-  const float G = chunk_cumsum(gval, tid, tmp);
-  if (tid < 64) {
-    Gs[tid] = G;
-    dGs[tid] = bval;   // reused below as the beta table until the gate gradient is formed
-  }
-  __syncthreads();
-  mbar_wait_warp(bar_load, 0, ctl, 421);
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
-    const int r = idx >> 4, ch = idx & 15;
-    float x[8], y[8];
-    unpack8_bf16(tile_ld_chunk(KB, r, ch, 128), x);
-    tile_st_chunk(KB, r, ch, 128, pack8_f16(x));
-    const float bg = dGs[r] * __expf(Gs[r]);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) y[i] = x[i] * bg;
-    tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
-  }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
-    const int r = idx / (V / 8), ch = idx % (V / 8);
-    float x[8];
-    unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
-    tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
-    const float be = dGs[r];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] *= be;
-    tile_st_chunk(BVt, r, ch, 64, pack8_f16(x));
-  }
-  sync_for_issue();
-
-  uint32_t ph = 0;
-  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  // ---- group 1: KK, dT = dv2 (beta v)^T + dw (beta gamma k)^T, [dbv | dbgk] = T^T [dv2 | dw]
-  if (tid == 0) {
-    tc_fence_after();
-    issue_product(c0, Tile{smem_u32(KB), 128, false}, Tile{smem_u32(KB), 128, false}, 64, 128, 0u);
-    issue_product(c1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(BVt), 64, false}, 64, V, 0u);
-    issue_product(c1, Tile{smem_u32(DWt), 64, false}, Tile{smem_u32(KB) + 8192, 128, false}, 64, 128, 1u);
-    issue_product(c4, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V + 128, 64, 0u);
-    umma_commit(bar_mma);
-  }
-  wait_products(bar_mma, ph, ctl, 422);
-  if (tid < 64) {
-    float d[64];
-    tmem_ld32(c1 + lane_base, d);
-    tmem_ld32(c1 + lane_base + 32, d + 32);
-    tmem_ld_wait();
-#pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(DTt, tid, s8, 64, pack8_f16(d + 8 * s8));
-  }
-  sync_for_issue();
-  // ---- group 2: X = dT T^T
-  if (tid == 0) {
-    tc_fence_after();
-    issue_product(c2, Tile{smem_u32(DTt), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
-    umma_commit(bar_mma);
-  }
-  wait_products(bar_mma, ph, ctl, 423);
-  if (tid < 64) {
-    float d[64];
-    tmem_ld32(c2 + lane_base, d);
-    tmem_ld32(c2 + lane_base + 32, d + 32);
-    tmem_ld_wait();
-#pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(XT, tid, s8, 64, pack8_f16(d + 8 * s8));
-  }
-  sync_for_issue();
-  // ---- group 3: dM = -T^T X
-  if (tid == 0) {
-    tc_fence_after();
-    issue_product(c3, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(XT), 64, true}, 64, 64, 0u, true);
-    umma_commit(bar_mma);
-  }
-  wait_products(bar_mma, ph, ctl, 424);
-  float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f;
-  float kk[64];
-  if (tid < 64) {
-    const int r = tid;
-    float dm[64];
-    tmem_ld32(c3 + lane_base, dm);
-    tmem_ld32(c3 + lane_base + 32, dm + 32);
-    tmem_ld32(c0 + lane_base, kk);
-    tmem_ld32(c0 + lane_base + 32, kk + 32);
-    tmem_ld_wait();
-    const float Gr = Gs[r];
-#pragma unroll
-    for (int s = 0; s < 64; ++s) {
-      const float ra = (s < r) ? __expf(Gr - Gs[s]) : 0.f;
-      const float x = (s < r) ? dm[s] * ra : 0.f;      // dM * ratio, strict lower
-      dbeta_m += x * kk[s];
-      const float dkk = x * bval;
-      rowsum_e += dkk * kk[s];
-      DK[r * 65 + s] = dkk;
-    }
-  }
-  __syncthreads();
-  if (tid < 64) {
-    const int r = tid;
-#pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
-      float y[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int s = s8 * 8 + i;
-        const float up = DK[s * 65 + r];          // dkk[s, r], non-zero for s > r
-        y[i] = DK[r * 65 + s] + up;
-        colsum_e += up * kk[s];                   // KK is symmetric
-      }
-      tile_st_chunk(SY, r, s8, 64, pack8_f16(y));
-    }
-  }
-  sync_for_issue();
-  // ---- group 4: (dkk + dkk^T) k
-  if (tid == 0) {
-    tc_fence_after();
-    issue_product(c2, Tile{smem_u32(SY), 64, false}, Tile{smem_u32(KB), 128, true}, 128, 64, 0u);
-    umma_commit(bar_mma);
-  }
-  wait_products(bar_mma, ph, ctl, 425);
-  if (tid < 64) {
-    const int r = tid;
-    const float gam = __expf(Gs[r]);
-    const float bg = bval * gam;
-    // dv = beta * dbv,  r_i = <dbv, v>
-    float rv = 0.f;
-    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
-#pragma unroll
-    for (int jb = 0; jb < V / 32; ++jb) {
-      float d[32];
-      tmem_ld32(c4 + lane_base + jb * 32, d);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float vv[8], o8[8];
-        unpack8_f16(tile_ld_chunk(VT, r, jb * 4 + i, 64), vv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          rv += d[8 * i + e] * vv[e];
-          o8[e] = bval * d[8 * i + e];
-        }
-        *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
-      }
-    }
-    // dk = Stage-B part + sym k + beta gamma dbgk,  p_i = <dbgk, k>
-    float pk = 0.f;
-    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(r) * p.H) * kK;
-    const float* dkb_g = reinterpret_cast<const float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb) + r * kK;
-#pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
-      float dbgk[32], sk[32];
-      tmem_ld32(c4 + V + lane_base + jb * 32, dbgk);
-      tmem_ld32(c2 + lane_base + jb * 32, sk);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float kv[8], o8[8];
-        unpack8_f16(tile_ld_chunk(KB, r, jb * 4 + i, 128), kv);
-        const float4 b0 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i);
-        const float4 b1 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i + 4);
-        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          pk += dbgk[8 * i + e] * kv[e];
-          o8[e] = bb[e] + sk[8 * i + e] + bg * dbgk[8 * i + e];
-        }
-        *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(o8);
-      }
-    }
-    if (p.dbeta_w) {
-      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
-      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = gam * pk + dbeta_m;
-    } else {
-      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
-    }
-    const float dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[r];
-    dGs[r] = dgb + rowsum_e - colsum_e + bval * pk * gam;
-  }
-  __syncthreads();
-  if (tid < 64 && p.gate == LETHE_GATE_SCALAR) {
-    float acc = 0.f;
-    for (int j = 63; j >= tid; --j) acc += dGs[j];
-    p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
-// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 template <typename Kern>
@@ -671,15 +424,6 @@ static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtens
   bwd_stageb_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mdo);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
-template <int V>
-static int launch_wy_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
-  const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 * 2 + 16384 + 64 * 65 * 4 + 136 * 4 +
-                   static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (set_smem(bwd_wy_kernel<V>, smem)) return kErrLaunch;
-  bwd_wy_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
-}
-
 int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
   if (p.gate == LETHE_GATE_CHANNEL) {
     if (p.V == 64) return p.delta ? launch_pre_t<64, true, true>(p, mq, mdo, st) : launch_pre_t<64, false, true>(p, mq, mdo, st);

@@ -222,16 +222,17 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     if (DELTA) {
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        float acc = (i == tid) ? 1.f : 0.f;
+        // four partial sums: the products of one row do not wait on one another
+        float a0 = (i == tid) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
         for (int s4 = 0; s4 < (i + 3) / 4; ++s4) {
           const float4 m = *reinterpret_cast<const float4*>(&Msm[i * kMsC + 4 * s4]);
-          acc -= m.x * col[4 * s4];
-          if (4 * s4 + 1 < i) acc -= m.y * col[4 * s4 + 1];
-          if (4 * s4 + 2 < i) acc -= m.z * col[4 * s4 + 2];
-          if (4 * s4 + 3 < i) acc -= m.w * col[4 * s4 + 3];
+          a0 -= m.x * col[4 * s4];
+          if (4 * s4 + 1 < i) a1 -= m.y * col[4 * s4 + 1];
+          if (4 * s4 + 2 < i) a2 -= m.z * col[4 * s4 + 2];
+          if (4 * s4 + 3 < i) a3 -= m.w * col[4 * s4 + 3];
         }
-        col[i] = acc;
+        col[i] = (a0 + a1) + (a2 + a3);
       }
     }
 #pragma unroll

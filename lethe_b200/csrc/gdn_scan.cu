@@ -80,27 +80,23 @@ scan_kernel(const Problem p) {
     rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
   }
 
+  float a_next = ADg[(static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid];
   for (int it = 0; it < NT; ++it) {
     const int c = chunk_of(it);
     const size_t z = static_cast<size_t>(bh) * NT + c;
     const int st = it % kStages;
     const uint32_t st_par = static_cast<uint32_t>((it / kStages) & 1);
-    const float a = ADg[z * kK + tid];
-    float rr[kVs];
-    unpack8_f16(rnext[0], rr);
-    unpack8_f16(rnext[1], rr + 8);
-    if (it + 1 < NT) {
-      const __half* r = Rg + ((static_cast<size_t>(bh) * NT + chunk_of(it + 1)) * kK + tid) * V + v0;
+    const float a = a_next;
+    const uint4 r0 = rnext[0], r1 = rnext[1];
+    if (it + 1 < NT) {   // next chunk's decay and input: a whole step of latency cover
+      const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
+      const __half* r = Rg + (zn * kK + tid) * V + v0;
       rnext[0] = *reinterpret_cast<const uint4*>(r);
       rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
-    }
-    // state seen by this chunk: image record for the chunk-parallel kernels
-    {
-      unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
-      *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
-      *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
+      a_next = ADg[zn * kK + tid];
     }
     if (has_p) {
+      // critical path: the state as a tensor-core operand, then the product
 #pragma unroll
       for (int n = 0; n < kVs; ++n)
         *reinterpret_cast<__half*>(XB + sw128_off(n, tid, kVs)) = __float2half_rn(x[n]);
@@ -115,6 +111,17 @@ scan_kernel(const Problem p) {
         umma_commit(bar_mma);
       }
       __syncwarp();
+    }
+    // off the critical path (overlaps the product): the state record
+    {
+      unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
+      *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
+      *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
+    }
+    float rr[kVs];
+    unpack8_f16(r0, rr);
+    unpack8_f16(r1, rr + 8);
+    if (has_p) {
       mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
       tc_fence_after();
       float acc[kVs];
