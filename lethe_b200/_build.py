@@ -15,6 +15,7 @@ LIB = os.path.join(LIBDIR, "liblethe_gdn.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-I", os.path.join(HERE, "..", "include")]
+FLAGS += os.environ.get("LETHE_NVCC_FLAGS", "").split()      # e.g. -DLETHE_PHASE_TIMING for kernel phase stamps
 
 
 def _sources():

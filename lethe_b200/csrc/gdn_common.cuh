@@ -34,6 +34,19 @@
 #include "../../include/lethe_gdn.h"
 #include "tiles.cuh"
 
+// Development aid: with -DLETHE_PHASE_TIMING one CTA of every kernel prints clock64() stamps at its
+// phase boundaries (never enabled in a normal build).
+#ifdef LETHE_PHASE_TIMING
+#include <stdio.h>
+#define LETHE_PHASE(name)                                                                          \
+  do {                                                                                             \
+    if (blockIdx.x == 200 && blockIdx.y == 0 && threadIdx.x == 0)                                  \
+      printf("PHASE %s %s %lld\n", __func__, name, static_cast<long long>(clock64()));             \
+  } while (0)
+#else
+#define LETHE_PHASE(name)
+#endif
+
 namespace lg {
 
 constexpr int kC = 64;    // chunk length

@@ -90,9 +90,11 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
   }
+  LETHE_PHASE("start");
   gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 601);
+  LETHE_PHASE("loaded");
   {  // exp(G_last,d) sum_v dh[d,v] h[d,v]: thread d owns row d of both images
     float acc = 0.f;
 #pragma unroll
@@ -124,6 +126,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   sync_for_issue();
 
+  LETHE_PHASE("built");
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   if (tid == 0) {
@@ -134,6 +137,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     umma_commit(bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 602);
+  LETHE_PHASE("g1");
   if (tid >= 64) {
     const int r = tid - 64;
     unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
@@ -167,6 +171,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   sync_for_issue();
+  LETHE_PHASE("epi1");
   if (tid == 0) {
     tc_fence_after();
     issue_product(cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
@@ -174,6 +179,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     umma_commit(bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 603);
+  LETHE_PHASE("g2");
   __syncthreads();          // every thread is past the products: Ht / DHt may be overwritten (DDE)
   float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
   float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
@@ -229,6 +235,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   __syncthreads();
+  LETHE_PHASE("epi2");
   {  // last row of the chunk: exp(G_last) <dh, h> + sum_i dde[i, d]   (thread d, column d)
     float acc = hh[tid];
     for (int i = 0; i < 64; ++i) acc += DDE[exi(i, tid)];
@@ -395,13 +402,9 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
         *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
       }
     }
-    if (p.dbeta_w) {
-      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
-      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = 0.f;
-    } else {
-      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv;
-    }
-    // d(beta gamma k) = T^T dw, fp32 -> record
+    // d(beta gamma k) = T^T dw: fp32 -> record; its direct part of the erase-gate gradient,
+    // sum_d d(beta gamma k) gamma k, is closed here
+    float pq = 0.f;
     float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4)) + r * kK;
 #pragma unroll 1
     for (int jb = 0; jb < 4; ++jb) {
@@ -409,8 +412,21 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
       tmem_ld32(c4 + V + lane_base + jb * 32, d);
       tmem_ld_wait();
 #pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float kv[8];
+        unpack8_f16(tile_ld_chunk(KB, r, jb * 4 + i, 128), kv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pq += d[8 * i + e] * kv[e] * __expf(Gt[gidx(r, jb * 32 + i * 8 + e)]);
+      }
+#pragma unroll
       for (int i = 0; i < 8; ++i)
         *reinterpret_cast<float4*>(dqp_g + jb * 32 + 4 * i) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+    }
+    if (p.dbeta_w) {
+      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = pq;
+    } else {
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + pq;
     }
   }
   tc_fence_before();
@@ -473,9 +489,12 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
     bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_load);
   }
+  LETHE_PHASE("start");
   gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
+  LETHE_PHASE("gate");
   mbar_wait_warp(bar_load, 0, ctl, 621);
+  LETHE_PHASE("loaded");
   // ---- decayed operand rows
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8, blk = r >> 4;
@@ -503,6 +522,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       tile_st_chunk(XE, off + (r - 16 * (J + 1)), ch, 128, pack8_f16(y));
     }
   }
+  LETHE_PHASE("rows");
   // ---- masked copies of C and its diagonal blocks
   for (int idx = tid; idx < 64 * 8; idx += 128) {
     const int r = idx >> 3, s8 = idx & 7, blk = r >> 4, cb = s8 >> 1;
@@ -520,6 +540,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
   }
   sync_for_issue();
+  LETHE_PHASE("built");
   uint32_t ph = 0;
   if (tid == 0) {
     tc_fence_after();
@@ -538,6 +559,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   wait_products(bar_mma, ph, ctl, 622);
   __syncthreads();          // products done for every thread: KR / XE become the exchange tiles
+  LETHE_PHASE("products");
   // ---- diagonal blocks, exact; thread d owns channel d
   {
     const int d = tid;
@@ -571,16 +593,11 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
   }
   __syncthreads();
-  // ---- assembly
+  LETHE_PHASE("diag");
+  // ---- phase A: row owners fold the tensor-core part (with its decay) into the exchange tiles
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
-  float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
-  float* dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
   if (tid < 64) {
-    // out1 row i: decay from the block's reference row, plus the diagonal block
-    const int i = tid, a = (i >> 4) * 16;
-    const float be = betas[i];
-    __nv_bfloat16* dq_g = p.dq + (tok0 + static_cast<size_t>(i) * p.H) * kK;
+    const int i = tid, a = (i >> 4) * 16;      // out1 row i: decay from the block's reference row
     float rsum = 0.f;
 #pragma unroll 1
     for (int jb = 0; jb < 4; ++jb) {
@@ -589,77 +606,85 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       tmem_ld_wait();
 #pragma unroll
       for (int q8 = 0; q8 < 4; ++q8) {
-        const int c0 = jb * 32 + q8 * 8;
-        float kv[8], xv[8], o8[8], part[8], dg8[8], dk8[8];
-        unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
-        unpack8_f16(tile_ld_chunk(KX, 64 + i, jb * 4 + q8, 128), xv);
-        ld8(dqp_g + i * kK + c0, part);
-        ld8(dgb_g + i * kK + c0, dg8);
-        if (MODE == 1) ld8(dkb_g + i * kK + c0, dk8);
+        float kv[8];
+        if (MODE == 1) unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int d = c0 + e;
-          const float gi = Gt[gidx(i, d)];
-          const float o1 = acc[8 * q8 + e] * __expf(gi - Gt[gidx(a, d)]) + EX1[exi(i, d)];
-          if (MODE == 0) {
-            o8[e] = part[e] + o1;                                     // dq
-            dg8[e] += xv[e] * o1;       // + q~ . dq_intra (the scale already sits in C)
-          } else {
-            const float eg = __expf(gi);
-            const float dbk = part[e] * eg + o1;                      // d(beta k)
-            rsum += dbk * kv[e];
-            dk8[e] += dbk * be;
-            dg8[e] += part[e] * xv[e] * eg + xv[e] * o1;              // dq_wy (b gamma k) + (b k) dbk_m
-          }
+          const int d = jb * 32 + q8 * 8 + e;
+          const float o1 = acc[8 * q8 + e] * __expf(Gt[gidx(i, d)] - Gt[gidx(a, d)]) + EX1[exi(i, d)];
+          EX1[exi(i, d)] = o1;
+          if (MODE == 1) rsum += o1 * kv[e];
         }
-        st8(dgb_g + i * kK + c0, dg8);
-        if (MODE == 0) *reinterpret_cast<uint4*>(dq_g + c0) = pack8_bf16(o8);
-        else st8(dkb_g + i * kK + c0, dk8);
       }
     }
-    if (MODE == 1) red[i] = rsum;
-  }
-  __syncthreads();
-  if (tid >= 64) {
-    // out2 row s: decay to the last row of its block, plus the diagonal block
-    const int s = tid - 64, el = (s >> 4) * 16 + 15;
-    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(s) * p.H) * kK;
-    constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
+    if (MODE == 1) p.dbeta[tok0 + static_cast<size_t>(i) * p.H] += rsum;   // sum_d d(bk)_m k
+  } else {
+    const int s = tid - 64, el = (s >> 4) * 16 + 15;   // out2 row s: decay to the last row of its block
 #pragma unroll 1
     for (int jb = 0; jb < 4; ++jb) {
       float acc[32];
       tmem_ld32(tmem + 128 + lane_base + jb * 32, acc);
       tmem_ld_wait();
 #pragma unroll
-      for (int q8 = 0; q8 < 4; ++q8) {
-        const int c0 = jb * 32 + q8 * 8;
-        float kv[8], dk8[8], dg8[8];
-        unpack8_f16(tile_ld_chunk(KX, s, jb * 4 + q8, 128), kv);
-        ld8(dkb_g + s * kK + c0, dk8);
-        ld8(dgb_g + s * kK + c0, dg8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int d = c0 + e;
-          const float o2 = acc[8 * q8 + e] * __expf(Gt[gidx(el, d)] - Gt[gidx(s, d)]) + EX2[exi(s, d)];
-          dk8[e] += o2;
-          dg8[e] -= kv[e] * o2;
-        }
-        st8(dgb_g + s * kK + c0, dg8);
-        if (kFinalK) *reinterpret_cast<uint4*>(dk_g + c0) = pack8_bf16(dk8);
-        else st8(dkb_g + s * kK + c0, dk8);
+      for (int e = 0; e < 32; ++e) {
+        const int d = jb * 32 + e;
+        EX2[exi(s, d)] = acc[e] * __expf(Gt[gidx(el, d)] - Gt[gidx(s, d)]) + EX2[exi(s, d)];
       }
     }
-  } else if (MODE == 1) {
-    p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid];
   }
   __syncthreads();
-  if (FINAL_G) {   // dg[i, d] = sum_{j >= i} dG[j, d]; thread d walks its channel
-    float acc = 0.f;
-    for (int i = 63; i >= 0; --i) {
-      acc += dgb_g[i * kK + tid];
-      p.dg[(tok0 + static_cast<size_t>(i) * p.H) * kK + tid] = acc;
+  LETHE_PHASE("phaseA");
+  // ---- phase B: column owners (thread d) combine with the fp32 records; every global access is
+  // coalesced and the rows are independent, so the loads of several rows are in flight at once.
+  // Rows run from the last to the first so that the reverse cumulative sum is a running sum.
+  {
+    const int d = tid;
+    const float* __restrict__ dqp_g = reinterpret_cast<const float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
+    float* __restrict__ dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
+    float* __restrict__ dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
+    constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
+    float run = 0.f;
+#pragma unroll 1
+    for (int i0 = 56; i0 >= 0; i0 -= 8) {
+      // the records of eight rows are requested before any of them is used or overwritten
+      float part8[8], dgb8[8], dkb8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        part8[j] = dqp_g[(i0 + j) * kK + d];
+        dgb8[j] = dgb_g[(i0 + j) * kK + d];
+        dkb8[j] = dkb_g[(i0 + j) * kK + d];
+      }
+#pragma unroll
+      for (int j = 7; j >= 0; --j) {
+        const int i = i0 + j;
+        const float part = part8[j], dgb = dgb8[j], dkb = dkb8[j];
+        const float o1 = EX1[exi(i, d)], o2 = EX2[exi(i, d)];
+        const float kv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(i, d, 128)));
+        const float xv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(64 + i, d, 128)));
+        const size_t tok = (tok0 + static_cast<size_t>(i) * p.H) * kK + d;
+        float dk, dG;
+        if (MODE == 0) {
+          p.dq[tok] = __float2bfloat16_rn(part + o1);
+          dk = dkb + o2;
+          dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
+        } else {
+          const float eg = __expf(Gt[gidx(i, d)]);
+          const float dbk = part * eg + o1;              // d(beta k)
+          dk = dkb + dbk * betas[i] + o2;
+          dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
+        }
+        if (kFinalK) p.dk[tok] = __float2bfloat16_rn(dk);
+        else dkb_g[i * kK + d] = dk;
+        if (FINAL_G) {
+          run += dG;
+          p.dg[tok] = run;
+        } else {
+          dgb_g[i * kK + d] = dG;
+        }
+      }
     }
   }
+  LETHE_PHASE("phaseB");
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);

@@ -71,10 +71,12 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     }
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
+  LETHE_PHASE("start");
   gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
   __syncthreads();
 
+  LETHE_PHASE("gate");
   // ---- operand tiles
   mbar_wait_warp(bar_load, 0, ctl, 501);
   for (int idx = tid; idx < 64 * 16; idx += 128) {
@@ -127,6 +129,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   sync_for_issue();
 
+  LETHE_PHASE("built");
   // ---- off-diagonal blocks on the tensor cores: columns [0,16) I=1, [16,48) I=2, [48,96) I=3
   uint32_t ph = 0;
   if (tid == 0) {
@@ -164,6 +167,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     Mdg[i * 16 + ss] = (DELTA && ss < ii) ? betas[i] * acc_m : 0.f;
   }
   __syncthreads();
+  LETHE_PHASE("diag");
   wait_products(bar_mma, ph, ctl, 502);
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   {
@@ -214,6 +218,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   tc_fence_before();
   __syncthreads();
 
+  LETHE_PHASE("epi1");
   // ---- T = (I + M)^-1 (fp32, one column per thread)
   if (tid < 64) {
     float col[64];
@@ -243,6 +248,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   sync_for_issue();
 
+  LETHE_PHASE("inverse");
   if (DELTA) {
     if (tid == 0) {
       tc_fence_after();
@@ -268,6 +274,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     bulk_commit();
   }
 
+  LETHE_PHASE("wu");
   constexpr int N3 = DELTA ? 128 + V : V;
   if (tid == 0) {
     tc_fence_after();
@@ -302,6 +309,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       }
     }
   }
+  LETHE_PHASE("pr");
   if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
