@@ -41,6 +41,7 @@ WORKLOADS = {
     "gdn_scalar_B4_H8_L4096_dk128_dv64": (4, 4096, 8, 128, 64, "scalar", True),     # > L2: for ncu DRAM figures
     "kda_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "channel", True),          # configuration 2
     "gla_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "channel", False),       # configuration 3
+    "kda_B4_H8_L4096_dk128_dv128": (4, 4096, 8, 128, 128, "channel", True),          # > L2: for ncu DRAM figures
     "kda_B2_H32_L8192_dk128_dv128": (2, 8192, 32, 128, 128, "channel", True),        # configuration 4a, one GPU's share
     "kda_B1_H32_L65536_dk128_dv128": (1, 65536, 32, 128, 128, "channel", True),      # configuration 4b (use --sp)
     "ssd_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "scalar", False),

@@ -39,7 +39,7 @@ __device__ __forceinline__ void st8(float* p, const float* v) {
 // cD [320,448) v_new dh^T.
 // ---------------------------------------------------------------------------------------------
 template <int V, bool DELTA>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                   const __grid_constant__ CUtensorMap mdo) {
   extern __shared__ unsigned char smem_raw[];
@@ -91,11 +91,11 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
   }
   LETHE_PHASE("start");
-  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+  if (tid < 128) gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 601);
   LETHE_PHASE("loaded");
-  {  // exp(G_last,d) sum_v dh[d,v] h[d,v]: thread d owns row d of both images
+  if (tid < 128) {  // exp(G_last,d) sum_v dh[d,v] h[d,v]: thread d owns row d of both images
     float acc = 0.f;
 #pragma unroll
     for (int ch = 0; ch < V / 8; ++ch) {
@@ -107,7 +107,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
     hh[tid] = acc * __expf(Gt[gidx(63, tid)]);
   }
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
     unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
@@ -118,7 +118,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(DD, r, ch, 128), x);
@@ -138,7 +138,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   wait_products(bar_mma, ph, ctl, 602);
   LETHE_PHASE("g1");
-  if (tid >= 64) {
+  if (tid >= 64 && tid < 128) {
     const int r = tid - 64;
     unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
     __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
@@ -155,7 +155,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
         else *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(d + 8 * i);
       }
     }
-  } else {
+  } else if (tid < 64) {
     const int r = tid;
     float d[64];
     tmem_ld32(cC + lane_base, d);
@@ -184,10 +184,11 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
   float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
   float* dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
-  if (tid < 64) {
-    const int r = tid;
+  const int tq = tid & 127, jb0 = 2 * (tid >> 7);   // threads 128-255 take the upper 64 columns
+  if (tq < 64) {
+    const int r = tq;
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jb = jb0; jb < jb0 + 2; ++jb) {
       float dqg[32], dkd[32];
       tmem_ld32(cB + lane_base + jb * 32, dqg);
       tmem_ld32(cD + lane_base + jb * 32, dkd);
@@ -220,10 +221,10 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
       }
     }
   } else if (DELTA) {
-    const int r = tid - 64;
+    const int r = tq - 64;
     unsigned char* dw_g = p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw;
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jb = jb0; jb < jb0 + 2; ++jb) {
       float d[32];
       tmem_ld32(cB + lane_base + jb * 32, d);
       tmem_ld_wait();
@@ -236,7 +237,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   __syncthreads();
   LETHE_PHASE("epi2");
-  {  // last row of the chunk: exp(G_last) <dh, h> + sum_i dde[i, d]   (thread d, column d)
+  if (tid < 128) {  // last row of the chunk: exp(G_last) <dh, h> + sum_i dde[i, d]   (thread d, column d)
     float acc = hh[tid];
     for (int i = 0; i < 64; ++i) acc += DDE[exi(i, tid)];
     dgb_g[63 * kK + tid] += acc;
@@ -441,7 +442,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
 // Accumulators: out1 rows 0-63 of [0,128); out2 rows 64-127 of [128,256).
 // ---------------------------------------------------------------------------------------------
 template <int MODE, bool FINAL_G>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024(smem_raw);
@@ -455,8 +456,8 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   float* fs = Gt + 64 * kK;
   float* Cd = fs;                // [64][16] diagonal blocks of C
   float* betas = fs + 1024;      // [64]
-  float* red = fs + 1088;        // [64] row sums for dbeta
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 1152);
+  float* red = fs + 1088;        // [2][64] partial row sums for dbeta
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 1216);
   float* EX1 = reinterpret_cast<float*>(KR);    // exchange tiles, once the products are done
   float* EX2 = reinterpret_cast<float*>(XE);
 
@@ -490,13 +491,13 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_load);
   }
   LETHE_PHASE("start");
-  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+  if (tid < 128) gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
   LETHE_PHASE("gate");
   mbar_wait_warp(bar_load, 0, ctl, 621);
   LETHE_PHASE("loaded");
   // ---- decayed operand rows
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8, blk = r >> 4;
     float kx[8], xx[8], y[8], gr[8];
     unpack8_bf16(tile_ld_chunk(KX, r, ch, 128), kx);
@@ -524,7 +525,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   LETHE_PHASE("rows");
   // ---- masked copies of C and its diagonal blocks
-  for (int idx = tid; idx < 64 * 8; idx += 128) {
+  for (int idx = tid; idx < 64 * 8; idx += 256) {
     const int r = idx >> 3, s8 = idx & 7, blk = r >> 4, cb = s8 >> 1;
     const uint4 cv = tile_ld_chunk(CS, r, s8, 64);
     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -562,9 +563,9 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   LETHE_PHASE("products");
   // ---- diagonal blocks, exact; thread d owns channel d
   {
-    const int d = tid;
+    const int d = tid & 127;
 #pragma unroll 1
-    for (int blk = 0; blk < 4; ++blk) {
+    for (int blk = 2 * (tid >> 7); blk < 2 * (tid >> 7) + 2; ++blk) {
       float g[16], kk[16], xv[16], a1[16], a2[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -594,59 +595,63 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   __syncthreads();
   LETHE_PHASE("diag");
-  // ---- phase A: row owners fold the tensor-core part (with its decay) into the exchange tiles
+  // ---- phase A: row owners fold the tensor-core part (with its decay) into the exchange tiles.
+  // Threads 0-127 own accumulator lanes 0-127 and take columns 0-63; threads 128-255 (warps 4-7 reach
+  // the same lanes) take columns 64-127.
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  if (tid < 64) {
-    const int i = tid, a = (i >> 4) * 16;      // out1 row i: decay from the block's reference row
-    float rsum = 0.f;
+  {
+    const int t = tid & 127, jb0 = 2 * (tid >> 7);
+    if (t < 64) {
+      const int i = t, a = (i >> 4) * 16;      // out1 row i: decay from the block's reference row
+      float rsum = 0.f;
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
-      float acc[32];
-      tmem_ld32(tmem + lane_base + jb * 32, acc);
-      tmem_ld_wait();
+      for (int jb = jb0; jb < jb0 + 2; ++jb) {
+        float acc[32];
+        tmem_ld32(tmem + lane_base + jb * 32, acc);
+        tmem_ld_wait();
 #pragma unroll
-      for (int q8 = 0; q8 < 4; ++q8) {
-        float kv[8];
-        if (MODE == 1) unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
+        for (int q8 = 0; q8 < 4; ++q8) {
+          float kv[8];
+          if (MODE == 1) unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int d = jb * 32 + q8 * 8 + e;
-          const float o1 = acc[8 * q8 + e] * __expf(Gt[gidx(i, d)] - Gt[gidx(a, d)]) + EX1[exi(i, d)];
-          EX1[exi(i, d)] = o1;
-          if (MODE == 1) rsum += o1 * kv[e];
+          for (int e = 0; e < 8; ++e) {
+            const int d = jb * 32 + q8 * 8 + e;
+            const float o1 = acc[8 * q8 + e] * __expf(Gt[gidx(i, d)] - Gt[gidx(a, d)]) + EX1[exi(i, d)];
+            EX1[exi(i, d)] = o1;
+            if (MODE == 1) rsum += o1 * kv[e];
+          }
         }
       }
-    }
-    if (MODE == 1) p.dbeta[tok0 + static_cast<size_t>(i) * p.H] += rsum;   // sum_d d(bk)_m k
-  } else {
-    const int s = tid - 64, el = (s >> 4) * 16 + 15;   // out2 row s: decay to the last row of its block
+      if (MODE == 1) red[(tid >> 7) * 64 + i] = rsum;
+    } else {
+      const int s = t - 64, el = (s >> 4) * 16 + 15;   // out2 row s: decay to the last row of its block
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
-      float acc[32];
-      tmem_ld32(tmem + 128 + lane_base + jb * 32, acc);
-      tmem_ld_wait();
+      for (int jb = jb0; jb < jb0 + 2; ++jb) {
+        float acc[32];
+        tmem_ld32(tmem + 128 + lane_base + jb * 32, acc);
+        tmem_ld_wait();
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const int d = jb * 32 + e;
-        EX2[exi(s, d)] = acc[e] * __expf(Gt[gidx(el, d)] - Gt[gidx(s, d)]) + EX2[exi(s, d)];
+        for (int e = 0; e < 32; ++e) {
+          const int d = jb * 32 + e;
+          EX2[exi(s, d)] = acc[e] * __expf(Gt[gidx(el, d)] - Gt[gidx(s, d)]) + EX2[exi(s, d)];
+        }
       }
     }
   }
   __syncthreads();
+  if (MODE == 1 && tid < 64) p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid] + red[64 + tid];   // sum_d d(bk)_m k
   LETHE_PHASE("phaseA");
-  // ---- phase B: column owners (thread d) combine with the fp32 records; every global access is
-  // coalesced and the rows are independent, so the loads of several rows are in flight at once.
-  // Rows run from the last to the first so that the reverse cumulative sum is a running sum.
+  // ---- phase B: column owners (thread d; the two halves of the CTA split the rows) combine with the
+  // fp32 records; every global access is coalesced and the records of eight rows are requested before
+  // any of them is used or overwritten.
   {
-    const int d = tid;
+    const int d = tid & 127, ibase = 32 * (tid >> 7);
     const float* __restrict__ dqp_g = reinterpret_cast<const float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
     float* __restrict__ dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
     float* __restrict__ dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
     constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
-    float run = 0.f;
 #pragma unroll 1
-    for (int i0 = 56; i0 >= 0; i0 -= 8) {
-      // the records of eight rows are requested before any of them is used or overwritten
+    for (int i0 = ibase; i0 < ibase + 32; i0 += 8) {
       float part8[8], dgb8[8], dkb8[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -655,7 +660,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
         dkb8[j] = dkb_g[(i0 + j) * kK + d];
       }
 #pragma unroll
-      for (int j = 7; j >= 0; --j) {
+      for (int j = 0; j < 8; ++j) {
         const int i = i0 + j;
         const float part = part8[j], dgb = dgb8[j], dkb = dkb8[j];
         const float o1 = EX1[exi(i, d)], o2 = EX2[exi(i, d)];
@@ -675,12 +680,19 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
         }
         if (kFinalK) p.dk[tok] = __float2bfloat16_rn(dk);
         else dkb_g[i * kK + d] = dk;
-        if (FINAL_G) {
-          run += dG;
-          p.dg[tok] = run;
-        } else {
-          dgb_g[i * kK + d] = dG;
-        }
+        if (FINAL_G) EX1[exi(i, d)] = dG;                // closed below by the reverse cumulative sum
+        else dgb_g[i * kK + d] = dG;
+      }
+    }
+  }
+  if (FINAL_G) {   // dg[i, d] = sum_{j >= i} dG[j, d]; thread d walks its channel from the last row up
+    __syncthreads();
+    if (tid < 128) {
+      float run = 0.f;
+#pragma unroll 8
+      for (int i = 63; i >= 0; --i) {
+        run += EX1[exi(i, tid)];
+        p.dg[(tok0 + static_cast<size_t>(i) * p.H) * kK + tid] = run;
       }
     }
   }
@@ -702,7 +714,7 @@ static int launch_sb1_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
   const int smem = 32768 + 16384 + V * 256 + 16384 + V * 128 + V * 512 + 32768 + 128 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem_cw(bwd_cw_sb1_kernel<V, DELTA>, smem)) return kErrLaunch;
-  bwd_cw_sb1_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mdo);
+  bwd_cw_sb1_kernel<V, DELTA><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mdo);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V>
@@ -715,9 +727,9 @@ static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
 }
 template <int MODE, bool FINAL_G>
 static int launch_pair_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, cudaStream_t st) {
-  const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1152 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1216 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem_cw(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
-  bwd_cw_pair_kernel<MODE, FINAL_G><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk);
+  bwd_cw_pair_kernel<MODE, FINAL_G><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -21,7 +21,7 @@ namespace lg {
 constexpr int kMsC = 68;
 
 template <int V, bool DELTA>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
                   const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
   extern __shared__ unsigned char smem_raw[];
@@ -72,14 +72,16 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
   LETHE_PHASE("start");
-  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
-  reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
+  if (tid < 128) {
+    gate_tile_cw(p.g, tok0, p.H, tid, Gt);
+    reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
+  }
   __syncthreads();
 
   LETHE_PHASE("gate");
   // ---- operand tiles
   mbar_wait_warp(bar_load, 0, ctl, 501);
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8;
     const int blk = r >> 4;
     float kx[8], qx[8], y[8], gr[8], ga[8], gl[8];
@@ -118,7 +120,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
     }
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(BV, r, ch, 64), x);
@@ -141,7 +143,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   __syncwarp();
   // ---- diagonal blocks, exact: pair (i, s) of one block, s <= i
-  for (int pp = tid; pp < 4 * 136; pp += 128) {
+  for (int pp = tid; pp < 4 * 136; pp += 256) {
     const int blk = pp / 136, t = pp % 136;
     int ii = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
     while ((ii + 1) * (ii + 2) / 2 <= t) ++ii;
@@ -170,7 +172,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   LETHE_PHASE("diag");
   wait_products(bar_mma, ph, ctl, 502);
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  {
+  if (tid < 128) {
     float d[96];
     tmem_ld32(tmem + lane_base, d);
     tmem_ld32(tmem + lane_base + 32, d + 32);
@@ -289,7 +291,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     bulk_commit();
   }
   wait_products(bar_mma, ph, ctl, 504);
-  {
+  if (tid < 128) {
     unsigned char* Pg = p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p;
     __half* Rg = reinterpret_cast<__half*>(p.saved + p.lay.r + static_cast<size_t>(z) * p.lay.sz_r) +
                  static_cast<size_t>(tid) * V;
@@ -322,7 +324,7 @@ static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CU
   const int smem = 32768 * 4 + 16384 + V * 128 + 16384 + 16384 + 2112 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_cw_kernel<V, DELTA>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
-  kern<<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
