@@ -315,6 +315,7 @@ def main():
     fwd_ms = timed(lambda: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale), args.steps, 3)
     bwd_ms = timed(lambda: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale),
                    args.steps, 3)
+    ops.check_status(buf.status)
 
     # ---- end to end through the public op, host buffers in, host buffers out
     outs_host = {}

@@ -387,10 +387,13 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
         }
       }
     }
-    tc_fence_before();
-    fence_proxy_async();
-    __syncthreads();
   }
+  // Every thread must be past its wait on the first product before the second one is committed: a
+  // thread still polling the barrier's first phase when the second phase completes would wait for
+  // a third completion that never comes.
+  tc_fence_before();
+  fence_proxy_async();
+  __syncthreads();
 
   if (tid == 0) {
     tc_fence_after();

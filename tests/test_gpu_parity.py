@@ -139,3 +139,22 @@ def test_single_chunk_and_ragged_rejection():
     inp = make_inputs(1, 96, 1, 128, 64, seed=1)
     with pytest.raises(Exception):
         run_op(inp, 0.1)
+
+
+def test_repeated_no_delta_forward_keeps_status_clean():
+    """The no-delta output kernel commits two product groups back to back; every thread has to be past
+    its wait on the first before the second is committed (else a bounded wait runs out).  Many
+    launches, status word checked, results bitwise stable."""
+    from lethe_b200 import ops
+
+    B, L, H, K, V = 2, 1024, 8, 128, 128
+    inp = make_inputs(B, L, H, K, V, gate="scalar", delta=False, seed=13)
+    d = {k: t.cuda() for k, t in inp.items() if t is not None}
+    buf = ops.GdnBuffers(B, L, H, K, V, ops.GATE_SCALAR, False, torch.device("cuda"), backward=False)
+    ops.forward_into(buf, d["q"], d["k"], d["v"], d["g"], None, d["h0"], K ** -0.5)
+    ref = buf.o.clone()
+    for _ in range(300):
+        ops.forward_into(buf, d["q"], d["k"], d["v"], d["g"], None, d["h0"], K ** -0.5, kernel_mask=4)
+    torch.cuda.synchronize()
+    ops.check_status(buf.status)
+    assert torch.equal(buf.o, ref)
