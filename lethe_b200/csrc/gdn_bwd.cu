@@ -60,7 +60,8 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u));
+    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u) + (CW ? 32768u : 0u));
+    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) tma_load_4d(QG + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
     for (int a = 0; a < V / 64; ++a) tma_load_4d(DO + a * 8192, &mdo, bar_load, a * 64, h, c * kC, b);
     if (DELTA) {
@@ -70,7 +71,6 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
-  if (CW) gate_tile_cw(p.g, (static_cast<size_t>(b) * p.L + c * kC) * p.H + h, p.H, tid, Gt);
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 401);
   for (int idx = tid; idx < 64 * 16; idx += 128) {

@@ -16,6 +16,9 @@
 //           the final state, so record index is (b*H + h)*(NT + 1) + c
 //     VN    64 x V  image: v_new = u - w h
 //     AD    128 fp32: exp(G_last) per key channel     (the decay of the chunk)
+//     GT    channel-wise gate only: 64 x 128 fp32, the cumulative log decay of the chunk in the
+//           swizzled shared-memory arrangement of gidx(), written once by prepare and bulk-loaded
+//           by every later kernel instead of being recomputed
 //   scratch (backward only)
 //     RB    128 x V fp16 row-major: (q gamma)^T do - w^T (A^T do)
 //     DH    128 x V image: adjoint of the state leaving the chunk
@@ -54,7 +57,7 @@ constexpr int kK = 128;   // key dimension
 
 struct Layout {
   // byte offsets of the record arrays inside `saved` / `scratch`, and record sizes
-  size_t ta, w, u, p, r, hc, vn, ad, saved_total;
+  size_t ta, w, u, p, r, hc, vn, ad, gt, saved_total;
   size_t rb, dh, dv2, dw, dkb, dgb, da, dm, dqp, scratch_total;
   size_t sz_ta, sz_w, sz_u, sz_p, sz_r, sz_hc, sz_vn, sz_ad;
   size_t sz_rb, sz_dh, sz_dv2, sz_dw, sz_dkb, sz_dgb;
@@ -77,6 +80,9 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
   l.hc = o; o = align_up(o + (Z + static_cast<size_t>(d.B) * d.H) * l.sz_hc, 1024);
   l.vn = o; o = align_up(o + Z * l.sz_vn, 1024);
   l.ad = o; o = align_up(o + Z * l.sz_ad, 1024);
+  if (d.gate == LETHE_GATE_CHANNEL) {
+    l.gt = o; o = align_up(o + Z * static_cast<size_t>(kC * kK * 4), 1024);
+  }
   l.saved_total = o;
   l.sz_rb = kK * V * 2; l.sz_dh = kK * V * 2; l.sz_dv2 = kC * V * 2; l.sz_dw = 16384;
   l.sz_dkb = kC * kK * 4; l.sz_dgb = (d.gate == LETHE_GATE_CHANNEL ? kC * kK : kC) * 4;

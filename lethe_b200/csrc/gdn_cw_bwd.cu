@@ -79,7 +79,8 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   const uint32_t tmem = cs->tmem_slot;
   const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u + 32768u);
+    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
       tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
@@ -91,7 +92,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
   }
   LETHE_PHASE("start");
-  if (tid < 128) gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 601);
   LETHE_PHASE("loaded");
@@ -296,14 +296,14 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   const uint32_t tmem = cs->tmem_slot;
   const uint32_t c1 = tmem + 64, c2 = tmem + 128, c3 = tmem + 192, c4 = tmem + 256;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u);
+    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u + 32768u);
+    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) tma_load_4d(KB + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
     for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
     bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
     bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
     bulk_g2s(DWt, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, 16384, bar_load);
   }
-  gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 611);
   for (int idx = tid; idx < 64 * 16; idx += 128) {
@@ -483,7 +483,8 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 32768u + 8192u);
+    mbar_expect_tx(bar_load, 32768u + 8192u + 32768u);
+    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(KX + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
       tma_load_4d(KX + a * 16384 + 8192, MODE == 0 ? &mq : &mk, bar_load, a * 64, h, c * kC, b);
@@ -491,7 +492,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_load);
   }
   LETHE_PHASE("start");
-  if (tid < 128) gate_tile_cw(p.g, tok0, p.H, tid, Gt);
   __syncthreads();
   LETHE_PHASE("gate");
   mbar_wait_warp(bar_load, 0, ctl, 621);

@@ -75,10 +75,15 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   if (tid < 128) {
     gate_tile_cw(p.g, tok0, p.H, tid, Gt);
     reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
+    fence_proxy_async();
   }
   __syncthreads();
 
   LETHE_PHASE("gate");
+  if (tid == 0) {   // the gate tile becomes a record: later kernels load it instead of rebuilding it
+    bulk_s2g(p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), Gt, 32768);
+    bulk_commit();
+  }
   // ---- operand tiles
   mbar_wait_warp(bar_load, 0, ctl, 501);
   for (int idx = tid; idx < 64 * 16; idx += 256) {

@@ -321,7 +321,8 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
 
   const unsigned char* Ug = p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + V * 256u + 16384u);
+    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + V * 256u + 16384u + (CW ? 32768u : 0u));
+    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(WQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
       if (DELTA)
@@ -339,7 +340,6 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
-  if (CW) gate_tile_cw(p.g, (static_cast<size_t>(b) * p.L + c * kC) * p.H + h, p.H, tid, Gt);
   __syncthreads();
 
   mbar_wait_warp(bar_load, 0, ctl, 211);
