@@ -13,14 +13,25 @@
 // gdn2_assemble.py:71-99 of the reference project, after substituting v_new / dv2.
 #include "gdn_common.cuh"
 #include "host_util.h"
+#include <stdio.h>
 
 namespace lg {
 
 constexpr int kStages = 3;
-constexpr int kVs = 16;  // columns of the state per CTA
+constexpr int kVs = 16;        // columns of the state per CTA
+constexpr int kMmaWarps = 2;   // warps that issue the step's products (each its own accumulator)
+// warps 0-3 hold the state (thread d = key channel d), warp 4 streams P, warps 5.. issue products
+constexpr int kScanThreads = (5 + kMmaWarps) * 32;
+constexpr int kStepBarrier = 128 + kMmaWarps * 32;
+constexpr int kTmemCols = kMmaWarps * 16 < 32 ? 32 : kMmaWarps * 16;
+
+// Step barrier of the delta path: the state-holding warps arrive once the operand is written (and go
+// on to work that does not depend on the product), the issuing warps wait for them.
+__device__ __forceinline__ void step_arrive() { asm volatile("bar.arrive 1, %0;" ::"n"(kStepBarrier) : "memory"); }
+__device__ __forceinline__ void step_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStepBarrier) : "memory"); }
 
 template <bool ADJOINT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const Problem p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -34,126 +45,177 @@ scan_kernel(const Problem p) {
   const int V = p.V, NT = p.NT;
   const bool has_p = p.delta != 0;
   CtaCtl ctl{p.status, &cs->abort_flag};
-  uint64_t* bar_mma = &cs->bar[kStages];
+  uint64_t* bar_full = &cs->bar[0];                 // [kStages] P stage loaded
+  uint64_t* bar_free = &cs->bar[kStages];           // [kStages] the products reading the stage are done
+  uint64_t* bar_mma = &cs->bar[2 * kStages];        // the step's products are done
 
   if (tid == 0) {
     cs->abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) mbar_init(&cs->bar[s], 1);
-    mbar_init(bar_mma, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_free[s], kMmaWarps);
+    }
+    mbar_init(bar_mma, kMmaWarps);
     fence_mbar_init();
   }
   if (warp == 0) {
-    tmem_alloc(&cs->tmem_slot, 32);
+    tmem_alloc(&cs->tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-
-  const unsigned char* Pg = p.saved + p.lay.p;
-  const __half* Rg = reinterpret_cast<const __half*>(ADJOINT ? p.scratch + p.lay.rb : p.saved + p.lay.r);
-  const float* ADg = reinterpret_cast<const float*>(p.saved + p.lay.ad);
-  unsigned char* Xg = ADJOINT ? p.scratch + p.lay.dh : p.saved + p.lay.hc;
-  const size_t szx = p.lay.sz_hc;
   auto chunk_of = [&](int it) { return ADJOINT ? NT - 1 - it : it; };
 
-  if (has_p && tid == 0) {
-    for (int s = 0; s < kStages && s < NT; ++s) {
-      mbar_expect_tx(&cs->bar[s], 32768u);
-      bulk_g2s(Pst + s * 32768, Pg + (static_cast<size_t>(bh) * NT + chunk_of(s)) * 32768, 32768u, &cs->bar[s]);
+  if (warp == 4) {
+    // ---- producer: keeps the ring of P stages full
+    if (has_p && tid == 128) {
+      const unsigned char* Pg = p.saved + p.lay.p;
+      for (int it = 0; it < NT; ++it) {
+        const int st = it % kStages;
+        if (it >= kStages) mbar_wait(&bar_free[st], static_cast<uint32_t>(((it / kStages) - 1) & 1), ctl, 303);
+        mbar_expect_tx(&bar_full[st], 32768u);
+        bulk_g2s(Pst + st * 32768, Pg + (static_cast<size_t>(bh) * NT + chunk_of(it)) * 32768, 32768u, &bar_full[st]);
+      }
     }
-  }
-
-  float x[kVs];
-  {
-    const float* x0 = ADJOINT ? p.dhT : p.h0;
+  } else if (warp > 4) {
+    // ---- product issue: warp m takes contraction steps [m * 8 / kMmaWarps, ...) into accumulator m.
+    // All lanes stay on the path (uniform descriptors); the elected lane issues.
+    if (has_p) {
+      const int m = warp - 5;
+      constexpr int kPer = 8 / kMmaWarps;
+      const uint32_t leader = elect_leader();
+      // A = the P stage (contracted along its columns forward, along its rows for the adjoint),
+      // B = the state operand; one 16-element contraction step moves each by a fixed amount
+      const uint64_t b_desc0 = make_desc(smem_u32(XB), 16u, 1024u);
+      const uint32_t idesc = make_idesc(128, kVs, ADJOINT, false);
+      const uint32_t acc = tmem + static_cast<uint32_t>(m * kVs);
+      for (int it = 0; it < NT; ++it) {
+        const int st = it % kStages;
+        mbar_wait_warp(&bar_full[st], static_cast<uint32_t>((it / kStages) & 1), ctl, 301);
+        step_sync();
+        tc_fence_after();
+        const uint32_t pa = smem_u32(Pst + st * 32768);
+        const uint64_t a_desc0 = ADJOINT ? make_desc(pa, 16384u, 1024u) : make_desc(pa, 16u, 1024u);
 #pragma unroll
-    for (int j = 0; j < kVs; ++j)
-      x[j] = x0 ? x0[(static_cast<size_t>(bh) * kK + tid) * V + v0 + j] : 0.f;
-  }
-  uint4 rnext[2];
-  {
-    const __half* r = Rg + ((static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid) * V + v0;
-    rnext[0] = *reinterpret_cast<const uint4*>(r);
-    rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
-  }
+        for (int jj = 0; jj < kPer; ++jj) {
+          const int j = m * kPer + jj;
+          // byte offsets of contraction step j, in the descriptors' 16-byte units
+          const uint32_t aoff = ADJOINT ? static_cast<uint32_t>(j * 2048) >> 4
+                                        : static_cast<uint32_t>((j >> 2) * 16384 + (j & 3) * 32) >> 4;
+          const uint32_t boff = static_cast<uint32_t>((j >> 2) * 2048 + (j & 3) * 32) >> 4;
+          umma_led(leader, acc, a_desc0 + aoff, b_desc0 + boff, idesc, jj > 0 ? 1u : 0u);
+        }
+        umma_commit_led(leader, bar_mma);
+        umma_commit_led(leader, &bar_free[st]);
+      }
+    }
+  } else {
+    // ---- the state: thread d holds row d of x (16 columns) in fp32
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const __half* Rg = reinterpret_cast<const __half*>(ADJOINT ? p.scratch + p.lay.rb : p.saved + p.lay.r);
+    const float* ADg = reinterpret_cast<const float*>(p.saved + p.lay.ad);
+    unsigned char* Xg = ADJOINT ? p.scratch + p.lay.dh : p.saved + p.lay.hc;
+    const size_t szx = p.lay.sz_hc;
 
-  float a_next = ADg[(static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid];
-  for (int it = 0; it < NT; ++it) {
-    const int c = chunk_of(it);
-    const size_t z = static_cast<size_t>(bh) * NT + c;
-    const int st = it % kStages;
-    const uint32_t st_par = static_cast<uint32_t>((it / kStages) & 1);
-    const float a = a_next;
-    const uint4 r0 = rnext[0], r1 = rnext[1];
-    if (it + 1 < NT) {   // next chunk's decay and input: a whole step of latency cover
-      const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
-      const __half* r = Rg + (zn * kK + tid) * V + v0;
+    float x[kVs];
+    {
+      const float* x0 = ADJOINT ? p.dhT : p.h0;
+#pragma unroll
+      for (int j = 0; j < kVs; ++j) x[j] = x0 ? x0[(static_cast<size_t>(bh) * kK + tid) * V + v0 + j] : 0.f;
+    }
+    uint4 rnext[2];
+    {
+      const __half* r = Rg + ((static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid) * V + v0;
       rnext[0] = *reinterpret_cast<const uint4*>(r);
       rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
-      a_next = ADg[zn * kK + tid];
     }
-    if (has_p) {
-      // critical path: the state as a tensor-core operand, then the product
+    float a_next = ADg[(static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid];
+
+#ifdef LETHE_PHASE_TIMING
+    long long ph[8] = {0,0,0,0,0,0,0,0}; long long tl = clock64(); const long long tstart = tl;
+#define ST(i) { long long tn = clock64(); ph[i] += tn - tl; tl = tn; }
+#else
+#define ST(i)
+#endif
+    for (int it = 0; it < NT; ++it) {
+      const size_t z = static_cast<size_t>(bh) * NT + chunk_of(it);
+      ST(0)
+      if (has_p) {
+        // critical path: the state as a tensor-core operand
 #pragma unroll
-      for (int n = 0; n < kVs; ++n)
-        *reinterpret_cast<__half*>(XB + sw128_off(n, tid, kVs)) = __float2half_rn(x[n]);
-      fence_proxy_async();
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        mbar_wait(&cs->bar[st], st_par, ctl, 301);
-        tc_fence_after();
-        issue_product(tmem, Tile{smem_u32(Pst + st * 32768), 128, ADJOINT}, Tile{smem_u32(XB), kVs, false},
-                      kVs, 128, 0u);
-        umma_commit(bar_mma);
+        for (int n = 0; n < kVs; ++n)
+          *reinterpret_cast<__half*>(XB + sw128_off(n, tid, kVs)) = __float2half_rn(x[n]);
+        fence_proxy_async();
+        tc_fence_before();
+        step_arrive();
       }
-      __syncwarp();
+      ST(1)
+      // in the shadow of the product: this chunk's input and decay, the next chunk's loads, the record
+      const float a = a_next;
+      float rr[kVs];
+      unpack8_f16(rnext[0], rr);
+      unpack8_f16(rnext[1], rr + 8);
+#pragma unroll
+      for (int j = 0; j < kVs; ++j) rr[j] = fmaf(a, x[j], rr[j]);
+      ST(2)
+      if (it + 1 < NT) {
+        const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
+        const __half* r = Rg + (zn * kK + tid) * V + v0;
+        rnext[0] = *reinterpret_cast<const uint4*>(r);
+        rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
+        a_next = ADg[zn * kK + tid];
+      }
+      ST(3)
+      {
+        unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
+        *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
+        *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
+      }
+      ST(4)
+      if (has_p) {
+        mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
+        ST(5)
+        tc_fence_after();
+        float acc[kMmaWarps * kVs];
+        if (kMmaWarps == 1) tmem_ld16(tmem + lane_base, acc);
+        if (kMmaWarps >= 2) tmem_ld32(tmem + lane_base, acc);
+        if (kMmaWarps == 4) tmem_ld32(tmem + lane_base + 32, acc + 32);
+        tmem_ld_wait();
+        ST(6)
+#pragma unroll
+        for (int j = 0; j < kVs; ++j) {
+          float s = acc[j];
+          if (kMmaWarps >= 2) s += acc[kVs + j];
+          if (kMmaWarps == 4) s += acc[2 * kVs + j] + acc[3 * kVs + j];
+          x[j] = rr[j] - s;
+        }
+        ST(7)
+      } else {
+#pragma unroll
+        for (int j = 0; j < kVs; ++j) x[j] = rr[j];
+      }
     }
-    // off the critical path (overlaps the product): the state record
-    {
-      unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
+#ifdef LETHE_PHASE_TIMING
+    if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 3) printf("SCAN adj=%d total %lld | top %lld write %lld unpack %lld pref %lld rec %lld mmawait %lld ld %lld fma %lld\n", (int)ADJOINT, clock64()-tstart, ph[0],ph[1],ph[2],ph[3],ph[4],ph[5],ph[6],ph[7]);
+#endif
+    if (!ADJOINT) {   // the final state as one more record
+      unsigned char* rec = Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx;
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
     }
-    float rr[kVs];
-    unpack8_f16(r0, rr);
-    unpack8_f16(r1, rr + 8);
-    if (has_p) {
-      mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
-      tc_fence_after();
-      float acc[kVs];
-      tmem_ld16(tmem + lane_base, acc);
-      tmem_ld_wait();
+    float* xT = ADJOINT ? p.dh0 : p.hT;
+    if (xT) {
 #pragma unroll
-      for (int j = 0; j < kVs; ++j) x[j] = a * x[j] + rr[j] - acc[j];
-      if (tid == 0 && it + kStages < NT) {
-        mbar_expect_tx(&cs->bar[st], 32768u);
-        bulk_g2s(Pst + st * 32768, Pg + (static_cast<size_t>(bh) * NT + chunk_of(it + kStages)) * 32768, 32768u,
-                 &cs->bar[st]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < kVs; ++j) x[j] = a * x[j] + rr[j];
+      for (int j = 0; j < kVs; j += 4)
+        *reinterpret_cast<float4*>(xT + (static_cast<size_t>(bh) * kK + tid) * V + v0 + j) =
+            make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
     }
-  }
-  if (!ADJOINT) {   // the final state as one more record (the adjoint of the gate needs it)
-    unsigned char* rec = Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx;
-    *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
-    *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
-  }
-  float* xT = ADJOINT ? p.dh0 : p.hT;
-  if (xT) {
-#pragma unroll
-    for (int j = 0; j < kVs; j += 4)
-      *reinterpret_cast<float4*>(xT + (static_cast<size_t>(bh) * kK + tid) * V + v0 + j) =
-          make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 32);
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
 int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
@@ -162,11 +224,11 @@ int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
   if (adjoint) {
     if (cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return kErrLaunch;
-    scan_kernel<true><<<grid, 128, smem, st>>>(p);
+    scan_kernel<true><<<grid, kScanThreads, smem, st>>>(p);
   } else {
     if (cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return kErrLaunch;
-    scan_kernel<false><<<grid, 128, smem, st>>>(p);
+    scan_kernel<false><<<grid, kScanThreads, smem, st>>>(p);
   }
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
