@@ -98,11 +98,12 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   if (DELTA) {
     // rows 64-127: A^T do
-    if (tid == 0) {
+    if (warp == 0) {
       tc_fence_after();
-      issue_product(tmem, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
-      issue_product(tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
-      umma_commit(bar_mma);
+      const uint32_t leader = elect_leader();
+      issue_product_led(leader, tmem, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+      issue_product_led(leader, tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+      umma_commit_led(leader, bar_mma);
     }
     wait_products(bar_mma, ph, ctl, 402);
     if (tid >= 64) {
@@ -116,15 +117,17 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
       }
     }
     sync_for_issue();
-    if (tid == 0) {
+    if (warp == 0) {
       tc_fence_after();
-      issue_product(tmem + 128, Tile{smem_u32(Wt), 64, true}, Tile{smem_u32(DVL), 64, true}, V, 64, 1u, true);
-      umma_commit(bar_mma);
+      const uint32_t leader = elect_leader();
+      issue_product_led(leader, tmem + 128, Tile{smem_u32(Wt), 64, true}, Tile{smem_u32(DVL), 64, true}, V, 64, 1u, true);
+      umma_commit_led(leader, bar_mma);
     }
-  } else if (tid == 0) {
+  } else if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 403);
   {
@@ -185,6 +188,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     tmem_alloc(&cs->tmem_slot, 512);
     tmem_relinquish();
   }
+  LETHE_PHASE_INIT();
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;   // token index of row 0 (stride H)
   float gval = 0.f;
   if (tid < 64 && p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
@@ -214,7 +218,9 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   __syncthreads();
   const float Glast = Gs[63];
 
+  LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 411);
+  LETHE_PHASE("loaded");
   // exp(G_last) <dh, h>: the two tile images share the swizzle, so the product is elementwise
   float dhh = 0.f;
   for (int idx = tid; idx < kK * V / 8; idx += 128) {
@@ -225,6 +231,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     for (int i = 0; i < 8; ++i) dhh += x[i] * y[i];
   }
   dhh = cta_sum128(dhh, tid, tmp + 2) * __expf(Glast);
+  LETHE_PHASE("dhh");
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
@@ -250,18 +257,22 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     tile_st_chunk(VNt, 64 + r, ch, 128, pack8_f16(x));
   }
   sync_for_issue();
+  LETHE_PHASE("convert");
 
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   // ---- group 1: kd dh (rows 64-127 of cD), A^T do (rows 64-127 of cA), dA = do v_new^T (rows 0-63 of cC)
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(cD, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
-    issue_product(cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
-    issue_product(cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 128, false}, 64, V, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, cD, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
+    issue_product_led(leader, cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
+    issue_product_led(leader, cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 128, false}, 64, V, 0u);
+    umma_commit_led(leader, bar_mma);
   }
+  LETHE_PHASE("issue1");
   wait_products(bar_mma, ph, ctl, 412);
+  LETHE_PHASE("g1");
   float t2 = 0.f;
   if (tid >= 64) {
     const int r = tid - 64;
@@ -314,17 +325,21 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   sync_for_issue();
+  LETHE_PHASE("epi1");
 
   // ---- group 2: cB = [do; dv2] h^T;  cA = dAr k (rows 0-63 dq_intra);  cD = dAr^T q + (dec v_new) dh^T
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
-    issue_product(cA, Tile{smem_u32(DS), 128, false}, Tile{smem_u32(X1), 128, true}, 128, 64, 0u);
-    issue_product(cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
-    issue_product(cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
+    issue_product_led(leader, cA, Tile{smem_u32(DS), 128, false}, Tile{smem_u32(X1), 128, true}, 128, 64, 0u);
+    issue_product_led(leader, cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
+    issue_product_led(leader, cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
+    umma_commit_led(leader, bar_mma);
   }
+  LETHE_PHASE("issue2");
   wait_products(bar_mma, ph, ctl, 413);
+  LETHE_PHASE("g2");
   float t1 = 0.f;
   if (tid < 64) {
     const int r = tid;
@@ -379,6 +394,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   __syncthreads();
+  LETHE_PHASE("epi2");
   // ---- Stage-B gate gradient of the chunk (before the reverse cumulative sum)
   if (tid < 64) {
     float dG = t1 + t2 - t3s[tid];
@@ -398,6 +414,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 

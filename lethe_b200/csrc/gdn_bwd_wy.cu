@@ -53,6 +53,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     tmem_alloc(&cs->tmem_slot, kCols);
     tmem_relinquish();
   }
+  LETHE_PHASE_INIT();
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
   float gval = 0.f, bval = 0.f;
   if (tid < 64) {
@@ -81,7 +82,9 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     betas[tid] = bval;
   }
   __syncthreads();
+  LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 421);
+  LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
@@ -106,19 +109,22 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
   }
   sync_for_issue();
+  LETHE_PHASE("convert");
 
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   // ---- group 1: [KK | k dw^T], dT / beta_s, T^T du
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(R0, Tile{smem_u32(T1), 128, false}, Tile{smem_u32(T1), 128, false}, 128, 128, 0u);
-    issue_product(R1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(VT), 64, false}, 64, V, 0u);
-    issue_product(R1, Tile{smem_u32(T1) + 8192, 128, false}, Tile{smem_u32(GK), 64, false}, 64, 128, 1u);
-    issue_product(R2, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, R0, Tile{smem_u32(T1), 128, false}, Tile{smem_u32(T1), 128, false}, 128, 128, 0u);
+    issue_product_led(leader, R1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(VT), 64, false}, 64, V, 0u);
+    issue_product_led(leader, R1, Tile{smem_u32(T1) + 8192, 128, false}, Tile{smem_u32(GK), 64, false}, 64, 128, 1u);
+    issue_product_led(leader, R2, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V, 64, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 422);
+  LETHE_PHASE("g1");
   float pk = 0.f;
   if (tid < 64) {
     float d[64];
@@ -141,13 +147,16 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
       pk += d[l] * __half2float(*reinterpret_cast<const __half*>(TAt + sw128_off(l, tid, 128)));
   }
   sync_for_issue();
+  LETHE_PHASE("epi1");
   // ---- group 2: X = dT T^T
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(R1, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, R1, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 423);
+  LETHE_PHASE("g2");
   if (tid < 64) {
     float d[64];
     tmem_ld32(R1 + lane_base, d);
@@ -157,13 +166,16 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(W8, tid, s8, 64, pack8_f16(d + 8 * s8));
   }
   sync_for_issue();
+  LETHE_PHASE("epi2");
   // ---- group 3: dM = -T^T X
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(R1, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(W8), 64, true}, 64, 64, 0u, true);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, R1, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(W8), 64, true}, 64, 64, 0u, true);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 424);
+  LETHE_PHASE("g3");
   float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f;
   float kk[64];
   if (tid < 64) {
@@ -185,6 +197,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     }
   }
   __syncthreads();
+  LETHE_PHASE("epi3a");
   if (tid < 64) {
     const int r = tid;
 #pragma unroll
@@ -201,14 +214,17 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     }
   }
   sync_for_issue();
+  LETHE_PHASE("epi3b");
   // ---- group 4: dk accumulator = (dkk + dkk^T) k + T'^T dw
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(R0, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(T1), 128, true}, 128, 64, 0u);
-    issue_product(R0, Tile{smem_u32(TP), 64, true}, Tile{smem_u32(T1) + 8192, 128, true}, 128, 64, 1u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, R0, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(T1), 128, true}, 128, 64, 0u);
+    issue_product_led(leader, R0, Tile{smem_u32(TP), 64, true}, Tile{smem_u32(T1) + 8192, 128, true}, 128, 64, 1u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 425);
+  LETHE_PHASE("g4");
   if (tid < 64) {
     const int r = tid;
     const float gam = __expf(Gs[r]);
@@ -259,6 +275,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     dGs[r] = dgb + rowsum_e - colsum_e + bval * pk * gam;
   }
   __syncthreads();
+  LETHE_PHASE("epi4");
   if (tid < 64 && p.gate == LETHE_GATE_SCALAR) {
     float acc = 0.f;
     for (int j = 63; j >= tid; --j) acc += dGs[j];
@@ -266,6 +283,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 

@@ -37,17 +37,38 @@
 #include "../../include/lethe_gdn.h"
 #include "tiles.cuh"
 
-// Development aid: with -DLETHE_PHASE_TIMING one CTA of every kernel prints clock64() stamps at its
-// phase boundaries (never enabled in a normal build).
+// Development aid: with -DLETHE_PHASE_TIMING one CTA of every instrumented kernel records clock64()
+// at its phase boundaries and prints the differences when it ends (never enabled in a normal build).
 #ifdef LETHE_PHASE_TIMING
 #include <stdio.h>
+static __device__ long long g_ph_t[32];
+static __device__ const char* g_ph_name[32];
+#define LETHE_PHASE_INIT()                                                                         \
+  int ph_i_ = 0;                                                                                   \
+  const bool ph_on_ = (blockIdx.x == 200 && blockIdx.y == 0 && threadIdx.x == 0);                  \
+  LETHE_PHASE("start")
 #define LETHE_PHASE(name)                                                                          \
   do {                                                                                             \
-    if (blockIdx.x == 200 && blockIdx.y == 0 && threadIdx.x == 0)                                  \
-      printf("PHASE %s %s %lld\n", __func__, name, static_cast<long long>(clock64()));             \
+    if (ph_on_ && ph_i_ < 32) {                                                                    \
+      g_ph_t[ph_i_] = clock64();                                                                   \
+      g_ph_name[ph_i_] = name;                                                                     \
+      ++ph_i_;                                                                                     \
+    }                                                                                              \
+  } while (0)
+#define LETHE_PHASE_DUMP()                                                                         \
+  do {                                                                                             \
+    if (ph_on_) {                                                                                  \
+      g_ph_t[ph_i_] = clock64();                                                                   \
+      printf("PHASE %s:", __func__);                                                               \
+      for (int i_ = 1; i_ <= ph_i_; ++i_)                                                          \
+        printf(" %s %lld", i_ < ph_i_ ? g_ph_name[i_] : "end", g_ph_t[i_] - g_ph_t[i_ - 1]);       \
+      printf(" | total %lld\n", g_ph_t[ph_i_] - g_ph_t[0]);                                        \
+    }                                                                                              \
   } while (0)
 #else
+#define LETHE_PHASE_INIT()
 #define LETHE_PHASE(name)
+#define LETHE_PHASE_DUMP()
 #endif
 
 namespace lg {

@@ -91,7 +91,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
   }
-  LETHE_PHASE("start");
+  LETHE_PHASE_INIT();
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 601);
   LETHE_PHASE("loaded");
@@ -244,6 +244,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -491,7 +492,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
     bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_load);
   }
-  LETHE_PHASE("start");
+  LETHE_PHASE_INIT();
   __syncthreads();
   LETHE_PHASE("gate");
   mbar_wait_warp(bar_load, 0, ctl, 621);
@@ -699,6 +700,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   LETHE_PHASE("phaseB");
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 

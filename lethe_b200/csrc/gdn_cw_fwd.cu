@@ -71,7 +71,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     }
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
-  LETHE_PHASE("start");
+  LETHE_PHASE_INIT();
   if (tid < 128) {
     gate_tile_cw(p.g, tok0, p.H, tid, Gt);
     reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
@@ -320,6 +320,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 

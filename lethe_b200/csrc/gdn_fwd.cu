@@ -40,7 +40,8 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   float* bgs = fs + 192;     // [64] beta_i exp(G_i)
   float* tmp = fs + 256;     // [2]
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 264);
-  float* Msm = reinterpret_cast<float*>(KQ);
+  float* Msm = reinterpret_cast<float*>(KQ);           // [64][kMs]
+  float* Tsm = Msm + 64 * kMs;                          // [48][64]: finished rows of T, fp32
   unsigned char* WU = KQ;
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -59,6 +60,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tmem_alloc(&cs->tmem_slot, 256);
     tmem_relinquish();
   }
+  LETHE_PHASE_INIT();
   float gval = 0.f, bval = 1.f;
   if (tid < 64) {
     const size_t tok = (static_cast<size_t>(b) * p.L + c * kC + tid) * p.H + h;
@@ -95,7 +97,9 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   __syncthreads();
 
   // ---- operands: k, q -> fp16 in place; kd, beta gamma k, beta v
+  LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 201);
+  LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
@@ -125,15 +129,18 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   fence_proxy_async();
   __syncthreads();
+  LETHE_PHASE("convert");
 
   // ---- product 1: [KK; QK] = [k; q] k^T
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem, Tile{smem_u32(KQ), 128, false}, Tile{smem_u32(KQ), 128, false}, 64, 128, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem, Tile{smem_u32(KQ), 128, false}, Tile{smem_u32(KQ), 128, false}, 64, 128, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   __syncwarp();
   mbar_wait_warp(bar_mma, 0, ctl, 202);
+  LETHE_PHASE("g1");
   tc_fence_after();
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   {
@@ -167,49 +174,76 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE("epi1");
 
-  // ---- T = (I + M)^-1 by forward substitution, one column per thread, column kept in registers
+  // ---- T = (I + M)^-1 by forward substitution, one column per thread, in four blocks of 16 rows.
+  // A block first collects what the finished blocks above it contribute (sixteen independent sums,
+  // T read back from shared memory), then resolves its own 16 rows in registers.
   if (tid < 64) {
-    float col[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) col[i] = 0.f;
+    const int j = tid, jb = j >> 4;
     if (DELTA) {
+#pragma unroll 1
+      for (int blk = 0; blk < 4; ++blk) {
+        float col[16];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        // four partial sums: the products of one row do not wait on one another
-        float a0 = (i == tid) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int r = 0; r < 16; ++r) col[r] = (blk * 16 + r == j) ? 1.f : 0.f;
+        if (blk >= jb) {
+          const float* Mb = Msm + blk * 16 * kMs;
+          for (int s = jb * 16; s < blk * 16; s += 4) {
+            const float t0 = Tsm[(s + 0) * 64 + j], t1 = Tsm[(s + 1) * 64 + j];
+            const float t2 = Tsm[(s + 2) * 64 + j], t3 = Tsm[(s + 3) * 64 + j];
 #pragma unroll
-        for (int s4 = 0; s4 < (i + 3) / 4; ++s4) {
-          const float4 m = *reinterpret_cast<const float4*>(&Msm[i * kMs + 4 * s4]);
-          a0 -= m.x * col[4 * s4];
-          if (4 * s4 + 1 < i) a1 -= m.y * col[4 * s4 + 1];
-          if (4 * s4 + 2 < i) a2 -= m.z * col[4 * s4 + 2];
-          if (4 * s4 + 3 < i) a3 -= m.w * col[4 * s4 + 3];
+            for (int r = 0; r < 16; ++r) {
+              const float4 m = *reinterpret_cast<const float4*>(Mb + r * kMs + s);
+              col[r] -= (m.x * t0 + m.y * t1) + (m.z * t2 + m.w * t3);
+            }
+          }
+#pragma unroll
+          for (int r = 1; r < 16; ++r) {
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < (r + 3) / 4; ++q) {
+              const float4 m = *reinterpret_cast<const float4*>(Mb + r * kMs + blk * 16 + 4 * q);
+              a0 += m.x * col[4 * q];
+              if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
+              if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
+              if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
+            }
+            col[r] -= a0 + a1;
+          }
+          if (blk < 3) {
+#pragma unroll
+            for (int r = 0; r < 16; ++r) Tsm[(blk * 16 + r) * 64 + j] = col[r];
+          }
         }
-        col[i] = (a0 + a1) + (a2 + a3);
-      }
-    }
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      const float t = DELTA ? col[i] : ((i == tid) ? 1.f : 0.f);
-      *reinterpret_cast<__half*>(TA + sw128_off(i, tid, 128)) = __float2half_rn(t);
+        for (int r = 0; r < 16; ++r)
+          *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(col[r]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        *reinterpret_cast<__half*>(TA + sw128_off(i, j, 128)) = __float2half_rn((i == j) ? 1.f : 0.f);
     }
   }
   fence_proxy_async();
   __syncthreads();
+  LETHE_PHASE("inverse");
 
   uint32_t ph = 1;
   if (DELTA) {
     // ---- product 2: [w | u] = T [beta gamma k | beta v]
-    if (tid == 0) {
+    if (warp == 0) {
       tc_fence_after();
-      issue_product(tmem, Tile{smem_u32(TA), 128, false}, Tile{smem_u32(BGK), 64, true}, 128 + V, 64, 0u);
-      umma_commit(bar_mma);
-      bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
-      bulk_commit();
+      const uint32_t leader = elect_leader();
+      issue_product_led(leader, tmem, Tile{smem_u32(TA), 128, false}, Tile{smem_u32(BGK), 64, true}, 128 + V, 64, 0u);
+      umma_commit_led(leader, bar_mma);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
+      if (tid == 0) bulk_commit();
     }
     __syncwarp();
     mbar_wait_warp(bar_mma, ph, ctl, 203);
+    LETHE_PHASE("g2");
     ph ^= 1;
     tc_fence_after();
     if (tid < 64) {
@@ -225,6 +259,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tc_fence_before();
     fence_proxy_async();
     __syncthreads();
+    LETHE_PHASE("epi2");
   } else if (tid == 0) {
     bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
     bulk_commit();
@@ -232,20 +267,22 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
 
   // ---- product 3: [P | R] = kd^T [w | u]   (no delta: R = kd^T v)
   constexpr int N3 = DELTA ? 128 + V : V;
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem, Tile{smem_u32(KD), 64, true}, Tile{smem_u32(DELTA ? WU : BV), 64, true}, N3, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem, Tile{smem_u32(KD), 64, true}, Tile{smem_u32(DELTA ? WU : BV), 64, true}, N3, 64, 0u);
+    umma_commit_led(leader, bar_mma);
     if (DELTA) {
-      bulk_s2g(p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, WU, 16384);
-      bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, WU + 16384, V * 128);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, WU, 16384);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, WU + 16384, V * 128);
     } else {
-      bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, BV, V * 128);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, BV, V * 128);
     }
-    bulk_commit();
+    if (tid == 0) bulk_commit();
   }
   __syncwarp();
   mbar_wait_warp(bar_mma, ph, ctl, 204);
+  LETHE_PHASE("g3");
   tc_fence_after();
   {
     unsigned char* Pg = p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p;
@@ -267,9 +304,11 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       }
     }
   }
+  LETHE_PHASE("epi3");
   if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
+  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -361,10 +400,11 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   fence_proxy_async();
   __syncthreads();
 
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem, Tile{smem_u32(WQ), 128, false}, Tile{smem_u32(HT), 128, true}, V, 128, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem, Tile{smem_u32(WQ), 128, false}, Tile{smem_u32(HT), 128, true}, V, 128, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   __syncwarp();
   mbar_wait_warp(bar_mma, 0, ctl, 212);
@@ -395,12 +435,13 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   fence_proxy_async();
   __syncthreads();
 
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem, Tile{smem_u32(TAt), 128, false}, Tile{smem_u32(VN), 64, true}, V, 64, 1u);
-    umma_commit(bar_mma);
-    bulk_s2g(p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn, VN, V * 128);
-    bulk_commit();
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem, Tile{smem_u32(TAt), 128, false}, Tile{smem_u32(VN), 64, true}, V, 64, 1u);
+    umma_commit_led(leader, bar_mma);
+    if (tid == 0) bulk_s2g(p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn, VN, V * 128);
+    if (tid == 0) bulk_commit();
   }
   __syncwarp();
   mbar_wait_warp(bar_mma, 1, ctl, 213);

@@ -35,6 +35,17 @@ __device__ __forceinline__ void issue_product(uint32_t tmem_d, const Tile& A, co
   }
 }
 
+// The same, called by every lane of a converged warp with identical arguments; the lane whose
+// `leader` (from elect_leader) is non-zero issues.  With the whole warp on the path the descriptors
+// are uniform values, which is markedly cheaper per product than issuing from a one-thread branch.
+__device__ __forceinline__ void issue_product_led(uint32_t leader, uint32_t tmem_d, const Tile& A, const Tile& B,
+                                                  int N, int kc, uint32_t acc, bool a_neg = false) {
+  const uint32_t idesc = make_idesc(128, static_cast<uint32_t>(N), A.mn, B.mn, a_neg);
+  for (int j = 0; j < kc / 16; ++j) {
+    umma_led(leader, tmem_d, tile_desc(A, j), tile_desc(B, j), idesc, (j > 0) ? 1u : acc);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // register <-> tile helpers (16-bit elements, 8 per 16-byte chunk)
 // ---------------------------------------------------------------------------------------------
