@@ -13,7 +13,7 @@ int launch_output(const Problem&, const CUtensorMap&, cudaStream_t);
 int launch_scan(const Problem&, bool adjoint, cudaStream_t);
 int launch_bwd_pre(const Problem&, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t);
 int launch_bwd_main(const Problem&, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                    const CUtensorMap& mdo, cudaStream_t, uint32_t mask);
+                    const CUtensorMap& mdo, const OutMaps& mo, cudaStream_t, uint32_t mask);
 int launch_bwd_main_cw(const Problem&, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                        const CUtensorMap& mdo, cudaStream_t, uint32_t mask);
 
@@ -147,8 +147,17 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
   const uint32_t m = a->kernel_mask ? a->kernel_mask : 15u;
   if ((m & 1u) && (e = launch_bwd_pre(p, mq, mdo, st))) return e;
   if ((m & 2u) && (e = launch_scan(p, true, st))) return e;
-  if ((m & 12u) && (e = (p.gate == LETHE_GATE_CHANNEL ? launch_bwd_main_cw(p, mq, mk, mv, mdo, st, m)
-                                                      : launch_bwd_main(p, mq, mk, mv, mdo, st, m)))) return e;
+  if (m & 12u) {
+    if (p.gate == LETHE_GATE_CHANNEL) {
+      if ((e = launch_bwd_main_cw(p, mq, mk, mv, mdo, st, m))) return e;
+    } else {
+      OutMaps mo;
+      if ((e = token_map(&mo.dq, a->dq, a->dims, kK))) return e;
+      if ((e = token_map(&mo.dk, a->dk, a->dims, kK))) return e;
+      if ((e = token_map(&mo.dv, a->dv, a->dims, a->dims.V))) return e;
+      if ((e = launch_bwd_main(p, mq, mk, mv, mdo, mo, st, m))) return e;
+    }
+  }
   return kOk;
 }
 

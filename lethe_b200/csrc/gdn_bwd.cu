@@ -131,15 +131,21 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   }
   wait_products(bar_mma, ph, ctl, 403);
   {
-    __half* Rg = reinterpret_cast<__half*>(p.scratch + p.lay.rb + static_cast<size_t>(z) * p.lay.sz_rb) +
-                 static_cast<size_t>(tid) * V;
+    unsigned char* SR = QG;   // q and w are dead: Rb is staged there as its record image
 #pragma unroll
     for (int jb = 0; jb < V / 32; ++jb) {
       float d[32];
       tmem_ld32(tmem + 128 + lane_base + jb * 32, d);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Rg + jb * 32 + 8 * i) = pack8_f16(d + 8 * i);
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tid, jb * 4 + i)) = pack8_f16(d + 8 * i);
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      bulk_s2g(p.scratch + p.lay.rb + static_cast<size_t>(z) * p.lay.sz_rb, SR, V * 256);
+      bulk_commit();
+      bulk_wait_read();
     }
   }
   tc_fence_before();
@@ -152,9 +158,10 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
 // [do; dv2] h^T; cC [256,320) do v_new^T; cD [320,448) Stage-B dk.
 // ---------------------------------------------------------------------------------------------
 template <int V, bool DELTA>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                  const __grid_constant__ CUtensorMap mdo) {
+                  const __grid_constant__ CUtensorMap mdo, const __grid_constant__ CUtensorMap mdq,
+                  const __grid_constant__ CUtensorMap mdk) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024(smem_raw);
   unsigned char* X1 = sm;                       // 32 KB: rows 0-63 k, rows 64-127 kd
@@ -166,14 +173,17 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   unsigned char* DHt = Ht + V * 256;            // V*256: dh
   unsigned char* DS = DHt + V * 256;            // 16 KB: rows 0-63 scale*dA*ratio, rows 64-127 zero
   float* fs = reinterpret_cast<float*>(DS + 16384);
-  float* Gs = fs;          // [64]
-  float* t3s = fs + 64;    // [64] column sum of E plus dde row sum
-  float* dde_s = fs + 208; // [64] dde row sums
-  float* dGs = fs + 128;   // [64]
-  float* tmp = fs + 192;   // [8]
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 272);
+  float* Gs = fs;            // [64]
+  float* t3p = fs + 64;      // [2][64] per column half: column sum of E plus dde row sum
+  float* ddep = fs + 192;    // [2][64] per column half: dde row sums
+  float* t2p = fs + 320;     // [2][64] per column half: row sums of dA o A
+  float* t1p = fs + 448;     // [2][64] per column half: <dq_inter, q>
+  float* tmp = fs + 640;     // [16]
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 656);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves
+  // take the same rows and split the columns of every epilogue.
+  const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
   const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
@@ -223,16 +233,16 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("loaded");
   // exp(G_last) <dh, h>: the two tile images share the swizzle, so the product is elementwise
   float dhh = 0.f;
-  for (int idx = tid; idx < kK * V / 8; idx += 128) {
+  for (int idx = tid; idx < kK * V / 8; idx += 256) {
     float x[8], y[8];
     unpack8_f16(*reinterpret_cast<const uint4*>(DHt + idx * 16), x);
     unpack8_f16(*reinterpret_cast<const uint4*>(Ht + idx * 16), y);
 #pragma unroll
     for (int i = 0; i < 8; ++i) dhh += x[i] * y[i];
   }
-  dhh = cta_sum128(dhh, tid, tmp + 2) * __expf(Glast);
+  dhh = cta_sum256(dhh, tid, tmp + 2) * __expf(Glast);
   LETHE_PHASE("dhh");
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
     unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
@@ -245,7 +255,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
     if (ch < 8) tile_st_chunk(DS, 64 + r, ch, 128, make_uint4(0, 0, 0, 0));
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(DD, r, ch, 128), x);
@@ -273,14 +283,13 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("issue1");
   wait_products(bar_mma, ph, ctl, 412);
   LETHE_PHASE("g1");
-  float t2 = 0.f;
-  if (tid >= 64) {
-    const int r = tid - 64;
+  if (tq >= 64) {
+    const int r = tq - 64;
     float t3 = 0.f, dde = 0.f;
-    unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
     __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
 #pragma unroll
-    for (int jb = 0; jb < V / 32; ++jb) {
+    for (int jj = 0; jj < V / 64; ++jj) {
+      const int jb = half * (V / 64) + jj;
       float d[32], d1[32];
       tmem_ld32(cA + lane_base + jb * 32, d);
       tmem_ld32(cD + lane_base + jb * 32, d1);
@@ -297,32 +306,33 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
         }
         const uint4 pk = pack8_f16(d + 8 * i);
         tile_st_chunk(DD, 64 + r, jb * 4 + i, 128, pk);
-        if (DELTA) *reinterpret_cast<uint4*>(dv2_g + sw128_chunk(r, jb * 4 + i, 64)) = pk;
-        else *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(d + 8 * i);
+        if (!DELTA) *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(d + 8 * i);
       }
     }
-    t3s[r] = t3 + dde;
-    dde_s[r] = dde;
+    t3p[half * 64 + r] = t3 + dde;
+    ddep[half * 64 + r] = dde;
   } else {
-    const int r = tid;
-    float d[64];
-    tmem_ld32(cC + lane_base, d);
-    tmem_ld32(cC + lane_base + 32, d + 32);
+    const int r = tq;
+    float d[32];
+    tmem_ld32(cC + lane_base + half * 32, d);
     tmem_ld_wait();
     const float Gr = Gs[r];
+    float t2 = 0.f;
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
+    for (int q = 0; q < 4; ++q) {
+      const int s8 = half * 4 + q;
       float a[8], y[8];
       unpack8_f16(tile_ld_chunk(TAt, 64 + r, s8, 128), a);   // A[r, s] (already holds scale * ratio)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int s = s8 * 8 + i;
-        const float da = (s <= r) ? d[s] : 0.f;
+        const float da = (s <= r) ? d[q * 8 + i] : 0.f;
         t2 += da * a[i];
         y[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * da : 0.f;
       }
       tile_st_chunk(DS, r, s8, 128, pack8_f16(y));
     }
+    t2p[half * 64 + r] = t2;
   }
   sync_for_issue();
   LETHE_PHASE("epi1");
@@ -336,19 +346,32 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     issue_product_led(leader, cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
     issue_product_led(leader, cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
     umma_commit_led(leader, bar_mma);
+    if (DELTA && tid == 0) {   // dv2 record: rows 64-127 of each DD atom are one atom of the 64-row image
+      unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
+      for (int a = 0; a < V / 64; ++a) bulk_s2g(dv2_g + a * 8192, DD + a * 16384 + 8192, 8192);
+      bulk_commit();
+    }
   }
   LETHE_PHASE("issue2");
   wait_products(bar_mma, ph, ctl, 413);
   LETHE_PHASE("g2");
-  float t1 = 0.f;
-  if (tid < 64) {
-    const int r = tid;
+  // Every operand tile is dead now: the outputs are staged in them as the images their consumers read
+  // and leave by bulk / tensor-map stores (row-per-thread stores straight from registers would touch
+  // 32 lines per instruction).
+  if (tid == 0) bulk_wait_read();
+  __syncthreads();
+  unsigned char* SQ = X1;            // dq, bf16 64 x 128 (two atoms)
+  unsigned char* SK = DD;            // delta: fp32 dk partial, 32 KB (runs on into the next tiles); else dk bf16
+  unsigned char* SW = Ht;            // dw, fp16 64 x 128
+  if (tq < 64) {
+    const int r = tq;
     const float sg = p.scale * __expf(Gs[r]);
-    __nv_bfloat16* dq_g = p.dq + (tok0 + static_cast<size_t>(r) * p.H) * kK;
-    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(r) * p.H) * kK;
-    float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb) + r * kK;
+    float t1 = 0.f;
+    // fp32 dk partial for the WY kernel: four 32-column blocks of [row][eight 16-byte pieces], piece c
+    // of row r stored at c ^ (r & 7), so that the record can be read back from shared memory row-wise
+    float* dkb_s = reinterpret_cast<float*>(SK) + r * 32;
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jb = 2 * half; jb < 2 * half + 2; ++jb) {
       float dqg[32], dqi[32];
       tmem_ld32(cB + lane_base + jb * 32, dqg);
       tmem_ld32(cA + lane_base + jb * 32, dqi);
@@ -363,7 +386,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
           t1 += a * qv[e];
           o8[e] = a + dqi[8 * i + e];
         }
-        *reinterpret_cast<uint4*>(dq_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+        tile_st_chunk(SQ, r, jb * 4 + i, 64, pack8_bf16(o8));
       }
       float dkv[32];
       tmem_ld32(cD + lane_base + jb * 32, dkv);
@@ -371,47 +394,59 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
       if (DELTA) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<float4*>(dkb_g + jb * 32 + 4 * i) =
+          *reinterpret_cast<float4*>(dkb_s + jb * 2048 + 4 * (i ^ (r & 7))) =
               make_float4(dkv[4 * i], dkv[4 * i + 1], dkv[4 * i + 2], dkv[4 * i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(dkv + 8 * i);
+        for (int i = 0; i < 4; ++i) tile_st_chunk(SK, r, jb * 4 + i, 64, pack8_bf16(dkv + 8 * i));
       }
     }
+    t1p[half * 64 + r] = t1;
   } else if (DELTA) {
-    const int r = tid - 64;
-    unsigned char* dw_g = p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw;
+    const int r = tq - 64;
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jb = 2 * half; jb < 2 * half + 2; ++jb) {
       float d[32];
       tmem_ld32(cB + lane_base + jb * 32, d);
       tmem_ld_wait();
 #pragma unroll
       for (int e = 0; e < 32; ++e) d[e] = -d[e];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(dw_g + sw128_chunk(r, jb * 4 + i, 64)) = pack8_f16(d + 8 * i);
+      for (int i = 0; i < 4; ++i) tile_st_chunk(SW, r, jb * 4 + i, 64, pack8_f16(d + 8 * i));
     }
   }
+  fence_proxy_async();
   __syncthreads();
+  if (tid == 0) {
+    for (int a = 0; a < 2; ++a) tma_store_4d(&mdq, SQ + a * 8192, a * 64, h, c * kC, b);
+    if (DELTA) {
+      bulk_s2g(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb, SK, 32768);
+      bulk_s2g(p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, SW, 16384);
+    } else {
+      for (int a = 0; a < 2; ++a) tma_store_4d(&mdk, SK + a * 8192, a * 64, h, c * kC, b);
+    }
+    bulk_commit();
+  }
   LETHE_PHASE("epi2");
   // ---- Stage-B gate gradient of the chunk (before the reverse cumulative sum)
-  if (tid < 64) {
-    float dG = t1 + t2 - t3s[tid];
-    if (tid == 63) {
-      float sdde = 0.f;
-      for (int j = 0; j < 64; ++j) sdde += dde_s[j];
-      dG += dhh + sdde;
-    }
-    dGs[tid] = dG;
-    if (DELTA) reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid] = dG;
+  float dG = 0.f;
+  {
+    float sdde = (tid < 64) ? ddep[tid] + ddep[64 + tid] : 0.f;   // sum over the chunk's rows, fixed tree
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sdde += __shfl_xor_sync(0xffffffffu, sdde, o);
+    if (tid == 0 || tid == 32) tmp[12 + (tid >> 5)] = sdde;
   }
   __syncthreads();
-  if (!DELTA && tid < 64 && p.gate == LETHE_GATE_SCALAR) {
-    float acc = 0.f;
-    for (int j = 63; j >= tid; --j) acc += dGs[j];
-    p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  if (tid < 64) {
+    dG = (t1p[tid] + t1p[64 + tid]) + (t2p[tid] + t2p[64 + tid]) - (t3p[tid] + t3p[64 + tid]);
+    if (tid == 63) dG += dhh + (tmp[12] + tmp[13]);
+    if (DELTA) reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid] = dG;
   }
+  if (!DELTA) {
+    const float acc = chunk_rev_cumsum(dG, tid, tmp);
+    if (tid < 64 && p.gate == LETHE_GATE_SCALAR) p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  }
+  if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
   LETHE_PHASE_DUMP();
@@ -435,10 +470,10 @@ static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
 }
 template <int V, bool DELTA>
 static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo,
-                           cudaStream_t st) {
-  const int smem = 32768 + 16384 + V * 256 * 4 + 16384 * 2 + 272 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+                           const OutMaps& mo, cudaStream_t st) {
+  const int smem = 32768 + 16384 + V * 256 * 4 + 16384 * 2 + 656 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
-  bwd_stageb_kernel<V, DELTA><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mdo);
+  bwd_stageb_kernel<V, DELTA><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mdo, mo.dq, mo.dk);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
@@ -450,18 +485,18 @@ int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& m
   return p.delta ? launch_pre_t<128, true, false>(p, mq, mdo, st) : launch_pre_t<128, false, false>(p, mq, mdo, st);
 }
 
-int launch_bwd_wy(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st);
+int launch_bwd_wy(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, const OutMaps& mo, cudaStream_t st);
 
 // mask bit 4: Stage B, bit 8: WY VJP (delta variants only)
 int launch_bwd_main(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                    const CUtensorMap& mdo, cudaStream_t st, uint32_t mask) {
+                    const CUtensorMap& mdo, const OutMaps& mo, cudaStream_t st, uint32_t mask) {
   int e = kOk;
   if (mask & 4u) {
-    if (p.V == 64) e = p.delta ? launch_stageb_t<64, true>(p, mq, mk, mdo, st) : launch_stageb_t<64, false>(p, mq, mk, mdo, st);
-    else e = p.delta ? launch_stageb_t<128, true>(p, mq, mk, mdo, st) : launch_stageb_t<128, false>(p, mq, mk, mdo, st);
+    if (p.V == 64) e = p.delta ? launch_stageb_t<64, true>(p, mq, mk, mdo, mo, st) : launch_stageb_t<64, false>(p, mq, mk, mdo, mo, st);
+    else e = p.delta ? launch_stageb_t<128, true>(p, mq, mk, mdo, mo, st) : launch_stageb_t<128, false>(p, mq, mk, mdo, mo, st);
   }
   if (e || !p.delta || !(mask & 8u)) return e;
-  return launch_bwd_wy(p, mk, mv, st);
+  return launch_bwd_wy(p, mk, mv, mo, st);
 }
 
 }  // namespace lg

@@ -19,7 +19,8 @@ namespace lg {
 
 template <int V>
 __global__ void __launch_bounds__(128)
-bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
+bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv,
+               const __grid_constant__ CUtensorMap mdk, const __grid_constant__ CUtensorMap mdv) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024(smem_raw);
   unsigned char* T1 = sm;                       // 32 KB: rows 0-63 k, rows 64-127 dw
@@ -32,9 +33,9 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   float* fs = reinterpret_cast<float*>(VT + V * 128 + 8192);
   float* Gs = fs;          // [64]
   float* betas = fs + 64;  // [64]
-  float* dGs = fs + 128;   // [64]
   float* tmp = fs + 192;   // [8]
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 200);
+  float* bgs = fs + 200;   // [64] beta_i exp(G_i)
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 264);
   float* DK = reinterpret_cast<float*>(GK);    // fp32 [64][64], column XOR swizzle
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -42,11 +43,13 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  uint64_t* bar_dkb = &cs->bar[2];
   constexpr uint32_t kCols = (V == 64) ? 256u : 512u;
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
+    mbar_init(bar_dkb, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -55,10 +58,11 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   LETHE_PHASE_INIT();
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
-  float gval = 0.f, bval = 0.f;
+  float gval = 0.f, bval = 0.f, dgb = 0.f;
   if (tid < 64) {
     if (p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
     bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+    dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid];
   }
   tc_fence_before();
   __syncthreads();
@@ -80,6 +84,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   if (tid < 64) {
     Gs[tid] = G;
     betas[tid] = bval;
+    bgs[tid] = bval * __expf(G);
   }
   __syncthreads();
   LETHE_PHASE("setup");
@@ -98,7 +103,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
       float t[8];
       unpack8_f16(tile_ld_chunk(TAt, r, ch, 128), t);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) t[i] *= betas[ch * 8 + i] * __expf(Gs[ch * 8 + i]);
+      for (int i = 0; i < 8; ++i) t[i] *= bgs[ch * 8 + i];
       tile_st_chunk(TP, r, ch, 64, pack8_f16(t));
     }
   }
@@ -176,7 +181,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   wait_products(bar_mma, ph, ctl, 424);
   LETHE_PHASE("g3");
-  float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f;
+  float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f, dgv = 0.f;
   float kk[64];
   if (tid < 64) {
     const int r = tid;
@@ -222,14 +227,22 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     issue_product_led(leader, R0, Tile{smem_u32(W8), 64, false}, Tile{smem_u32(T1), 128, true}, 128, 64, 0u);
     issue_product_led(leader, R0, Tile{smem_u32(TP), 64, true}, Tile{smem_u32(T1) + 8192, 128, true}, 128, 64, 1u);
     umma_commit_led(leader, bar_mma);
+    // Stage B's fp32 dk partial lands in the two tiles nothing reads any more (GK / DK and [T | A])
+    if (tid == 0) {
+      mbar_expect_tx(bar_dkb, 32768u);
+      bulk_g2s(GK, p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb, 32768u, bar_dkb);
+    }
   }
   wait_products(bar_mma, ph, ctl, 425);
   LETHE_PHASE("g4");
+  // [k; dw] is dead once the last products are done: dk and dv are staged there as bf16 tiles and
+  // leave by tensor-map stores
+  unsigned char* SKo = T1;            // dk: 64 x 128, two atoms
+  unsigned char* SV = T1 + 16384;     // dv: 64 x V
   if (tid < 64) {
     const int r = tid;
     const float gam = __expf(Gs[r]);
     float rv = 0.f;
-    __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
 #pragma unroll
     for (int jb = 0; jb < V / 32; ++jb) {
       float d[32];
@@ -244,11 +257,11 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
           rv += d[8 * i + e] * vv[e];
           o8[e] = bval * d[8 * i + e];
         }
-        *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+        tile_st_chunk(SV, r, jb * 4 + i, 64, pack8_bf16(o8));
       }
     }
-    __nv_bfloat16* dk_g = p.dk + (tok0 + static_cast<size_t>(r) * p.H) * kK;
-    const float* dkb_g = reinterpret_cast<const float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb) + r * kK;
+    const float* dkb_s = reinterpret_cast<const float*>(GK) + r * 32;
+    mbar_wait_warp(bar_dkb, 0, ctl, 426);
 #pragma unroll 1
     for (int jb = 0; jb < 4; ++jb) {
       float sk[32];
@@ -256,13 +269,13 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float4 b0 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i);
-        const float4 b1 = *reinterpret_cast<const float4*>(dkb_g + jb * 32 + 8 * i + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(dkb_s + jb * 2048 + 4 * ((2 * i) ^ (r & 7)));
+        const float4 b1 = *reinterpret_cast<const float4*>(dkb_s + jb * 2048 + 4 * ((2 * i + 1) ^ (r & 7)));
         const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         float o8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) o8[e] = bb[e] + sk[8 * i + e];
-        *reinterpret_cast<uint4*>(dk_g + jb * 32 + 8 * i) = pack8_bf16(o8);
+        tile_st_chunk(SKo, r, jb * 4 + i, 64, pack8_bf16(o8));
       }
     }
     if (p.dbeta_w) {
@@ -271,16 +284,21 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     } else {
       p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
     }
-    const float dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[r];
-    dGs[r] = dgb + rowsum_e - colsum_e + bval * pk * gam;
+    dgv = dgb + rowsum_e - colsum_e + bval * pk * gam;
   }
+  fence_proxy_async();
   __syncthreads();
-  LETHE_PHASE("epi4");
-  if (tid < 64 && p.gate == LETHE_GATE_SCALAR) {
-    float acc = 0.f;
-    for (int j = 63; j >= tid; --j) acc += dGs[j];
-    p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  if (tid == 0) {
+    for (int a = 0; a < 2; ++a) tma_store_4d(&mdk, SKo + a * 8192, a * 64, h, c * kC, b);
+    for (int a = 0; a < V / 64; ++a) tma_store_4d(&mdv, SV + a * 8192, a * 64, h, c * kC, b);
+    bulk_commit();
   }
+  LETHE_PHASE("epi4");
+  {
+    const float acc = chunk_rev_cumsum(dgv, tid, tmp);
+    if (tid < 64 && p.gate == LETHE_GATE_SCALAR) p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
+  }
+  if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
   LETHE_PHASE_DUMP();
@@ -288,16 +306,17 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
 }
 
 template <int V>
-static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
-  const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 200 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, const OutMaps& mo,
+                        cudaStream_t st) {
+  const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 264 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   if (cudaFuncSetAttribute(bwd_wy2_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return kErrLaunch;
-  bwd_wy2_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv);
+  bwd_wy2_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv, mo.dk, mo.dv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
-int launch_bwd_wy(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
-  return p.V == 64 ? launch_wy2_t<64>(p, mk, mv, st) : launch_wy2_t<128>(p, mk, mv, st);
+int launch_bwd_wy(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, const OutMaps& mo, cudaStream_t st) {
+  return p.V == 64 ? launch_wy2_t<64>(p, mk, mv, mo, st) : launch_wy2_t<128>(p, mk, mv, mo, st);
 }
 
 }  // namespace lg

@@ -155,6 +155,20 @@ __device__ __forceinline__ float chunk_cumsum(float x, int tid, float* tmp) {
   return x;
 }
 
+// Inclusive suffix sum over threads 0..63 (x_t + x_{t+1} + ... + x_63), same calling rules.
+__device__ __forceinline__ float chunk_rev_cumsum(float x, int tid, float* tmp) {
+  const int lane = tid & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float y = __shfl_down_sync(0xffffffffu, x, o);
+    if (lane + o < 32) x += y;
+  }
+  if (tid == 32) tmp[0] = x;
+  __syncthreads();
+  if (tid < 32) x += tmp[0];
+  return x;
+}
+
 // Channel-wise gate tile: cumulative log decay of the chunk, 64 rows x 128 channels of fp32 in
 // shared memory.  Element (row, col) lives at gidx(row, col): the column is XOR-ed with the low row
 // bits so that both "thread d walks column d" and "thread i walks row i" are free of bank conflicts.
@@ -202,6 +216,13 @@ __device__ __forceinline__ void wait_products(uint64_t* bar, uint32_t& phase, co
   tc_fence_after();
 }
 
+// The scan's input records R / Rb (128 rows x V columns, fp16) are stored as V / 16 column blocks of
+// [128 rows][16 columns]: one contiguous 4 KB block per scan CTA, 32 bytes per thread.  Byte offset of
+// the 8-column piece `col8` of `row`:
+__device__ __forceinline__ uint32_t rrec_off(int row, int col8) {
+  return static_cast<uint32_t>((col8 >> 1) * 4096 + row * 32 + (col8 & 1) * 16);
+}
+
 // Deterministic sum over the 128 threads of a CTA (fixed tree).  `red` is a shared float[4].
 __device__ __forceinline__ float cta_sum128(float x, int tid, float* red) {
 #pragma unroll
@@ -210,6 +231,16 @@ __device__ __forceinline__ float cta_sum128(float x, int tid, float* red) {
   if ((tid & 31) == 0) red[tid >> 5] = x;
   __syncthreads();
   return (red[0] + red[1]) + (red[2] + red[3]);
+}
+
+// The same over 256 threads.  `red` is a shared float[8].
+__device__ __forceinline__ float cta_sum256(float x, int tid, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = x;
+  __syncthreads();
+  return ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
 }
 
 }  // namespace lg

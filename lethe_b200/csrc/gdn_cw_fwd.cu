@@ -296,28 +296,37 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     bulk_commit();
   }
   wait_products(bar_mma, ph, ctl, 504);
-  if (tid < 128) {
-    unsigned char* Pg = p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p;
-    __half* Rg = reinterpret_cast<__half*>(p.saved + p.lay.r + static_cast<size_t>(z) * p.lay.sz_r) +
-                 static_cast<size_t>(tid) * V;
+  {
+    // P and R are staged as their record images in the two ratio-scaled operand tiles (dead now) and
+    // leave by bulk stores; the two thread halves split the columns.
+    unsigned char* SP = LA;
+    unsigned char* SR = KR;
+    const int tq = tid & 127, half = tid >> 7;
+    constexpr int kHalfBlocks = N3 / 64;
 #pragma unroll 1
-    for (int jb = 0; jb < N3 / 32; ++jb) {
+    for (int jb = half * kHalfBlocks; jb < (half + 1) * kHalfBlocks; ++jb) {
       float d[32];
       tmem_ld32(tmem + lane_base + jb * 32, d);
       tmem_ld_wait();
       if (DELTA && jb < 4) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(Pg + sw128_chunk(tid, jb * 4 + i, 128)) = pack8_f16(d + 8 * i);
+        for (int i = 0; i < 4; ++i) tile_st_chunk(SP, tq, jb * 4 + i, 128, pack8_f16(d + 8 * i));
       } else {
-        const int c0 = (jb - (DELTA ? 4 : 0)) * 32;
+        const int c8 = (jb - (DELTA ? 4 : 0)) * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Rg + c0 + 8 * i) = pack8_f16(d + 8 * i);
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tq, c8 + i)) = pack8_f16(d + 8 * i);
       }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      if (DELTA) bulk_s2g(p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p, SP, 32768);
+      bulk_s2g(p.saved + p.lay.r + static_cast<size_t>(z) * p.lay.sz_r, SR, V * 256);
+      bulk_commit();
     }
   }
   LETHE_PHASE("pr");
-  if (tid == 0) bulk_wait_all();
+  if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
   LETHE_PHASE_DUMP();

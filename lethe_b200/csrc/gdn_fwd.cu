@@ -189,13 +189,16 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
         for (int r = 0; r < 16; ++r) col[r] = (blk * 16 + r == j) ? 1.f : 0.f;
         if (blk >= jb) {
           const float* Mb = Msm + blk * 16 * kMs;
-          for (int s = jb * 16; s < blk * 16; s += 4) {
-            const float t0 = Tsm[(s + 0) * 64 + j], t1 = Tsm[(s + 1) * 64 + j];
-            const float t2 = Tsm[(s + 2) * 64 + j], t3 = Tsm[(s + 3) * 64 + j];
+          for (int s = jb * 16; s < blk * 16; s += 8) {
+            float t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = Tsm[(s + i) * 64 + j];
 #pragma unroll
             for (int r = 0; r < 16; ++r) {
-              const float4 m = *reinterpret_cast<const float4*>(Mb + r * kMs + s);
-              col[r] -= (m.x * t0 + m.y * t1) + (m.z * t2 + m.w * t3);
+              const float4 m0 = *reinterpret_cast<const float4*>(Mb + r * kMs + s);
+              const float4 m1 = *reinterpret_cast<const float4*>(Mb + r * kMs + s + 4);
+              col[r] -= ((m0.x * t[0] + m0.y * t[1]) + (m0.z * t[2] + m0.w * t[3])) +
+                        ((m1.x * t[4] + m1.y * t[5]) + (m1.z * t[6] + m1.w * t[7]));
             }
           }
 #pragma unroll
@@ -284,10 +287,14 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   mbar_wait_warp(bar_mma, ph, ctl, 204);
   LETHE_PHASE("g3");
   tc_fence_after();
+  // P and R are staged as their record images in tiles nothing reads any more and leave by bulk
+  // stores: P behind BGK (beta gamma k, beta v, kd are dead), R where k and q were once the stores
+  // of [w | u] have finished reading it.
+  if (tid == 0) bulk_wait_read();
+  __syncthreads();
   {
-    unsigned char* Pg = p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p;
-    __half* Rg = reinterpret_cast<__half*>(p.saved + p.lay.r + static_cast<size_t>(z) * p.lay.sz_r) +
-                 static_cast<size_t>(tid) * V;
+    unsigned char* SP = BGK;
+    unsigned char* SR = KQ;
 #pragma unroll 1
     for (int jb = 0; jb < N3 / 32; ++jb) {
       float d[32];
@@ -295,17 +302,23 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       tmem_ld_wait();
       if (DELTA && jb < 4) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(Pg + sw128_chunk(tid, jb * 4 + i, 128)) = pack8_f16(d + 8 * i);
+        for (int i = 0; i < 4; ++i) tile_st_chunk(SP, tid, jb * 4 + i, 128, pack8_f16(d + 8 * i));
       } else {
-        const int c0 = (jb - (DELTA ? 4 : 0)) * 32;
+        const int c8 = (jb - (DELTA ? 4 : 0)) * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Rg + c0 + 8 * i) = pack8_f16(d + 8 * i);
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tid, c8 + i)) = pack8_f16(d + 8 * i);
       }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      if (DELTA) bulk_s2g(p.saved + p.lay.p + static_cast<size_t>(z) * p.lay.sz_p, SP, 32768);
+      bulk_s2g(p.saved + p.lay.r + static_cast<size_t>(z) * p.lay.sz_r, SR, V * 256);
+      bulk_commit();
     }
   }
   LETHE_PHASE("epi3");
-  if (tid == 0) bulk_wait_all();
+  if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
   LETHE_PHASE_DUMP();
@@ -458,7 +471,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
       for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(og + jb * 32 + 8 * i) = pack8_bf16(d + 8 * i);
     }
   }
-  if (tid == 0) bulk_wait_all();
+  if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, V);

@@ -118,6 +118,8 @@ scan_kernel(const Problem p) {
     const float* ADg = reinterpret_cast<const float*>(p.saved + p.lay.ad);
     unsigned char* Xg = ADJOINT ? p.scratch + p.lay.dh : p.saved + p.lay.hc;
     const size_t szx = p.lay.sz_hc;
+    // R / Rb records are [V / 16 column blocks][128 rows][16 columns]: this CTA's block, this thread's row
+    const size_t rofs = (static_cast<size_t>(blockIdx.x) * kK + tid) * kVs;
 
     float x[kVs];
     {
@@ -127,7 +129,7 @@ scan_kernel(const Problem p) {
     }
     uint4 rnext[2];
     {
-      const __half* r = Rg + ((static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid) * V + v0;
+      const __half* r = Rg + (static_cast<size_t>(bh) * NT + chunk_of(0)) * kK * V + rofs;
       rnext[0] = *reinterpret_cast<const uint4*>(r);
       rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
     }
@@ -162,7 +164,7 @@ scan_kernel(const Problem p) {
       ST(2)
       if (it + 1 < NT) {
         const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
-        const __half* r = Rg + (zn * kK + tid) * V + v0;
+        const __half* r = Rg + zn * kK * V + rofs;
         rnext[0] = *reinterpret_cast<const uint4*>(r);
         rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
         a_next = ADg[zn * kK + tid];

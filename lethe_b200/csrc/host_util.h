@@ -69,4 +69,9 @@ inline int make_tmap_16bit(CUtensorMap* map, const void* ptr, int rank, const ui
   return r == CUDA_SUCCESS ? kOk : kErrDriver;
 }
 
+// Tensor maps of the token-major gradient outputs that leave by tensor-map stores.
+struct OutMaps {
+  CUtensorMap dq, dk, dv;
+};
+
 }  // namespace lg

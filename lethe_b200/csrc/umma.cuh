@@ -126,10 +126,19 @@ __device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t by
                "r"(smem_u32(src)), "r"(bytes)
                : "memory");
 }
+// Tensor-map tiled store of one box from shared memory (joins this thread's bulk group).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+      "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All of this thread's bulk stores have finished reading shared memory and writing global memory.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// ... have finished reading shared memory (the source may be overwritten).
+// ... have finished reading shared memory: the source may be overwritten, or the CTA may exit (the
+// global writes complete on their own and are visible when the kernel ends).
 __device__ __forceinline__ void bulk_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }

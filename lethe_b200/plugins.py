@@ -108,7 +108,9 @@ def k1_fn(q: Tensor, k: Tensor, w: Tensor, g2: Tensor, g_last: Tensor, do: Tenso
     Z, sz, off, sz2, off2 = _layout(B, H, L, V, gate)
     _record_view(buf.saved, off["p"], sz["p"], Z, torch.float16).copy_(to_image(P.half()).reshape(Z, -1))
     _record_view(buf.saved, off["ad"], sz["ad"], Z, f32).copy_(a.reshape(Z, K))
-    _record_view(buf.scratch, off2["rb"], sz2["rb"], Z, torch.float16).copy_(Rb.half().reshape(Z, -1))
+    # the scan reads Rb as V / 16 column blocks of [128 rows][16 columns]
+    rb_img = Rb.half().reshape(Z, K, V // 16, 16).transpose(1, 2).reshape(Z, -1)
+    _record_view(buf.scratch, off2["rb"], sz2["rb"], Z, torch.float16).copy_(rb_img)
     dummy16 = torch.zeros(B, L, H, K, dtype=torch.bfloat16, device=dev)
     dummyv = torch.zeros(B, L, H, V, dtype=torch.bfloat16, device=dev)
     gdummy = torch.zeros((B, L, H, K) if cw else (B, L, H), dtype=f32, device=dev)

@@ -8,7 +8,7 @@ from lethe_b200 import ops
 from lethe_b200.synth import make_inputs
 from oracle.gdn_oracle import chunk_backward, chunk_forward, scale_rel
 
-from .wsview import layout, records, report, unswizzle
+from .wsview import layout, records, report, rrecords, unswizzle
 
 pytestmark = pytest.mark.gpu
 
@@ -38,7 +38,7 @@ def test_backward_records(V, delta, mild, gate):
     NT = L // 64
     shp = (B, H, NT)
     errs = {}
-    errs["Rb"] = scale_rel(records(scratch, off2["rb"], sz2["rb"], Z).reshape(*shp, 128, V).double(), it["Rb"])
+    errs["Rb"] = scale_rel(rrecords(scratch, off2["rb"], sz2["rb"], Z, V).reshape(*shp, 128, V).double(), it["Rb"])
     errs["dh"] = scale_rel(unswizzle(records(scratch, off2["dh"], sz2["dh"], Z), 128, V).reshape(*shp, 128, V).double(),
                            it["dh"])
     if delta:

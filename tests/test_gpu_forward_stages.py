@@ -9,7 +9,7 @@ from lethe_b200 import ops
 from lethe_b200.synth import make_inputs
 from oracle.gdn_oracle import chunk_forward, scale_rel
 
-from .wsview import layout, records, report, unswizzle
+from .wsview import layout, records, rrecords, report, unswizzle
 
 pytestmark = pytest.mark.gpu
 
@@ -44,7 +44,7 @@ def test_forward_records(V, delta, mild, gate):
     # the chunk decay exp(G_last) underflows fp32 under the strong gate draw: compare absolutely
     ad = records(saved, off["ad"], sz["ad"], Z, torch.float32).reshape(*shp, 128).double()
     errs["ad"] = float((ad - st.a).abs().max())
-    errs["R"] = scale_rel(records(saved, off["r"], sz["r"], Z).reshape(*shp, 128, V).double(), st.R)
+    errs["R"] = scale_rel(rrecords(saved, off["r"], sz["r"], Z, V).reshape(*shp, 128, V).double(), st.R)
     errs["h"] = scale_rel(unswizzle(records(saved, off["hc"], sz["hc"], Z + B * H), 128, V)
                           .reshape(B, H, NT + 1, 128, V).double(), st.h)
     errs["vn"] = scale_rel(unswizzle(records(saved, off["vn"], sz["vn"], Z), 64, V).reshape(*shp, 64, V).double(),

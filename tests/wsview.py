@@ -44,6 +44,13 @@ def records(buf: torch.Tensor, off: int, size: int, Z: int, dtype=torch.float16)
     return raw.view(dtype).reshape(Z, -1)
 
 
+def rrecords(buf: torch.Tensor, off: int, size: int, Z: int, V: int) -> torch.Tensor:
+    """The scan-input records R / Rb: stored as V / 16 column blocks of [128 rows][16 columns]; returned as
+    [Z, 128, V]."""
+    blk = records(buf, off, size, Z).reshape(Z, V // 16, 128, 16)
+    return blk.permute(0, 2, 1, 3).reshape(Z, 128, V)
+
+
 def report(label: str, errs: dict) -> None:
     """Print the per-tensor errors of a parity case and append them to a log next to the run."""
     line = label + " " + " ".join(f"{k}={v:.2e}" for k, v in errs.items())
