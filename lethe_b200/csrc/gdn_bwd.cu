@@ -48,6 +48,15 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u) + (CW ? 32768u : 0u));
+    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
+    for (int a = 0; a < 2; ++a) tma_load_4d(QG + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(DO + a * 8192, &mdo, bar_load, a * 64, h, c * kC, b);
+    if (DELTA) {
+      bulk_g2s(Wt, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, 16384, bar_load);
+      bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    }
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, 256);
@@ -59,16 +68,6 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u) + (CW ? 32768u : 0u));
-    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
-    for (int a = 0; a < 2; ++a) tma_load_4d(QG + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
-    for (int a = 0; a < V / 64; ++a) tma_load_4d(DO + a * 8192, &mdo, bar_load, a * 64, h, c * kC, b);
-    if (DELTA) {
-      bulk_g2s(Wt, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, 16384, bar_load);
-      bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-    }
-  }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
   __syncthreads();
@@ -193,6 +192,19 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    }
+    for (int a = 0; a < V / 64; ++a) {
+      tma_load_4d(DD + a * 16384, &mdo, bar_load, a * 64, h, c * kC, b);
+      bulk_g2s(VNt + a * 16384, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn + a * 8192, 8192, bar_load);
+    }
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
+    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, 512);
@@ -208,21 +220,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   const uint32_t tmem = cs->tmem_slot;
   const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
 
-  const unsigned char* dh_g = p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
-    for (int a = 0; a < 2; ++a) {
-      tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-      tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
-    }
-    for (int a = 0; a < V / 64; ++a) {
-      tma_load_4d(DD + a * 16384, &mdo, bar_load, a * 64, h, c * kC, b);
-      bulk_g2s(VNt + a * 16384, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn + a * 8192, 8192, bar_load);
-    }
-    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-    bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
-    bulk_g2s(DHt, dh_g, V * 256, bar_load);
-  }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
   __syncthreads();

@@ -51,6 +51,16 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     mbar_init(bar_mma, 1);
     mbar_init(bar_dkb, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(T1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
+               bar_load);
+    }
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, kCols);
@@ -69,17 +79,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
   const uint32_t R0 = tmem, R1 = tmem + 128, R2 = tmem + 192;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u);
-    for (int a = 0; a < 2; ++a) {
-      tma_load_4d(T1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
-               bar_load);
-    }
-    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
-    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
-  }
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) {
     Gs[tid] = G;
@@ -192,12 +191,16 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     tmem_ld32(R0 + lane_base + 32, kk + 32);
     tmem_ld_wait();
     const float Gr = Gs[r];
+    const bool upper = (warp & 1) != 0;   // rows 0-31 (warp 0) have nothing right of column 31
 #pragma unroll
     for (int s = 0; s < 64; ++s) {
-      const float x = (s < r) ? dm[s] * __expf(Gr - Gs[s]) : 0.f;      // dM * ratio, strictly lower
-      dbeta_m += x * kk[s];
-      const float dkk = x * bval;
-      rowsum_e += dkk * kk[s];
+      float dkk = 0.f;
+      if (s < 32 || upper) {
+        const float x = (s < r) ? dm[s] * __expf(Gr - Gs[s]) : 0.f;      // dM * ratio, strictly lower
+        dbeta_m += x * kk[s];
+        dkk = x * bval;
+        rowsum_e += dkk * kk[s];
+      }
       DK[r * 64 + (s ^ (r & 31))] = dkk;
     }
   }

@@ -55,6 +55,13 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    mbar_expect_tx(bar_load, 32768u + V * 128u);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(KQ + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(KQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    }
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, 256);
@@ -72,14 +79,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
 
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 32768u + V * 128u);
-    for (int a = 0; a < 2; ++a) {
-      tma_load_4d(KQ + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-      tma_load_4d(KQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
-    }
-    for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
-  }
 
   // ---- gate: cumulative log decay of the chunk
   const float G = chunk_cumsum(gval, tid, tmp);
@@ -150,23 +149,31 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tmem_ld_wait();
     if (tid < 64) {
       if (DELTA) {
+        // rows 0-31 (warp 0) have nothing right of column 31: the triangle is cut per warp
         const int r = tid;
+        const bool upper = (warp & 1) != 0;
 #pragma unroll
         for (int s = 0; s < 64; ++s) {
-          const float m = (s < r) ? bval * __expf(G - Gs[s]) * d[s] : 0.f;
+          float m = 0.f;
+          if (s < 32 || upper) m = (s < r) ? bval * __expf(G - Gs[s]) * d[s] : 0.f;
           Msm[r * kMs + s] = m;
         }
       }
     } else {
       const int r = tid - 64;
       const float Gr = Gs[r];
+      const bool upper = (warp & 1) != 0;
 #pragma unroll
       for (int s8 = 0; s8 < 8; ++s8) {
         float a[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int s = s8 * 8 + i;
-          a[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * d[s] : 0.f;
+        for (int i = 0; i < 8; ++i) a[i] = 0.f;
+        if (s8 < 4 || upper) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int s = s8 * 8 + i;
+            a[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * d[s] : 0.f;
+          }
         }
         tile_st_chunk(TA, 64 + r, s8, 128, pack8_f16(a));
       }
@@ -350,6 +357,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   const int tid = threadIdx.x, warp = tid >> 5;
   const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
+  const unsigned char* Ug = p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u;
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
 
@@ -358,6 +366,17 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + V * 256u + 16384u + (CW ? 32768u : 0u));
+    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(WQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
+      if (DELTA)
+        bulk_g2s(WQ + a * 16384, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w + a * 8192, 8192, bar_load);
+    }
+    if (!DELTA) bulk_g2s(VN, Ug, V * 128, bar_load);   // v_new = u = v
+    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, V);
@@ -371,19 +390,6 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
 
-  const unsigned char* Ug = p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + V * 256u + 16384u + (CW ? 32768u : 0u));
-    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
-    for (int a = 0; a < 2; ++a) {
-      tma_load_4d(WQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
-      if (DELTA)
-        bulk_g2s(WQ + a * 16384, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w + a * 8192, 8192, bar_load);
-    }
-    if (!DELTA) bulk_g2s(VN, Ug, V * 128, bar_load);   // v_new = u = v
-    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
-    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-  }
   // u row of this thread (threads 0-63), kept packed
   uint4 upk[V / 8];
   if (DELTA && tid < 64) {
