@@ -223,6 +223,58 @@ __device__ __forceinline__ uint32_t rrec_off(int row, int col8) {
   return static_cast<uint32_t>((col8 >> 1) * 4096 + row * 32 + (col8 & 1) * 16);
 }
 
+// T = (I + M)^-1 for a strictly lower-triangular 64 x 64 M (fp32, row stride MS floats, zeros on and
+// above the diagonal), by forward substitution: thread j (0..63) owns column j and works through four
+// blocks of 16 rows.  A block first collects what the finished blocks above it contribute (sixteen
+// independent sums, T read back from `Tsm`, [48][64] fp32), then resolves its own 16 rows in registers.
+// T is written as fp16 into rows 0-63 of the 128-row SW128 tile `TA`.  No synchronisation inside: a
+// thread reads back only what it wrote itself.
+template <int MS>
+__device__ __forceinline__ void unit_lower_inverse64(const float* Msm, float* Tsm, unsigned char* TA, int j) {
+  const int jb = j >> 4;
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    float col[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) col[r] = (blk * 16 + r == j) ? 1.f : 0.f;
+    if (blk >= jb) {
+      const float* Mb = Msm + blk * 16 * MS;
+      for (int s = jb * 16; s < blk * 16; s += 8) {
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = Tsm[(s + i) * 64 + j];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          const float4 m0 = *reinterpret_cast<const float4*>(Mb + r * MS + s);
+          const float4 m1 = *reinterpret_cast<const float4*>(Mb + r * MS + s + 4);
+          col[r] -= ((m0.x * t[0] + m0.y * t[1]) + (m0.z * t[2] + m0.w * t[3])) +
+                    ((m1.x * t[4] + m1.y * t[5]) + (m1.z * t[6] + m1.w * t[7]));
+        }
+      }
+#pragma unroll
+      for (int r = 1; r < 16; ++r) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int q = 0; q < (r + 3) / 4; ++q) {
+          const float4 m = *reinterpret_cast<const float4*>(Mb + r * MS + blk * 16 + 4 * q);
+          a0 += m.x * col[4 * q];
+          if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
+          if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
+          if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
+        }
+        col[r] -= a0 + a1;
+      }
+      if (blk < 3) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) Tsm[(blk * 16 + r) * 64 + j] = col[r];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r)
+      *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(col[r]);
+  }
+}
+
 // Deterministic sum over the 128 threads of a CTA (fixed tree).  `red` is a shared float[4].
 __device__ __forceinline__ float cta_sum128(float x, int tid, float* red) {
 #pragma unroll

@@ -25,6 +25,12 @@ namespace lg {
 // "thread i reads row i" are both free of bank conflicts
 __device__ __forceinline__ int exi(int row, int col) { return gidx(row, col); }
 
+// fp32 [64][128] records passed between the backward kernels (dq / dk / dG parts): element (i, d) of
+// a record lives at ridx(i, d) - the 16-byte pieces of a row are XOR-ed with the low row bits, so that
+// a shared-memory image of the record takes row-wise 16-byte stores and column-wise reads without
+// bank conflicts, and global accesses by 128 threads along d stay coalesced.
+__device__ __forceinline__ int ridx(int i, int d) { return i * kK + (d ^ ((i & 7) << 2)); }
+
 __device__ __forceinline__ void ld8(const float* p, float* v) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
@@ -129,12 +135,13 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("built");
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(cA, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
-    issue_product(cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 1u);
-    issue_product(cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 64, false}, 64, V, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, cA, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
+    issue_product_led(leader, cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 1u);
+    issue_product_led(leader, cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 64, false}, 64, V, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 602);
   LETHE_PHASE("g1");
@@ -172,11 +179,12 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   sync_for_issue();
   LETHE_PHASE("epi1");
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
-    issue_product(cD, Tile{smem_u32(VNt), 64, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
+    issue_product_led(leader, cD, Tile{smem_u32(VNt), 64, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 603);
   LETHE_PHASE("g2");
@@ -184,6 +192,12 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
   float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
   float* dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
+  // With d_v = 128 three dead operand tiles hold the three records as images that leave by bulk
+  // stores; with d_v = 64 there is no room and the rows go to global memory directly.
+  constexpr bool kStage = (V == 128);
+  float* dqp_w = kStage ? reinterpret_cast<float*>(DD) : dqp_g;
+  float* dkb_w = kStage ? reinterpret_cast<float*>(TAt) : dkb_g;     // [T | A] and v_new, contiguous
+  float* dgb_w = kStage ? reinterpret_cast<float*>(DHt) : dgb_g;
   const int tq = tid & 127, jb0 = 2 * (tid >> 7);   // threads 128-255 take the upper 64 columns
   if (tq < 64) {
     const int r = tq;
@@ -212,12 +226,12 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
           o3[e] = o1[e] * qv[e] - dde;                       // part of dG
         }
         const int c0 = jb * 32 + i * 8;
-        *reinterpret_cast<float4*>(dqp_g + r * kK + c0) = make_float4(o1[0], o1[1], o1[2], o1[3]);
-        *reinterpret_cast<float4*>(dqp_g + r * kK + c0 + 4) = make_float4(o1[4], o1[5], o1[6], o1[7]);
-        *reinterpret_cast<float4*>(dkb_g + r * kK + c0) = make_float4(o2[0], o2[1], o2[2], o2[3]);
-        *reinterpret_cast<float4*>(dkb_g + r * kK + c0 + 4) = make_float4(o2[4], o2[5], o2[6], o2[7]);
-        *reinterpret_cast<float4*>(dgb_g + r * kK + c0) = make_float4(o3[0], o3[1], o3[2], o3[3]);
-        *reinterpret_cast<float4*>(dgb_g + r * kK + c0 + 4) = make_float4(o3[4], o3[5], o3[6], o3[7]);
+        *reinterpret_cast<float4*>(dqp_w + ridx(r, c0)) = make_float4(o1[0], o1[1], o1[2], o1[3]);
+        *reinterpret_cast<float4*>(dqp_w + ridx(r, c0 + 4)) = make_float4(o1[4], o1[5], o1[6], o1[7]);
+        *reinterpret_cast<float4*>(dkb_w + ridx(r, c0)) = make_float4(o2[0], o2[1], o2[2], o2[3]);
+        *reinterpret_cast<float4*>(dkb_w + ridx(r, c0 + 4)) = make_float4(o2[4], o2[5], o2[6], o2[7]);
+        *reinterpret_cast<float4*>(dgb_w + ridx(r, c0)) = make_float4(o3[0], o3[1], o3[2], o3[3]);
+        *reinterpret_cast<float4*>(dgb_w + ridx(r, c0 + 4)) = make_float4(o3[4], o3[5], o3[6], o3[7]);
       }
     }
   } else if (DELTA) {
@@ -240,7 +254,18 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   if (tid < 128) {  // last row of the chunk: exp(G_last) <dh, h> + sum_i dde[i, d]   (thread d, column d)
     float acc = hh[tid];
     for (int i = 0; i < 64; ++i) acc += DDE[exi(i, tid)];
-    dgb_g[63 * kK + tid] += acc;
+    dgb_w[ridx(63, tid)] += acc;
+  }
+  if (kStage) {
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      bulk_s2g(dqp_g, dqp_w, 32768);
+      bulk_s2g(dkb_g, dkb_w, 32768);
+      bulk_s2g(dgb_g, dgb_w, 32768);
+      bulk_commit();
+      bulk_wait_read();
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -330,12 +355,13 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   sync_for_issue();
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(c1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(BVt), 64, false}, 64, V, 0u);
-    issue_product(c1, Tile{smem_u32(DWt), 64, false}, Tile{smem_u32(KB) + 8192, 128, false}, 64, 128, 1u);
-    issue_product(c4, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V + 128, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, c1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(BVt), 64, false}, 64, V, 0u);
+    issue_product_led(leader, c1, Tile{smem_u32(DWt), 64, false}, Tile{smem_u32(KB) + 8192, 128, false}, 64, 128, 1u);
+    issue_product_led(leader, c4, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V + 128, 64, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 612);
   if (tid < 64) {
@@ -347,10 +373,11 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(DTt, tid, s8, 64, pack8_f16(d + 8 * s8));
   }
   sync_for_issue();
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(c2, Tile{smem_u32(DTt), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, c2, Tile{smem_u32(DTt), 64, false}, Tile{smem_u32(TAt), 128, false}, 64, 64, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 613);
   if (tid < 64) {
@@ -362,10 +389,11 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(XT, tid, s8, 64, pack8_f16(d + 8 * s8));
   }
   sync_for_issue();
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(c3, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(XT), 64, true}, 64, 64, 0u, true);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, c3, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(XT), 64, true}, 64, 64, 0u, true);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 614);
   if (tid < 64) {
@@ -407,7 +435,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     // d(beta gamma k) = T^T dw: fp32 -> record; its direct part of the erase-gate gradient,
     // sum_d d(beta gamma k) gamma k, is closed here
     float pq = 0.f;
-    float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4)) + r * kK;
+    float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
 #pragma unroll 1
     for (int jb = 0; jb < 4; ++jb) {
       float d[32];
@@ -422,7 +450,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<float4*>(dqp_g + jb * 32 + 4 * i) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+        *reinterpret_cast<float4*>(dqp_g + ridx(r, jb * 32 + 4 * i)) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
     }
     if (p.dbeta_w) {
       p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
@@ -544,20 +572,21 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   sync_for_issue();
   LETHE_PHASE("built");
   uint32_t ph = 0;
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
+    const uint32_t leader = elect_leader();
     for (int I = 1; I < 4; ++I) {
       const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
-      issue_product(tmem, Tile{smem_u32(MA + (I - 1) * 8192), 64, false},
+      issue_product_led(leader, tmem, Tile{smem_u32(MA + (I - 1) * 8192), 64, false},
                     Tile{smem_u32(KR) + off * 128, 128, true}, 128, 16 * I, I > 1 ? 1u : 0u);
     }
     for (int J = 0; J < 3; ++J) {
       const int off = (J == 0) ? 0 : (J == 1 ? 48 : 80);
       const int r0 = 16 * (J + 1);
-      issue_product(tmem + 128, Tile{smem_u32(MB + J * 8192) - 8192 + r0 * 128, 64, true},
+      issue_product_led(leader, tmem + 128, Tile{smem_u32(MB + J * 8192) - 8192 + r0 * 128, 64, true},
                     Tile{smem_u32(XE) + off * 128, 128, true}, 128, 64 - r0, J > 0 ? 1u : 0u);
     }
-    umma_commit(bar_mma);
+    umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 622);
   __syncthreads();          // products done for every thread: KR / XE become the exchange tiles
@@ -656,9 +685,9 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       float part8[8], dgb8[8], dkb8[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        part8[j] = dqp_g[(i0 + j) * kK + d];
-        dgb8[j] = dgb_g[(i0 + j) * kK + d];
-        dkb8[j] = dkb_g[(i0 + j) * kK + d];
+        part8[j] = dqp_g[ridx(i0 + j, d)];
+        dgb8[j] = dgb_g[ridx(i0 + j, d)];
+        dkb8[j] = dkb_g[ridx(i0 + j, d)];
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -680,9 +709,9 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
           dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
         }
         if (kFinalK) p.dk[tok] = __float2bfloat16_rn(dk);
-        else dkb_g[i * kK + d] = dk;
+        else dkb_g[ridx(i, d)] = dk;
         if (FINAL_G) EX1[exi(i, d)] = dG;                // closed below by the reverse cumulative sum
-        else dgb_g[i * kK + d] = dG;
+        else dgb_g[ridx(i, d)] = dG;
       }
     }
   }

@@ -139,12 +139,13 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   LETHE_PHASE("built");
   // ---- off-diagonal blocks on the tensor cores: columns [0,16) I=1, [16,48) I=2, [48,96) I=3
   uint32_t ph = 0;
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem + 0, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR), 128, false}, 16, 128, 0u);
-    issue_product(tmem + 16, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 16 * 128, 128, false}, 32, 128, 0u);
-    issue_product(tmem + 48, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 48 * 128, 128, false}, 48, 128, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem + 0, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR), 128, false}, 16, 128, 0u);
+    issue_product_led(leader, tmem + 16, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 16 * 128, 128, false}, 32, 128, 0u);
+    issue_product_led(leader, tmem + 48, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 48 * 128, 128, false}, 48, 128, 0u);
+    umma_commit_led(leader, bar_mma);
   }
   __syncwarp();
   // ---- diagonal blocks, exact: pair (i, s) of one block, s <= i
@@ -226,43 +227,27 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   __syncthreads();
 
   LETHE_PHASE("epi1");
-  // ---- T = (I + M)^-1 (fp32, one column per thread)
+  // ---- T = (I + M)^-1 (fp32, CUDA cores)
   if (tid < 64) {
-    float col[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) col[i] = 0.f;
     if (DELTA) {
+      unit_lower_inverse64<kMsC>(Msm, Msm + 64 * kMsC, TA, tid);
+    } else {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        // four partial sums: the products of one row do not wait on one another
-        float a0 = (i == tid) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-        for (int s4 = 0; s4 < (i + 3) / 4; ++s4) {
-          const float4 m = *reinterpret_cast<const float4*>(&Msm[i * kMsC + 4 * s4]);
-          a0 -= m.x * col[4 * s4];
-          if (4 * s4 + 1 < i) a1 -= m.y * col[4 * s4 + 1];
-          if (4 * s4 + 2 < i) a2 -= m.z * col[4 * s4 + 2];
-          if (4 * s4 + 3 < i) a3 -= m.w * col[4 * s4 + 3];
-        }
-        col[i] = (a0 + a1) + (a2 + a3);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      const float t = DELTA ? col[i] : ((i == tid) ? 1.f : 0.f);
-      *reinterpret_cast<__half*>(TA + sw128_off(i, tid, 128)) = __float2half_rn(t);
+      for (int i = 0; i < 64; ++i)
+        *reinterpret_cast<__half*>(TA + sw128_off(i, tid, 128)) = __float2half_rn((i == tid) ? 1.f : 0.f);
     }
   }
   sync_for_issue();
 
   LETHE_PHASE("inverse");
   if (DELTA) {
-    if (tid == 0) {
+    if (warp == 0) {
       tc_fence_after();
-      issue_product(tmem, Tile{smem_u32(TA), 128, false}, Tile{smem_u32(BGK), 64, true}, 128 + V, 64, 0u);
-      umma_commit(bar_mma);
-      bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
-      bulk_commit();
+      const uint32_t leader = elect_leader();
+      issue_product_led(leader, tmem, Tile{smem_u32(TA), 128, false}, Tile{smem_u32(BGK), 64, true}, 128 + V, 64, 0u);
+      umma_commit_led(leader, bar_mma);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
+      if (tid == 0) bulk_commit();
     }
     wait_products(bar_mma, ph, ctl, 503);
     if (tid < 64) {
@@ -283,17 +268,18 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
 
   LETHE_PHASE("wu");
   constexpr int N3 = DELTA ? 128 + V : V;
-  if (tid == 0) {
+  if (warp == 0) {
     tc_fence_after();
-    issue_product(tmem, Tile{smem_u32(KD), 64, true}, Tile{smem_u32(DELTA ? WU : BV), 64, true}, N3, 64, 0u);
-    umma_commit(bar_mma);
+    const uint32_t leader = elect_leader();
+    issue_product_led(leader, tmem, Tile{smem_u32(KD), 64, true}, Tile{smem_u32(DELTA ? WU : BV), 64, true}, N3, 64, 0u);
+    umma_commit_led(leader, bar_mma);
     if (DELTA) {
-      bulk_s2g(p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, WU, 16384);
-      bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, WU + 16384, V * 128);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, WU, 16384);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, WU + 16384, V * 128);
     } else {
-      bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, BV, V * 128);
+      if (tid == 0) bulk_s2g(p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u, BV, V * 128);
     }
-    bulk_commit();
+    if (tid == 0) bulk_commit();
   }
   wait_products(bar_mma, ph, ctl, 504);
   {

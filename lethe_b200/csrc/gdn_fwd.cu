@@ -183,57 +183,14 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   __syncthreads();
   LETHE_PHASE("epi1");
 
-  // ---- T = (I + M)^-1 by forward substitution, one column per thread, in four blocks of 16 rows.
-  // A block first collects what the finished blocks above it contribute (sixteen independent sums,
-  // T read back from shared memory), then resolves its own 16 rows in registers.
+  // ---- T = (I + M)^-1 (fp32, CUDA cores)
   if (tid < 64) {
-    const int j = tid, jb = j >> 4;
     if (DELTA) {
-#pragma unroll 1
-      for (int blk = 0; blk < 4; ++blk) {
-        float col[16];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) col[r] = (blk * 16 + r == j) ? 1.f : 0.f;
-        if (blk >= jb) {
-          const float* Mb = Msm + blk * 16 * kMs;
-          for (int s = jb * 16; s < blk * 16; s += 8) {
-            float t[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) t[i] = Tsm[(s + i) * 64 + j];
-#pragma unroll
-            for (int r = 0; r < 16; ++r) {
-              const float4 m0 = *reinterpret_cast<const float4*>(Mb + r * kMs + s);
-              const float4 m1 = *reinterpret_cast<const float4*>(Mb + r * kMs + s + 4);
-              col[r] -= ((m0.x * t[0] + m0.y * t[1]) + (m0.z * t[2] + m0.w * t[3])) +
-                        ((m1.x * t[4] + m1.y * t[5]) + (m1.z * t[6] + m1.w * t[7]));
-            }
-          }
-#pragma unroll
-          for (int r = 1; r < 16; ++r) {
-            float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-            for (int q = 0; q < (r + 3) / 4; ++q) {
-              const float4 m = *reinterpret_cast<const float4*>(Mb + r * kMs + blk * 16 + 4 * q);
-              a0 += m.x * col[4 * q];
-              if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
-              if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
-              if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
-            }
-            col[r] -= a0 + a1;
-          }
-          if (blk < 3) {
-#pragma unroll
-            for (int r = 0; r < 16; ++r) Tsm[(blk * 16 + r) * 64 + j] = col[r];
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < 16; ++r)
-          *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(col[r]);
-      }
+      unit_lower_inverse64<kMs>(Msm, Tsm, TA, tid);
     } else {
 #pragma unroll
       for (int i = 0; i < 64; ++i)
-        *reinterpret_cast<__half*>(TA + sw128_off(i, j, 128)) = __float2half_rn((i == j) ? 1.f : 0.f);
+        *reinterpret_cast<__half*>(TA + sw128_off(i, tid, 128)) = __float2half_rn((i == tid) ? 1.f : 0.f);
     }
   }
   fence_proxy_async();
