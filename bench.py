@@ -135,6 +135,25 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 
 
 # ------------------------------------------------------------------------------------------------
+# DRAM traffic per chunk (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture / chunks of that
+# launch), from the captures summarised under profiles/ (2048-chunk workloads, records larger than L2;
+# every kernel's traffic grows in proportion to its chunks).  Keyed by (kernel, gate, d_v, delta); the
+# channel-wise "stageb" and "wy" are two launches each, summed.  Absent combinations report null.
+NCU_DRAM_BYTES_PER_CHUNK = {
+    ("stageb", "scalar", 64, True): (201.9e6 + 111.8e6) / 2048,
+    ("prepare", "scalar", 64, True): (85.0e6 + 128.3e6) / 2048,
+    ("wy", "scalar", 64, True): (203.0e6 + 34.6e6) / 2048,
+    ("scan_bwd", "scalar", 64, True): (101.7e6 + 13.9e6) / 2048,
+    ("prepare", "channel", 128, True): (168.4e6 + 248.4e6) / 2048,
+}
+
+
+def measured_traffic(kernel: str, gate: str, V: int, delta: bool, Z: int):
+    per = NCU_DRAM_BYTES_PER_CHUNK.get((kernel, gate, V, delta))
+    return None if per is None else int(per * Z)
+
+
+# ------------------------------------------------------------------------------------------------
 def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool, cw: bool = False) -> int:
     """Bytes one launch of `kernel` must move: each input tile and each record read once, each
     result written once (Z chunks, 64 tokens each; K = 128).  With the channel-wise gate every kernel
@@ -317,10 +336,37 @@ def main():
                    args.steps, 3)
     ops.check_status(buf.status)
 
-    # ---- end to end through the public op, host buffers in, host buffers out
-    outs_host = {}
+    # ---- end to end through the public host API: pinned host buffers in, pinned host buffers out, every
+    # step's copies inside the timed region.  Consecutive steps overlap their copy-in, kernels and
+    # copy-out on three streams (two sets of device buffers, together larger than L2; the L2 flush
+    # runs on the compute stream inside the timed region).
+    from lethe_b200.host import HostPipeline
+    pipe = HostPipeline(B, L, H, K, V, gate=gate_code, delta=delta, has_h0="h0" in host, scale=scale)
+    pipe.pre_run = flush.zero_
+    host_in = {n: host[n] for n in pipe.slots[0].inp}
+    outs_host = {n: torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for n, t in pipe.slots[0].outputs().items()}
 
-    def e2e_step():
+    def e2e_run(steps):
+        for _ in range(steps):
+            pipe.submit(host_in, outs_host)
+        pipe.join()
+
+    e2e_steps = max(6, args.steps)
+    e2e_run(3)
+    pipe.drain()
+    barrier()
+    ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ea.record()
+    e2e_run(e2e_steps)
+    eb.record()
+    barrier()
+    pipe.drain()
+    e2e_ms = ea.elapsed_time(eb) / e2e_steps
+
+    # one step alone through the autograd op (copy in, forward, backward, copy out, nothing overlapped)
+    single_host = {}
+
+    def e2e_single():
         leaves = {}
         for n in ("q", "k", "v", "g", "beta", "h0"):
             leaves[n] = host[n].to(dev, non_blocking=True).requires_grad_(True) if n in host else None
@@ -331,11 +377,11 @@ def main():
         grads = torch.autograd.grad(o, [leaves[n] for n in names], do_d)
         res = [("o", o.detach()), ("hT", hT.detach())] + [("d" + n, t) for n, t in zip(names, grads)]
         for n, t in res:
-            if n not in outs_host:
-                outs_host[n] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
-            outs_host[n].copy_(t, non_blocking=True)
+            if n not in single_host:
+                single_host[n] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            single_host[n].copy_(t, non_blocking=True)
 
-    e2e_ms = timed(e2e_step, max(3, args.steps // 2), 3)
+    e2e_single_ms = timed(e2e_single, 3, 3)
     clocks = sampler.stop()
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = sum(t.numel() * t.element_size() for t in outs_host.values())
@@ -359,11 +405,15 @@ def main():
             "data": "synthetic", "config": config,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "kernel_ms": kern,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "lethe_b200.host.HostPipeline (copy-in, kernels and copy-out of consecutive steps "
+                           "overlap)", "steps": e2e_steps,
+                    "single_step_ms": e2e_single_ms, "single_step_api": "lethe_b200.ops.gdn_chunk + autograd"},
             "gpu_launches": args.steps * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
             "clocks": clocks,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                         "frac": achieved / hbm, "peak_source": which, "traffic": None,
+                         "frac": achieved / hbm, "peak_source": which,
+                         "traffic": measured_traffic(top, gate, V, delta, Z),
                          "launch_ms": kern[top], "algorithmic_bytes": ab},
         }
         if world == 1 and not args.no_cpu_baseline:
