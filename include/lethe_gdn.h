@@ -111,6 +111,28 @@ int lethe_gdn_backward(const LetheGdnArgs* args, void* cuda_stream);
 int lethe_gdn_forward_static(const LetheGdnArgs* args, void* cuda_stream);
 size_t lethe_gdn_forward_static_capacity(void);
 
+/* One token of the same recurrence for generation (the body of the reference's token loop,
+ * src/lethe/kernels/references/gdn_backward.py:45-53; the reference has no device kernel for it):
+ *   S <- S * exp(g);  v_new = beta (v - k^T S);  S <- S + k v_new^T;  o = (scale q)^T S
+ * for every (batch, head) pair.  q, k: bf16 [B, H, K]; v, o: bf16 [B, H, V]; g: fp32 [B, H] (scalar
+ * gate) or [B, H, K] (channel-wise), unused for LETHE_GATE_NONE; beta: fp32 [B, H], required when
+ * delta != 0; state: fp32 [B, H, K, V], updated in place (the h_T of lethe_gdn_forward continues a
+ * prompt).  K = 128, V in {64, 128}.  No workspace, no status word (the kernel waits on nothing). */
+typedef struct LetheGdnDecodeArgs {
+  int32_t B, H, K, V;
+  int32_t gate;   /* LETHE_GATE_* */
+  int32_t delta;  /* 0: no delta term (v_new = v) */
+  float scale;
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* g;
+  const float* beta;
+  float* state;
+  void* o;
+} LetheGdnDecodeArgs;
+int lethe_gdn_decode_step(const LetheGdnDecodeArgs* args, void* cuda_stream);
+
 /* Text for a return code of the calls above or for a device status code. */
 const char* lethe_gdn_strerror(int code);
 

@@ -79,25 +79,6 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   return kOk;
 }
 
-// Makes the device that owns `ptr` current on the calling thread for the duration of a call and
-// binds its primary context.  A host framework may call from a worker thread that has never touched
-// CUDA (PyTorch's autograd thread when nothing else ran on it yet): without this the driver-level
-// tensor-map encoding fails with "invalid context".
-struct DeviceGuard {
-  int prev = -1, dev = -1;
-  bool ok = false;
-  explicit DeviceGuard(const void* ptr) {
-    cudaPointerAttributes at;
-    if (cudaGetDevice(&prev) != cudaSuccess) return;
-    dev = prev;
-    if (ptr && cudaPointerGetAttributes(&at, ptr) == cudaSuccess && at.type == cudaMemoryTypeDevice) dev = at.device;
-    ok = cudaSetDevice(dev) == cudaSuccess;
-  }
-  ~DeviceGuard() {
-    if (ok && prev >= 0 && prev != dev) cudaSetDevice(prev);
-  }
-};
-
 }  // namespace lg
 
 using namespace lg;

@@ -39,6 +39,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.lethe_gdn_forward_static.argtypes = [c_void_p, c_void_p]
     L.lethe_gdn_forward_static_capacity.restype = ctypes.c_size_t
     L.lethe_gdn_forward_static_capacity.argtypes = []
+    L.lethe_gdn_decode_step.restype = c_int
+    L.lethe_gdn_decode_step.argtypes = [c_void_p, c_void_p]
     L.lethe_gdn_strerror.restype = ctypes.c_char_p
     L.lethe_gdn_strerror.argtypes = [c_int]
     L.lethe_probe_umma.restype = c_int

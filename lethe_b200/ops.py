@@ -173,11 +173,22 @@ class _GdnChunk(torch.autograd.Function):
                 g32 = torch.nn.functional.pad(g32, (0, 64))
             if h32 is not None:
                 h32 = torch.nn.functional.pad(h32, (0, 0, 0, 64))
+        L = q.shape[1]
+        ctx.pad_l = (-L) % 64
+        if ctx.pad_l:
+            # The kernels work on chunks of 64 tokens.  Tokens appended with k = v = q = 0, g = 0 and
+            # beta = 0 leave the state untouched (decay 1, nothing erased, nothing written), so the
+            # result on the real tokens and the final state are exact.
+            def pad_tokens(t):
+                return None if t is None else torch.nn.functional.pad(t, (0, 0) * (t.dim() - 2) + (0, ctx.pad_l))
+            q16, k16, v16, g32, b32 = (pad_tokens(t) for t in (q16, k16, v16, g32, b32))
         o, hT, saved, status = gdn_forward_raw(q16, k16, v16, g32, b32, h32, scale)
         ctx.save_for_backward(q16, k16, v16, g32, b32, h32, saved, status)
         ctx.scale = scale
         if ctx.pad_k:
             hT = hT[:, :, :K].contiguous()
+        if ctx.pad_l:
+            o = o[:, :L]
         return o.to(v.dtype), hT
 
     @staticmethod
@@ -185,6 +196,8 @@ class _GdnChunk(torch.autograd.Function):
         q16, k16, v16, g32, b32, h32, saved, status = ctx.saved_tensors
         do16 = _prep16(do)
         dhT32 = _prep32(dhT)
+        if ctx.pad_l:
+            do16 = torch.nn.functional.pad(do16, (0, 0, 0, 0, 0, ctx.pad_l))
         if ctx.pad_k and dhT32 is not None:
             dhT32 = torch.nn.functional.pad(dhT32, (0, 0, 0, ctx.pad_k))
         dq, dk, dv, dg, dbeta, dh0, _ = gdn_backward_raw(q16, k16, v16, g32, b32, h32, do16, dhT32,
@@ -194,6 +207,11 @@ class _GdnChunk(torch.autograd.Function):
             dq, dk, dh0 = dq[..., :K], dk[..., :K], dh0[:, :, :K]
             if dg is not None and dg.dim() == 4:
                 dg = dg[..., :K]
+        if ctx.pad_l:
+            L = q16.shape[1] - ctx.pad_l
+            dq, dk, dv = dq[:, :L], dk[:, :L], dv[:, :L]
+            dg = None if dg is None else dg[:, :L]
+            dbeta = None if dbeta is None else dbeta[:, :L]
         dts = ctx.in_dtypes
         outs = [dq.to(dts[0]), dk.to(dts[1]), dv.to(dts[2]),
                 None if dg is None else dg.to(dts[3]),
@@ -209,13 +227,53 @@ def gdn_chunk(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | 
 
     ``g``: per-token log decay, ``[B,L,H]`` (scalar gate), ``[B,L,H,K]`` (channel-wise) or None.
     ``beta``: ``[B,L,H]`` (erase and write gate) or None for the variants without the delta term
-    (linear attention, GLA, SSD).  Gradients flow to q, k, v, g, beta and h0.
+    (linear attention, GLA, SSD).  Gradients flow to q, k, v, g, beta and h0.  ``L`` need not be a
+    multiple of the chunk length and d_k may be 64 or 128: both are met by exact zero padding.
     """
     if scale is None:
         scale = q.shape[-1] ** -0.5
     if use_qk_l2norm:
         q, k = _l2norm(q.float()).to(q.dtype), _l2norm(k.float()).to(k.dtype)
     return _GdnChunk.apply(q, k, v, g, beta, h0, float(scale))
+
+
+class _DecodeArgs(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("H", ctypes.c_int32), ("K", ctypes.c_int32), ("V", ctypes.c_int32),
+                ("gate", ctypes.c_int32), ("delta", ctypes.c_int32), ("scale", ctypes.c_float),
+                ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("g", ctypes.c_void_p), ("beta", ctypes.c_void_p), ("state", ctypes.c_void_p),
+                ("o", ctypes.c_void_p)]
+
+
+def gdn_decode_step(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | None, state: Tensor,
+                    *, scale: float | None = None) -> Tensor:
+    """One token of the recurrence for every (batch, head) pair, for generation: the body of the
+    reference's token loop (``src/lethe/kernels/references/gdn_backward.py:45-53``).
+
+    ``q, k [B,H,K]``, ``v [B,H,V]``; ``g [B,H]`` (scalar gate), ``[B,H,K]`` (channel-wise) or None;
+    ``beta [B,H]`` or None (no delta term); ``state [B,H,K,V]`` fp32 contiguous, **updated in place**
+    (start from the ``h_T`` that ``gdn_chunk`` returned for the prompt).  Returns ``o [B,H,V]`` bf16.
+    Not differentiable.  K must be 128, V 64 or 128.
+    """
+    if not state.is_cuda:
+        raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise GdnError("lethe_gdn: the decode state must be a contiguous fp32 tensor (it is updated in place)")
+    B, H, K, V = state.shape
+    q16, k16, v16 = _prep16(q), _prep16(k), _prep16(v)
+    g32, b32 = _prep32(g), _prep32(beta)
+    if q16.shape != (B, H, K) or k16.shape != (B, H, K) or v16.shape != (B, H, V):
+        raise GdnError("lethe_gdn: decode step expects q, k [B,H,K] and v [B,H,V] matching the state")
+    if g32 is not None and g32.shape not in ((B, H), (B, H, K)):
+        raise GdnError("lethe_gdn: decode step expects g [B,H] or [B,H,K]")
+    if b32 is not None and b32.shape != (B, H):
+        raise GdnError("lethe_gdn: decode step expects beta [B,H]")
+    o = torch.empty(B, H, V, dtype=torch.bfloat16, device=state.device)
+    a = _DecodeArgs(B=B, H=H, K=K, V=V, gate=_gate_code(None if g32 is None else g32.unsqueeze(1)),
+                    delta=0 if b32 is None else 1, scale=float(K ** -0.5 if scale is None else scale),
+                    q=_ptr(q16), k=_ptr(k16), v=_ptr(v16), g=_ptr(g32), beta=_ptr(b32), state=_ptr(state), o=_ptr(o))
+    _check(native.lib().lethe_gdn_decode_step(ctypes.byref(a), torch.cuda.current_stream(state.device).cuda_stream))
+    return o
 
 
 # ------------------------------------------------------------------------------------------------

@@ -23,9 +23,19 @@ def test_exports_every_declared_symbol(lib):
     hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
     names = set(re.findall(r"\b(lethe_[a-z0-9_]+)\s*\(", hdr))
     assert {"lethe_gdn_forward", "lethe_gdn_backward", "lethe_gdn_saved_bytes", "lethe_gdn_scratch_bytes",
-            "lethe_gdn_strerror", "lethe_gdn_forward_static", "lethe_probe_umma"} <= names
+            "lethe_gdn_strerror", "lethe_gdn_forward_static", "lethe_gdn_decode_step", "lethe_probe_umma"} <= names
     for n in names:
         assert hasattr(lib, n), n
+
+
+def test_decode_step_argument_errors(lib):
+    a = ops._DecodeArgs(B=1, H=1, K=128, V=64, gate=1, delta=1, scale=1.0)      # all pointers null
+    rc = lib.lethe_gdn_decode_step(ctypes.byref(a), None)
+    assert rc != 0 and b"null" in lib.lethe_gdn_strerror(rc)
+    a = ops._DecodeArgs(B=1, H=1, K=64, V=64, gate=0, delta=0, scale=1.0, q=0x1000, k=0x2000, v=0x3000,
+                        state=0x4000, o=0x5000)
+    rc = lib.lethe_gdn_decode_step(ctypes.byref(a), None)
+    assert rc != 0 and b"sizes" in lib.lethe_gdn_strerror(rc)
 
 
 def test_workspace_sizes(lib):
