@@ -120,6 +120,44 @@ def serial_backward(q, k, v, g, beta, h0, do, dhT=None, *, scale=None):
 
 
 # ----------------------------------------------------------------------------------------------
+# the full op: independent per-channel erase gate b [B,L,H,K] and write gate w [B,L,H,V]
+# ----------------------------------------------------------------------------------------------
+def serial_forward_full(q, k, v, g, b, w, h0=None, *, scale=None):
+    """Token-serial recurrence of the reference's six-input op (``gdn_backward.py:45-53``):
+    S <- S * exp(g_t);  v_new = w_t v_t - (b_t k_t)^T S;  S <- S + k_t v_new^T;  o_t = (scale q_t)^T S,
+    with ``g, b [B,L,H,K]`` and ``w [B,L,H,V]``.  Returns ``(o, h_T)``."""
+    B, L, H, K = k.shape
+    V = v.shape[-1]
+    s = K ** -0.5 if scale is None else scale
+    S = torch.zeros(B, H, K, V, dtype=q.dtype) if h0 is None else h0.to(q.dtype)
+    outs = []
+    for t in range(L):
+        kt = k[:, t]
+        S = S * g[:, t].exp().unsqueeze(-1)
+        vn = w[:, t] * v[:, t] - torch.einsum("bhk,bhkv->bhv", b[:, t] * kt, S)
+        S = S + kt.unsqueeze(-1) * vn.unsqueeze(-2)
+        outs.append(torch.einsum("bhk,bhkv->bhv", q[:, t] * s, S))
+    return torch.stack(outs, dim=1), S
+
+
+def serial_backward_full(q, k, v, g, b, w, h0, do, dhT=None, *, scale=None):
+    """Autograd through ``serial_forward_full`` (reference ``gdn_backward.py:70-122``).  Returns
+    ``(o, h_T, grads)`` with ``grads`` a dict over q, k, v, g, b, w and h0 (when given)."""
+    leaves = {}
+    for name, t in (("q", q), ("k", k), ("v", v), ("g", g), ("b", b), ("w", w), ("h0", h0)):
+        leaves[name] = None if t is None else t.detach().clone().requires_grad_(True)
+    o, hT = serial_forward_full(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["b"], leaves["w"],
+                                leaves["h0"], scale=scale)
+    names = [n for n, t in leaves.items() if t is not None]
+    outs, gouts = [o], [do]
+    if dhT is not None:
+        outs.append(hT)
+        gouts.append(dhT)
+    gr = torch.autograd.grad(outs, [leaves[n] for n in names], gouts, allow_unused=True)
+    return o.detach(), hT.detach(), dict(zip(names, gr))
+
+
+# ----------------------------------------------------------------------------------------------
 # chunkwise form
 # ----------------------------------------------------------------------------------------------
 def _chunks(x: Tensor, C: int) -> Tensor:

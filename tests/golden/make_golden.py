@@ -140,6 +140,25 @@ def main(ref_src: str) -> None:
     save("kda_k128", f32=True, q=q, k=k, v=v, g=g, beta=beta, do=do, o=o, dq=gr.grad_q,
          dk=gr.grad_k, dv=gr.grad_v, dg=gr.grad_g, dbeta=gr.grad_beta, scale=sg, C=C)
 
+    # ---- the full GDN-2 op: independent per-channel erase gate b [B,L,H,K] and write gate w [B,L,H,V]
+    #      (reference_gdn2_forward / _backward as they stand), one small case and one kernel-sized case
+    def full_gates(seed, Bx, Lx, Hx, Kx, Vx):
+        gen = torch.Generator().manual_seed(seed)
+        b = torch.randn(Bx, Lx, Hx, Kx, generator=gen, dtype=torch.float64).sigmoid()
+        w = torch.randn(Bx, Lx, Hx, Vx, generator=gen, dtype=torch.float64).sigmoid()
+        return b.to(torch.float32).to(torch.float64), w.to(torch.float32).to(torch.float64)
+
+    for name, (Bx, Lx, Hx, Kx, Vx), seed, f32 in (("gdn2_full_small", (B, L, H, K, V), 71, False),
+                                                    ("gdn2_full_k128", (Bg, Lg, Hg, Kg, Vg), 72, True)):
+        q, k, v, g, beta, do, h0 = draw(seed, Bx, Lx, Hx, Kx, Vx, "cw", True)
+        b, w = full_gates(seed + 100, Bx, Lx, Hx, Kx, Vx)
+        sx = Kx ** -0.5
+        o = reference_gdn2_forward(q, k, v, g, b, w, scale=sx, initial_state=h0, use_qk_l2norm=False)
+        gr = reference_gdn2_backward(q, k, v, g, b, w, do, scale=sx, initial_state=h0, use_qk_l2norm=False)
+        save(name, f32=f32, q=q, k=k, v=v, g=g, b=b.to(torch.float32), w=w.to(torch.float32), do=do, h0=h0, o=o,
+             dq=gr.grad_q, dk=gr.grad_k, dv=gr.grad_v, dg=gr.grad_g, db=gr.grad_b, dw=gr.grad_w,
+             dh0=gr.grad_initial_state, scale=sx, C=C)
+
     # ---- plain linear attention
     q, k, v, g, beta, do, h0 = draw(51, B, L, H, K, V, "scalar", True)
     o = fam.reference_la_forward(q, k, v, scale=scale, use_qk_l2norm=False)

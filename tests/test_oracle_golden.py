@@ -7,10 +7,12 @@ import numpy as np
 import pytest
 import torch
 
-from oracle.gdn_oracle import chunk_backward, chunk_forward, scale_rel, serial_backward
+from oracle.gdn_oracle import chunk_backward, chunk_forward, scale_rel, serial_backward, serial_backward_full
 
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
-CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")))
+ALL = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")))
+FULL_CASES = [n for n in ALL if n.startswith("gdn2_full")]     # independent per-channel gates b, w
+CASES = [n for n in ALL if n not in FULL_CASES]
 
 
 def load(name):
@@ -25,6 +27,18 @@ def _args(d):
 
 def test_golden_files_present():
     assert len(CASES) >= 11, CASES
+    assert len(FULL_CASES) >= 2, FULL_CASES
+
+
+@pytest.mark.parametrize("name", FULL_CASES)
+def test_full_gate_oracle_matches_reference(name):
+    d = load(name)
+    tol = 2e-6 if name.endswith("k128") else 1e-9
+    o, _hT, gr = serial_backward_full(d["q"], d["k"], d["v"], d["g"], d["b"], d["w"], d["h0"], d["do"],
+                                      scale=d["scale"])
+    assert scale_rel(o, d["o"]) < tol
+    for n in ("q", "k", "v", "g", "b", "w", "h0"):
+        assert scale_rel(gr[n], d["d" + n]) < tol, n
 
 
 @pytest.mark.parametrize("name", CASES)
