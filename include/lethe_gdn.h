@@ -43,6 +43,9 @@ typedef struct LetheGdnDims {
   int32_t gate;   /* LETHE_GATE_*                                                        */
   int32_t delta;  /* 1: erase and write gates are beta (gated delta rule, KDA)            */
                   /* 0: no erase term, write gate one (linear attention, GLA, SSD)        */
+                  /* 2: independent per-channel erase gate b and write gate w, the full   */
+                  /*    op of the reference (gdn_backward.py:45-53); needs the            */
+                  /*    channel-wise gate                                                 */
 } LetheGdnDims;
 
 typedef struct LetheGdnArgs {
@@ -82,6 +85,12 @@ typedef struct LetheGdnArgs {
   /* Non-NULL: `dbeta` receives the erase-gate part and `dbeta_write` the write-gate part, the two    */
   /* gradients the reference returns separately (db_erase / dw_write, gdn2_assemble.py:150-181).      */
   float* dbeta_write;
+  /* delta = 2 only (NULL otherwise): erase gate b [B, L, H, K] and write gate w [B, L, H, V], fp32,     */
+  /* and their gradients (backward).  `beta` / `dbeta` are not used in this mode.                       */
+  const float* b_gate;
+  const float* w_gate;
+  float* db_gate;
+  float* dw_gate;
 } LetheGdnArgs;
 
 /* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */

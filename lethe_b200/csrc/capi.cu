@@ -22,7 +22,8 @@ static bool dims_ok(const LetheGdnDims& d) {
   if (d.K != kK || (d.V != 64 && d.V != 128)) return false;
   if (d.L % kC) return false;
   if (d.gate < LETHE_GATE_NONE || d.gate > LETHE_GATE_CHANNEL) return false;
-  if (d.delta != 0 && d.delta != 1) return false;
+  if (d.delta < 0 || d.delta > 2) return false;
+  if (d.delta == 2 && d.gate != LETHE_GATE_CHANNEL) return false;
   return true;
 }
 
@@ -44,15 +45,17 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   if (!dims_ok(d)) return kErrDims;
   if (!a->q || !a->k || !a->v || !a->saved || !a->status) return kErrNull;
   if (d.gate != LETHE_GATE_NONE && !a->g) return kErrNull;
-  if (d.delta && !a->beta) return kErrNull;
+  if (d.delta == 1 && !a->beta) return kErrNull;
+  if (d.delta == 2 && (!a->b_gate || !a->w_gate)) return kErrNull;
   if (!backward && !a->o) return kErrNull;
   if (backward) {
     if (!a->d_o || !a->dq || !a->dk || !a->dv || !a->scratch) return kErrNull;
     if (d.gate != LETHE_GATE_NONE && !a->dg) return kErrNull;
-    if (d.delta && !a->dbeta) return kErrNull;
+    if (d.delta == 1 && !a->dbeta) return kErrNull;
+    if (d.delta == 2 && (!a->db_gate || !a->dw_gate)) return kErrNull;
   }
   const void* ptrs[] = {a->q, a->k, a->v, a->o, a->d_o, a->dq, a->dk, a->dv, a->h0, a->hT, a->dhT, a->dh0,
-                        a->saved, a->scratch};
+                        a->saved, a->scratch, a->b_gate, a->w_gate, a->db_gate, a->dw_gate};
   for (const void* x : ptrs)
     if (x && !aligned16(x)) return kErrAlign;
   Layout lay = make_layout(d);
@@ -60,7 +63,7 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   if (backward && a->scratch_bytes < lay.scratch_total) return kErrWorkspace;
   if (!aligned16(a->saved) || (reinterpret_cast<uintptr_t>(a->saved) & 1023u)) return kErrAlign;
   if (backward && (reinterpret_cast<uintptr_t>(a->scratch) & 1023u)) return kErrAlign;
-  p->B = d.B; p->H = d.H; p->L = d.L; p->NT = d.L / kC; p->V = d.V; p->gate = d.gate; p->delta = d.delta;
+  p->B = d.B; p->H = d.H; p->L = d.L; p->NT = d.L / kC; p->V = d.V; p->gate = d.gate; p->delta = d.delta ? 1 : 0;
   p->scale = a->scale;
   p->q = static_cast<const __nv_bfloat16*>(a->q);
   p->k = static_cast<const __nv_bfloat16*>(a->k);
@@ -72,6 +75,10 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   p->dk = static_cast<__nv_bfloat16*>(a->dk);
   p->dv = static_cast<__nv_bfloat16*>(a->dv);
   p->hT = a->hT; p->dg = a->dg; p->dbeta = a->dbeta; p->dh0 = a->dh0; p->dbeta_w = a->dbeta_write;
+  if (d.delta == 2) {
+    p->bch = a->b_gate; p->wch = a->w_gate; p->dbch = a->db_gate; p->dwch = a->dw_gate;
+    p->beta = nullptr; p->dbeta = nullptr; p->dbeta_w = nullptr;
+  }
   p->saved = static_cast<unsigned char*>(a->saved);
   p->scratch = static_cast<unsigned char*>(a->scratch);
   p->lay = lay;

@@ -131,6 +131,9 @@ struct Problem {
   const float *g, *beta, *h0, *dhT;
   __nv_bfloat16 *o, *dq, *dk, *dv;
   float *hT, *dg, *dbeta, *dh0, *dbeta_w;
+  // full op only (null otherwise): per-channel erase gate [B,L,H,K], write gate [B,L,H,V] and their gradients
+  const float *bch, *wch;
+  float *dbch, *dwch;
   unsigned char* saved;
   unsigned char* scratch;
   Layout lay;
@@ -214,6 +217,16 @@ __device__ __forceinline__ void wait_products(uint64_t* bar, uint32_t& phase, co
   mbar_wait_warp(bar, phase, ctl, code);
   phase ^= 1u;
   tc_fence_after();
+}
+
+// eight consecutive floats (16-byte aligned)
+__device__ __forceinline__ void ld8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void st8(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
 // The scan's input records R / Rb (128 rows x V columns, fp16) are stored as V / 16 column blocks of

@@ -31,14 +31,6 @@ __device__ __forceinline__ int exi(int row, int col) { return gidx(row, col); }
 // bank conflicts, and global accesses by 128 threads along d stay coalesced.
 __device__ __forceinline__ int ridx(int i, int d) { return i * kK + (d ^ ((i & 7) << 2)); }
 
-__device__ __forceinline__ void ld8(const float* p, float* v) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void st8(float* p, const float* v) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
 
 // ---------------------------------------------------------------------------------------------
 // Stage B, part 1.  Accumulators: cA [0,128) dv2; cB [128,256) [do; dv2] h^T; cC [256,320) dA;
@@ -311,9 +303,11 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     tmem_relinquish();
   }
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  // full op (per-channel erase gate b, write gate w): the gates enter element by element, beta is one
+  const bool full = p.bch != nullptr;
   float bval = 0.f;
   if (tid < 64) {
-    bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+    bval = full ? 1.f : p.beta[tok0 + static_cast<size_t>(tid) * p.H];
     betas[tid] = bval;
   }
   tc_fence_before();
@@ -337,9 +331,16 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     float x[8], y[8];
     unpack8_bf16(tile_ld_chunk(KB, r, ch, 128), x);
     tile_st_chunk(KB, r, ch, 128, pack8_f16(x));
-    const float be = betas[r];
+    float bb[8];
+    if (full) {
+      ld8(p.bch + (tok0 + static_cast<size_t>(r) * p.H) * kK + ch * 8, bb);
+    } else {
+      const float be = betas[r];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = x[e] * be * __expf(Gt[gidx(r, ch * 8 + e)]);
+      for (int e = 0; e < 8; ++e) bb[e] = be;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * bb[e] * __expf(Gt[gidx(r, ch * 8 + e)]);
     tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
@@ -347,9 +348,16 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     float x[8];
     unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
     tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
-    const float be = betas[r];
+    if (full) {
+      float wv[8];
+      ld8(p.wch + (tok0 + static_cast<size_t>(r) * p.H) * V + ch * 8, wv);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] *= be;
+      for (int i = 0; i < 8; ++i) x[i] *= wv[i];
+    } else {
+      const float be = betas[r];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] *= be;
+    }
     tile_st_chunk(BVt, r, ch, 64, pack8_f16(x));
   }
   sync_for_issue();
@@ -424,10 +432,22 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
       for (int i = 0; i < 4; ++i) {
         float vv[8], o8[8];
         unpack8_f16(tile_ld_chunk(VT, r, jb * 4 + i, 64), vv);
+        if (full) {   // dv = w dbv, dw = dbv v, element by element
+          float wv[8], dwv[8];
+          const size_t at = (tok0 + static_cast<size_t>(r) * p.H) * V + jb * 32 + 8 * i;
+          ld8(p.wch + at, wv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          rv += d[8 * i + e] * vv[e];
-          o8[e] = bval * d[8 * i + e];
+          for (int e = 0; e < 8; ++e) {
+            dwv[e] = d[8 * i + e] * vv[e];
+            o8[e] = wv[e] * d[8 * i + e];
+          }
+          st8(p.dwch + at, dwv);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            rv += d[8 * i + e] * vv[e];
+            o8[e] = bval * d[8 * i + e];
+          }
         }
         *reinterpret_cast<uint4*>(dv_g + jb * 32 + 8 * i) = pack8_bf16(o8);
       }
@@ -452,7 +472,9 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
       for (int i = 0; i < 8; ++i)
         *reinterpret_cast<float4*>(dqp_g + ridx(r, jb * 32 + 4 * i)) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
     }
-    if (p.dbeta_w) {
+    if (full) {
+      // the erase-gate gradient is formed per channel by the pair kernel
+    } else if (p.dbeta_w) {
       p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
       p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = pq;
     } else {
@@ -506,7 +528,8 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     tmem_relinquish();
   }
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
-  if (tid < 64) betas[tid] = (MODE == 1) ? p.beta[tok0 + static_cast<size_t>(tid) * p.H] : 1.f;
+  const bool full = (MODE == 1) && p.bch != nullptr;    // per-channel erase gate: x = b k element by element
+  if (tid < 64) betas[tid] = (MODE == 1 && !full) ? p.beta[tok0 + static_cast<size_t>(tid) * p.H] : 1.f;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -532,6 +555,12 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     unpack8_bf16(tile_ld_chunk(KX, r, ch, 128), kx);
     unpack8_bf16(tile_ld_chunk(KX, 64 + r, ch, 128), xx);
     const float be = betas[r];
+    if (full) {
+      float bb[8];
+      ld8(p.bch + (tok0 + static_cast<size_t>(r) * p.H) * kK + d0, bb);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xx[e] *= bb[e];
+    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       xx[e] *= be;
@@ -669,7 +698,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
   }
   __syncthreads();
-  if (MODE == 1 && tid < 64) p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid] + red[64 + tid];   // sum_d d(bk)_m k
+  if (MODE == 1 && !full && tid < 64) p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid] + red[64 + tid];   // sum_d d(bk)_m k
   LETHE_PHASE("phaseA");
   // ---- phase B: column owners (thread d; the two halves of the CTA split the rows) combine with the
   // fp32 records; every global access is coalesced and the records of eight rows are requested before
@@ -704,8 +733,13 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
           dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
         } else {
           const float eg = __expf(Gt[gidx(i, d)]);
-          const float dbk = part * eg + o1;              // d(beta k)
-          dk = dkb + dbk * betas[i] + o2;
+          const float dbk = part * eg + o1;              // d(beta k), or d(b k) of the full op
+          if (full) {
+            dk = dkb + dbk * p.bch[tok] + o2;
+            p.dbch[tok] = dbk * kv;
+          } else {
+            dk = dkb + dbk * betas[i] + o2;
+          }
           dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
         }
         if (kFinalK) p.dk[tok] = __float2bfloat16_rn(dk);

@@ -58,7 +58,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tmem_relinquish();
   }
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
-  if (DELTA && tid < 64) betas[tid] = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+  // full op (per-channel erase gate b, write gate w): the gates enter the operand tiles element by
+  // element and the per-row beta is one
+  const bool full = p.bch != nullptr;
+  if (DELTA && tid < 64) betas[tid] = full ? 1.f : p.beta[tok0 + static_cast<size_t>(tid) * p.H];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -100,11 +103,17 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       ga[e] = Gt[gidx((blk * 16), d0 + e)];
       gl[e] = Gt[gidx(63, d0 + e)];
     }
-    float ea[8];
+    float ea[8], bb[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) ea[e] = __expf(gr[e] - ga[e]);
+    if (DELTA && full) {
+      ld8(p.bch + (tok0 + static_cast<size_t>(r) * p.H) * kK + d0, bb);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = kx[e] * ea[e];
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * bb[e] * ea[e];     // left factor of M is b k
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * ea[e];
+    }
     tile_st_chunk(LA, r, ch, 128, pack8_f16(y));
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = qx[e] * ea[e];
@@ -113,9 +122,13 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(gl[e] - gr[e]);
     tile_st_chunk(KD, r, ch, 64, pack8_f16(y));
     if (DELTA) {
-      const float be = betas[r];
+      if (!full) {
+        const float be = betas[r];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = kx[e] * be * __expf(gr[e]);
+        for (int e = 0; e < 8; ++e) bb[e] = be;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * bb[e] * __expf(gr[e]);
       tile_st_chunk(BGK, r, ch, 64, pack8_f16(y));
     }
     for (int I = blk + 1; I < 4; ++I) {     // row r is a source row for every later row block I
@@ -129,9 +142,16 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(BV, r, ch, 64), x);
-    const float be = DELTA ? betas[r] : 1.f;
+    if (DELTA && full) {
+      float wv[8];
+      ld8(p.wch + (tok0 + static_cast<size_t>(r) * p.H) * V + ch * 8, wv);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] *= be;
+      for (int i = 0; i < 8; ++i) x[i] *= wv[i];
+    } else {
+      const float be = DELTA ? betas[r] : 1.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] *= be;
+    }
     tile_st_chunk(BV, r, ch, 64, pack8_f16(x));
   }
   sync_for_issue();
@@ -163,6 +183,12 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       unpack8_f16(tile_ld_chunk(KQ, 64 + i, ch, 128), qi);
       unpack8_f16(tile_ld_chunk(KQ, i, ch, 128), ki);
       unpack8_f16(tile_ld_chunk(KQ, s, ch, 128), ks);
+      if (DELTA && full) {
+        float bi[8];
+        ld8(p.bch + (tok0 + static_cast<size_t>(i) * p.H) * kK + ch * 8, bi);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ki[e] *= bi[e];
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float ex = __expf(Gt[gidx(i, ch * 8 + e)] - Gt[gidx(s, ch * 8 + e)]);

@@ -39,6 +39,8 @@ class _Args(ctypes.Structure):
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p), ("kernel_mask", ctypes.c_uint32),
         ("dbeta_write", ctypes.c_void_p),
+        ("b_gate", ctypes.c_void_p), ("w_gate", ctypes.c_void_p),
+        ("db_gate", ctypes.c_void_p), ("dw_gate", ctypes.c_void_p),
     ]
 
 
@@ -86,7 +88,9 @@ class GdnBuffers:
     def __init__(self, B, L, H, K, V, gate: int, delta: bool, device, backward: bool = True,
                  saved: Tensor | None = None, status: Tensor | None = None):
         L_ = native.lib()
-        self.dims = _Dims(B, H, L, K, V, gate, 1 if delta else 0)
+        # delta: False / True (one beta per token-head), or 2 for the full op's per-channel gates b, w
+        self.dims = _Dims(B, H, L, K, V, gate, int(delta))
+        full = int(delta) == 2
         nsaved = L_.lethe_gdn_saved_bytes(ctypes.byref(self.dims))
         if nsaved == 0:
             raise GdnError(f"lethe_gdn: unsupported sizes B={B} H={H} L={L} K={K} V={V} "
@@ -97,6 +101,7 @@ class GdnBuffers:
         self.o = torch.empty(B, L, H, V, dtype=bf, device=device)
         self.hT = torch.empty(B, H, K, V, dtype=f32, device=device)
         self.scratch = None
+        self.db = self.dw = None
         if backward:
             self.scratch = _workspace(L_.lethe_gdn_scratch_bytes(ctypes.byref(self.dims)), device)
             self.dq = torch.empty(B, L, H, K, dtype=bf, device=device)
@@ -104,26 +109,34 @@ class GdnBuffers:
             self.dv = torch.empty(B, L, H, V, dtype=bf, device=device)
             gshape = (B, L, H, K) if gate == GATE_CHANNEL else (B, L, H)
             self.dg = torch.empty(gshape, dtype=f32, device=device) if gate != GATE_NONE else None
-            self.dbeta = torch.empty(B, L, H, dtype=f32, device=device) if delta else None
+            self.dbeta = torch.empty(B, L, H, dtype=f32, device=device) if (delta and not full) else None
+            self.db = torch.empty(B, L, H, K, dtype=f32, device=device) if full else None
+            self.dw = torch.empty(B, L, H, V, dtype=f32, device=device) if full else None
             self.dbeta_write = None      # set to a [B, L, H] fp32 tensor to get the erase / write split
             self.dh0 = torch.empty(B, H, K, V, dtype=f32, device=device)
 
 
-def forward_into(buf: GdnBuffers, q, k, v, g, beta, h0, scale: float, kernel_mask: int = 0) -> None:
-    """Enqueue the forward kernels on the current stream; results land in ``buf.o`` / ``buf.hT``."""
+def forward_into(buf: GdnBuffers, q, k, v, g, beta, h0, scale: float, kernel_mask: int = 0, *,
+                 b_gate=None, w_gate=None) -> None:
+    """Enqueue the forward kernels on the current stream; results land in ``buf.o`` / ``buf.hT``.
+    ``b_gate [B,L,H,K]`` / ``w_gate [B,L,H,V]`` (fp32) replace ``beta`` for buffers made with ``delta=2``."""
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
               h0=_ptr(h0), o=_ptr(buf.o), hT=_ptr(buf.hT), saved=_ptr(buf.saved),
-              saved_bytes=buf.saved.numel(), status=_ptr(buf.status), kernel_mask=kernel_mask)
+              saved_bytes=buf.saved.numel(), status=_ptr(buf.status), kernel_mask=kernel_mask,
+              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate))
     _check(native.lib().lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
-def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, kernel_mask: int = 0) -> None:
-    """Enqueue the backward kernels; gradients land in ``buf.dq`` ... ``buf.dh0``."""
+def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, kernel_mask: int = 0, *,
+                  b_gate=None, w_gate=None) -> None:
+    """Enqueue the backward kernels; gradients land in ``buf.dq`` ... ``buf.dh0`` (``buf.db`` / ``buf.dw``
+    for the per-channel gates of buffers made with ``delta=2``)."""
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
               h0=_ptr(h0), d_o=_ptr(do), dhT=_ptr(dhT), dq=_ptr(buf.dq), dk=_ptr(buf.dk), dv=_ptr(buf.dv),
               dg=_ptr(buf.dg), dbeta=_ptr(buf.dbeta), dh0=_ptr(buf.dh0), saved=_ptr(buf.saved),
               saved_bytes=buf.saved.numel(), scratch=_ptr(buf.scratch), scratch_bytes=buf.scratch.numel(),
-              status=_ptr(buf.status), kernel_mask=kernel_mask, dbeta_write=_ptr(buf.dbeta_write))
+              status=_ptr(buf.status), kernel_mask=kernel_mask, dbeta_write=_ptr(buf.dbeta_write),
+              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), db_gate=_ptr(buf.db), dw_gate=_ptr(buf.dw))
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
@@ -276,6 +289,51 @@ def gdn_decode_step(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Ten
     return o
 
 
+class _GdnFull(torch.autograd.Function):
+    """The reference's full recurrence (``src/lethe/kernels/references/gdn_backward.py:45-53``): per-channel
+    log decay ``g`` and erase gate ``b`` (``[B,L,H,K]``), per-channel write gate ``w`` (``[B,L,H,V]``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, b, w, h0, scale):
+        if not q.is_cuda:
+            raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+        B, L, H, K = q.shape
+        V = v.shape[-1]
+        if K != 128 or L % 64:
+            raise GdnError("lethe_gdn: the full-gate op needs d_k = 128 and L a multiple of 64")
+        ctx.in_dtypes = tuple(None if t is None else t.dtype for t in (q, k, v, g, b, w, h0))
+        q16, k16, v16 = _prep16(q), _prep16(k), _prep16(v)
+        g32, b32, w32, h32 = _prep32(g), _prep32(b), _prep32(w), _prep32(h0)
+        buf = GdnBuffers(B, L, H, K, V, GATE_CHANNEL, 2, q.device, backward=False)
+        forward_into(buf, q16, k16, v16, g32, None, h32, scale, b_gate=b32, w_gate=w32)
+        ctx.save_for_backward(q16, k16, v16, g32, b32, w32, h32, buf.saved, buf.status)
+        ctx.scale = scale
+        return buf.o.to(v.dtype), buf.hT
+
+    @staticmethod
+    def backward(ctx, do, dhT):
+        q16, k16, v16, g32, b32, w32, h32, saved, status = ctx.saved_tensors
+        B, L, H, K = q16.shape
+        buf = GdnBuffers(B, L, H, K, v16.shape[-1], GATE_CHANNEL, 2, q16.device, saved=saved, status=status)
+        backward_into(buf, q16, k16, v16, g32, None, h32, _prep16(do), _prep32(dhT), ctx.scale,
+                      b_gate=b32, w_gate=w32)
+        dts = ctx.in_dtypes
+        return (buf.dq.to(dts[0]), buf.dk.to(dts[1]), buf.dv.to(dts[2]), buf.dg.to(dts[3]), buf.db.to(dts[4]),
+                buf.dw.to(dts[5]), None if dts[6] is None else buf.dh0.to(dts[6]), None)
+
+
+def gdn_chunk_full(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Tensor, h0: Tensor | None = None, *,
+                   scale: float | None = None, use_qk_l2norm: bool = False) -> tuple[Tensor, Tensor]:
+    """The reference's full six-input recurrence with an initial state in and the final state out:
+    ``g, b [B,L,H,K]`` (log decay and erase gate per key channel), ``w [B,L,H,V]`` (write gate per value
+    channel).  Returns ``(o, h_T)``; gradients flow to all seven inputs."""
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    if use_qk_l2norm:
+        q, k = _l2norm(q.float()).to(q.dtype), _l2norm(k.float()).to(k.dtype)
+    return _GdnFull.apply(q, k, v, g, b, w, h0, float(scale))
+
+
 # ------------------------------------------------------------------------------------------------
 # The reference's own six-input surface
 # ------------------------------------------------------------------------------------------------
@@ -291,7 +349,8 @@ class _Gdn2Op(torch.autograd.Function):
     (``src/lethe/kernels/cute/gdn2_backward.py:53-60,102-134`` and ``cute/gdn2_family.py``):
     ``b`` and ``w`` both equal to one beta per token-head broadcast over the channels (gated delta
     rule / KDA), or ``b = 0, w = 1`` (no delta term); ``g`` either constant over the channels
-    (scalar gate) or not (channel-wise gate).  Any other ``b`` / ``w`` raises.
+    (scalar gate) or not (channel-wise gate).  Independent per-channel ``b`` / ``w`` do not come
+    here: ``gdn2_op`` sends them to ``gdn_chunk_full``.
 
     Gradients of broadcast inputs are spread evenly over the channels, as the reference's scalar
     assembly does (``gdn2_assemble.py:343-345``); ``grad_b`` carries the erase part and ``grad_w`` the
@@ -359,4 +418,12 @@ def gdn2_op(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Tensor, *,
         scale = q.shape[-1] ** -0.5
     if q.shape[-1] != 128:
         raise GdnError("lethe_gdn: gdn2_op needs d_k = 128 (use gdn_chunk for d_k = 64)")
-    return _Gdn2Op.apply(q, k, v, g, b, w, float(scale), bool(use_qk_l2norm))
+    with torch.no_grad():
+        one_beta = _channel_constant(b) and _channel_constant(w) and bool(torch.equal(b[..., 0], w[..., 0]))
+        no_delta = not bool(b.any()) and bool((w == 1).all())
+    if one_beta or no_delta:
+        # the regimes the scalar-beta kernels cover (cheaper: one gate value per token-head)
+        return _Gdn2Op.apply(q, k, v, g, b, w, float(scale), bool(use_qk_l2norm))
+    # independent per-channel erase / write gates: the full recurrence
+    o, _ = gdn_chunk_full(q, k, v, g, b, w, None, scale=float(scale), use_qk_l2norm=bool(use_qk_l2norm))
+    return o

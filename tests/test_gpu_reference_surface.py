@@ -50,12 +50,86 @@ def test_gdn2_op_six_inputs(gate):
     assert max(errs.values()) <= 8e-3, errs
 
 
-def test_gdn2_op_rejects_general_gates():
-    B, L, H, K, V = 1, 64, 1, 128, 64
-    x = torch.rand(B, L, H, K, device="cuda")
-    with pytest.raises(GdnError):
-        gdn2_op(x.bfloat16(), x.bfloat16(), torch.rand(B, L, H, V, device="cuda").bfloat16(), -x, x,
-                torch.rand(B, L, H, V, device="cuda"))
+def _full_inputs(B, L, H, K, V, seed, with_h0=True):
+    inp = make_inputs(B, L, H, K, V, gate="channel", delta=True, seed=seed, with_h0=with_h0)
+    gen = torch.Generator().manual_seed(seed + 100)
+    inp["b"] = torch.randn(B, L, H, K, generator=gen).sigmoid()
+    inp["w"] = torch.randn(B, L, H, V, generator=gen).sigmoid()
+    return inp
+
+
+@pytest.mark.parametrize("V,L", [(64, 256), (128, 128)])
+def test_full_gate_op_matches_oracle(V, L):
+    """The reference's full recurrence (independent per-channel erase gate b and write gate w) against
+    the token-serial fp64 oracle, with an initial state and a final-state adjoint."""
+    from lethe_b200.ops import gdn_chunk_full
+    from oracle.gdn_oracle import serial_backward_full
+
+    B, H, K = 2, 2, 128
+    inp = _full_inputs(B, L, H, K, V, seed=21)
+    dhT = 0.1 * torch.randn(B, H, K, V, generator=torch.Generator().manual_seed(4))
+    names = ("q", "k", "v", "g", "b", "w", "h0")
+    f = {n: inp[n].double() for n in names}
+    o_ref, hT_ref, gr = serial_backward_full(f["q"], f["k"], f["v"], f["g"], f["b"], f["w"], f["h0"],
+                                             inp["do"].double(), dhT.double())
+    leaves = [inp[n].cuda().requires_grad_(True) for n in names]
+    o, hT = gdn_chunk_full(*leaves)
+    grads = torch.autograd.grad([o, hT], leaves, [inp["do"].cuda(), dhT.cuda()])
+    errs = {"o": scale_rel(o.detach().double().cpu(), o_ref), "hT": scale_rel(hT.detach().double().cpu(), hT_ref)}
+    for n, t in zip(names, grads):
+        errs["d" + n] = scale_rel(t.double().cpu(), gr[n])
+    report(f"full-gate op V={V} L={L}", errs)
+    assert max(errs.values()) <= 5e-3, errs
+    # run to run bitwise
+    o2, hT2 = gdn_chunk_full(*leaves)
+    grads2 = torch.autograd.grad([o2, hT2], leaves, [inp["do"].cuda(), dhT.cuda()])
+    assert torch.equal(o, o2) and all(torch.equal(a, b) for a, b in zip(grads, grads2))
+
+
+def test_full_gate_op_golden():
+    """Against the vectors the reference itself produced for its six-input op (tests/golden/make_golden.py)."""
+    import os
+
+    import numpy as np
+
+    from lethe_b200.ops import gdn_chunk_full
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "gdn2_full_k128.npz"))
+    t = {n: torch.from_numpy(z[n]) for n in z.files if z[n].ndim}
+    names = ("q", "k", "v", "g", "b", "w", "h0")
+    leaves = [(t[n].bfloat16() if n in ("q", "k", "v") else t[n].float()).cuda().requires_grad_(True) for n in names]
+    o, _ = gdn_chunk_full(*leaves, scale=float(z["scale"]))
+    grads = torch.autograd.grad(o, leaves, t["do"].bfloat16().cuda())
+    errs = {"o": scale_rel(o.detach().double().cpu(), t["o"].double())}
+    for n, gt in zip(names, grads):
+        errs["d" + n] = scale_rel(gt.double().cpu(), t["d" + n].double())
+    report("golden gdn2_full_k128", errs)
+    assert max(errs.values()) <= 5e-3, errs
+
+
+def test_gdn2_op_takes_general_gates():
+    """The six-input surface with independent b, w (and its default L2 normalisation of q, k)."""
+    from oracle.gdn_oracle import serial_backward_full
+
+    B, L, H, K, V = 1, 128, 2, 128, 64
+    inp = _full_inputs(B, L, H, K, V, seed=33, with_h0=False)
+    gen = torch.Generator().manual_seed(9)
+    q = torch.randn(B, L, H, K, generator=gen)
+    k = torch.randn(B, L, H, K, generator=gen)
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, inp["v"], inp["g"], inp["b"], inp["w"])]
+    o = gdn2_op(*leaves)
+    grads = torch.autograd.grad(o, leaves, inp["do"].cuda())
+    q64, k64 = q.double().requires_grad_(True), k.double().requires_grad_(True)
+    o_ref, _, gr = serial_backward_full(_l2(q64).detach(), _l2(k64).detach(), inp["v"].double(), inp["g"].double(),
+                                        inp["b"].double(), inp["w"].double(), None, inp["do"].double())
+    dq_ref, dk_ref = torch.autograd.grad((_l2(q64), _l2(k64)), (q64, k64), (gr["q"], gr["k"]))
+    errs = {"o": scale_rel(o.detach().double().cpu(), o_ref), "dq": scale_rel(grads[0].double().cpu(), dq_ref),
+            "dk": scale_rel(grads[1].double().cpu(), dk_ref), "dv": scale_rel(grads[2].double().cpu(), gr["v"]),
+            "dg": scale_rel(grads[3].double().cpu(), gr["g"]), "db": scale_rel(grads[4].double().cpu(), gr["b"]),
+            "dw": scale_rel(grads[5].double().cpu(), gr["w"])}
+    report("gdn2_op general gates", errs)
+    # q, k are rounded to bf16 after the normalisation: allow for that extra rounding
+    assert max(errs.values()) <= 8e-3, errs
 
 
 def test_family_wrappers():
