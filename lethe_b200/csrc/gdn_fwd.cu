@@ -23,7 +23,7 @@ constexpr int kMs = 68;  // row stride (floats) of the fp32 copy of M used by th
 // h' = exp(G_last) h + kd^T (u - w h) into h' = exp(G_last) h - P h + R.
 // ---------------------------------------------------------------------------------------------
 template <int V, bool DELTA>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
                const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
   extern __shared__ unsigned char smem_raw[];
@@ -44,7 +44,9 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   float* Tsm = Msm + 64 * kMs;                          // [48][64]: finished rows of T, fp32
   unsigned char* WU = KQ;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves take
+  // the same rows and split the columns of every epilogue.
+  const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
   const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
@@ -92,14 +94,14 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     decs[tid] = __expf(Glast - G);
     bgs[tid] = bval * __expf(G);
   }
-  reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Glast);
+  if (tid < kK) reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Glast);
   __syncthreads();
 
   // ---- operands: k, q -> fp16 in place; kd, beta gamma k, beta v
   LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 201);
   LETHE_PHASE("loaded");
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
     unpack8_bf16(tile_ld_chunk(KQ, r, ch, 128), x);
@@ -117,7 +119,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     unpack8_bf16(tile_ld_chunk(KQ, 64 + r, ch, 128), x);
     tile_st_chunk(KQ, 64 + r, ch, 128, pack8_f16(x));
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(BV, r, ch, 64), x);
@@ -143,36 +145,40 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   tc_fence_after();
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   {
-    float d[64];
-    tmem_ld32(tmem + lane_base, d);
-    tmem_ld32(tmem + lane_base + 32, d + 32);
-    tmem_ld_wait();
-    if (tid < 64) {
+    // each half takes 32 of the 64 columns; rows 0-31 (lane quadrant 0 of either operand half) have
+    // nothing right of column 31, so the triangle is cut per warp
+    const bool live = (half == 0) || ((warp & 1) != 0);
+    float d[32];
+    if (live) {
+      tmem_ld32(tmem + lane_base + half * 32, d);
+      tmem_ld_wait();
+    }
+    if (tq < 64) {
       if (DELTA) {
-        // rows 0-31 (warp 0) have nothing right of column 31: the triangle is cut per warp
-        const int r = tid;
-        const bool upper = (warp & 1) != 0;
+        const int r = tq;
+        const float Gr = Gs[r], be = betas[r];
 #pragma unroll
-        for (int s = 0; s < 64; ++s) {
+        for (int j = 0; j < 32; ++j) {
+          const int s = half * 32 + j;
           float m = 0.f;
-          if (s < 32 || upper) m = (s < r) ? bval * __expf(G - Gs[s]) * d[s] : 0.f;
+          if (live) m = (s < r) ? be * __expf(Gr - Gs[s]) * d[j] : 0.f;
           Msm[r * kMs + s] = m;
         }
       }
     } else {
-      const int r = tid - 64;
+      const int r = tq - 64;
       const float Gr = Gs[r];
-      const bool upper = (warp & 1) != 0;
 #pragma unroll
-      for (int s8 = 0; s8 < 8; ++s8) {
+      for (int q = 0; q < 4; ++q) {
+        const int s8 = half * 4 + q;
         float a[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) a[i] = 0.f;
-        if (s8 < 4 || upper) {
+        if (live) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int s = s8 * 8 + i;
-            a[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * d[s] : 0.f;
+            a[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * d[q * 8 + i] : 0.f;
           }
         }
         tile_st_chunk(TA, 64 + r, s8, 128, pack8_f16(a));
@@ -213,14 +219,15 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     LETHE_PHASE("g2");
     ph ^= 1;
     tc_fence_after();
-    if (tid < 64) {
+    if (tq < 64) {
+      constexpr int kHalf2 = (128 + V) / 64;
 #pragma unroll 1
-      for (int jb = 0; jb < (128 + V) / 32; ++jb) {
+      for (int jb = half * kHalf2; jb < (half + 1) * kHalf2; ++jb) {
         float d[32];
         tmem_ld32(tmem + lane_base + jb * 32, d);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tile_st_chunk(WU, tid, jb * 4 + i, 64, pack8_f16(d + 8 * i));
+        for (int i = 0; i < 4; ++i) tile_st_chunk(WU, tq, jb * 4 + i, 64, pack8_f16(d + 8 * i));
       }
     }
     tc_fence_before();
@@ -259,18 +266,19 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   {
     unsigned char* SP = BGK;
     unsigned char* SR = KQ;
+    constexpr int kHalf3 = N3 / 64;
 #pragma unroll 1
-    for (int jb = 0; jb < N3 / 32; ++jb) {
+    for (int jb = half * kHalf3; jb < (half + 1) * kHalf3; ++jb) {
       float d[32];
       tmem_ld32(tmem + lane_base + jb * 32, d);
       tmem_ld_wait();
       if (DELTA && jb < 4) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tile_st_chunk(SP, tid, jb * 4 + i, 128, pack8_f16(d + 8 * i));
+        for (int i = 0; i < 4; ++i) tile_st_chunk(SP, tq, jb * 4 + i, 128, pack8_f16(d + 8 * i));
       } else {
         const int c8 = (jb - (DELTA ? 4 : 0)) * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tid, c8 + i)) = pack8_f16(d + 8 * i);
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tq, c8 + i)) = pack8_f16(d + 8 * i);
       }
     }
     fence_proxy_async();
@@ -449,7 +457,7 @@ static int launch_prepare_t(const Problem& p, const CUtensorMap& mq, const CUten
   const int smem = 32768 + 16384 + V * 128 + 16384 + 16384 + 264 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_kernel<V, DELTA>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
-  kern<<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V, bool DELTA, bool CW>
