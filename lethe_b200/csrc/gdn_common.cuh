@@ -288,6 +288,72 @@ __device__ __forceinline__ void unit_lower_inverse64(const float* Msm, float* Ts
   }
 }
 
+// The same inverse on 128 threads (four warps): warp w owns columns 16 w .. 16 w + 15, lanes l and
+// l + 16 share column 16 w + (l & 15).  Of a block's sixteen sums over the finished rows each lane of
+// the pair takes eight; the upper lane hands its eight to the lower one, which resolves the block's
+// rows and writes them out.  Every lane of the four warps must call (warp-level exchange inside).
+template <int MS>
+__device__ __forceinline__ void unit_lower_inverse64_pairs(const float* Msm, float* Tsm, unsigned char* TA, int t) {
+  const int w = t >> 5, lane = t & 31, hh = lane >> 4, j = 16 * w + (lane & 15);
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    if (blk < w) {   // rows above the column's own block are zero (uniform per warp)
+      if (hh == 0) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(0.f);
+      }
+      continue;
+    }
+    const float* Mb = Msm + blk * 16 * MS;
+    float part[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) part[r] = 0.f;
+    const float* Mh = Mb + hh * 8 * MS;
+    for (int s = w * 16; s < blk * 16; s += 8) {
+      float tv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tv[i] = Tsm[(s + i) * 64 + j];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 m0 = *reinterpret_cast<const float4*>(Mh + r * MS + s);
+        const float4 m1 = *reinterpret_cast<const float4*>(Mh + r * MS + s + 4);
+        part[r] += ((m0.x * tv[0] + m0.y * tv[1]) + (m0.z * tv[2] + m0.w * tv[3])) +
+                   ((m1.x * tv[4] + m1.y * tv[5]) + (m1.z * tv[6] + m1.w * tv[7]));
+      }
+    }
+    float col[16];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const float up = __shfl_down_sync(0xffffffffu, part[r], 16);   // rows 8-15 from the upper lane
+      col[r] = ((blk * 16 + r == j) ? 1.f : 0.f) - part[r];
+      col[8 + r] = ((blk * 16 + 8 + r == j) ? 1.f : 0.f) - up;
+    }
+    if (hh == 0) {
+#pragma unroll
+      for (int r = 1; r < 16; ++r) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int q = 0; q < (r + 3) / 4; ++q) {
+          const float4 m = *reinterpret_cast<const float4*>(Mb + r * MS + blk * 16 + 4 * q);
+          a0 += m.x * col[4 * q];
+          if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
+          if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
+          if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
+        }
+        col[r] -= a0 + a1;
+      }
+      if (blk < 3) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) Tsm[(blk * 16 + r) * 64 + j] = col[r];
+      }
+#pragma unroll
+      for (int r = 0; r < 16; ++r)
+        *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(col[r]);
+    }
+    __syncwarp();   // the upper lanes read the rows just written
+  }
+}
+
 // Deterministic sum over the 128 threads of a CTA (fixed tree).  `red` is a shared float[4].
 __device__ __forceinline__ float cta_sum128(float x, int tid, float* red) {
 #pragma unroll

@@ -190,10 +190,10 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   LETHE_PHASE("epi1");
 
   // ---- T = (I + M)^-1 (fp32, CUDA cores)
-  if (tid < 64) {
-    if (DELTA) {
-      unit_lower_inverse64<kMs>(Msm, Tsm, TA, tid);
-    } else {
+  if (DELTA) {
+    if (tid < 128) unit_lower_inverse64_pairs<kMs>(Msm, Tsm, TA, tid);
+  } else if (tid < 64) {
+    {
 #pragma unroll
       for (int i = 0; i < 64; ++i)
         *reinterpret_cast<__half*>(TA + sw128_off(i, tid, 128)) = __float2half_rn((i == tid) ? 1.f : 0.f);
