@@ -18,7 +18,7 @@
 namespace lg {
 
 template <int V>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv,
                const __grid_constant__ CUtensorMap mdk, const __grid_constant__ CUtensorMap mdv) {
   extern __shared__ unsigned char smem_raw[];
@@ -35,10 +35,13 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   float* betas = fs + 64;  // [64]
   float* tmp = fs + 192;   // [8]
   float* bgs = fs + 200;   // [64] beta_i exp(G_i)
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 264);
+  float* prt = fs + 264;   // [2][5][64] per column half: pk, dbeta_m, rowsum_e, colsum_e, rv
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 904);
   float* DK = reinterpret_cast<float*>(GK);    // fp32 [64][64], column XOR swizzle
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves take
+  // the same rows and split the columns of every epilogue; per-row sums are combined through `prt`.
+  const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
   const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
@@ -89,7 +92,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 421);
   LETHE_PHASE("loaded");
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
     unpack8_bf16(tile_ld_chunk(T1, r, ch, 128), x);
@@ -106,7 +109,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
       tile_st_chunk(TP, r, ch, 64, pack8_f16(t));
     }
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
@@ -129,26 +132,27 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   wait_products(bar_mma, ph, ctl, 422);
   LETHE_PHASE("g1");
+  const int c0 = half * 32;           // this half's 32 columns of every 64-column accumulator
+  const bool live = (half == 0) || ((warp & 1) != 0);   // rows 0-31 have nothing right of column 31 in a triangle
   float pk = 0.f;
-  if (tid < 64) {
-    float d[64];
-    tmem_ld32(R1 + lane_base, d);
-    tmem_ld32(R1 + lane_base + 32, d + 32);
+  if (tq < 64) {
+    float d[32];
+    tmem_ld32(R1 + lane_base + c0, d);
     tmem_ld_wait();
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
+    for (int q = 0; q < 4; ++q) {
       float y[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = d[s8 * 8 + i] * betas[s8 * 8 + i];
-      tile_st_chunk(W8, tid, s8, 64, pack8_f16(y));
+      for (int i = 0; i < 8; ++i) y[i] = d[q * 8 + i] * betas[c0 + q * 8 + i];
+      tile_st_chunk(W8, tq, half * 4 + q, 64, pack8_f16(y));
     }
     // p_i = sum_l T[l, i] (k dw^T)[i, l]
-    tmem_ld32(R0 + 64 + lane_base, d);
-    tmem_ld32(R0 + 96 + lane_base, d + 32);
+    tmem_ld32(R0 + 64 + lane_base + c0, d);
     tmem_ld_wait();
 #pragma unroll
-    for (int l = 0; l < 64; ++l)
-      pk += d[l] * __half2float(*reinterpret_cast<const __half*>(TAt + sw128_off(l, tid, 128)));
+    for (int l = 0; l < 32; ++l)
+      pk += d[l] * __half2float(*reinterpret_cast<const __half*>(TAt + sw128_off(c0 + l, tq, 128)));
+    prt[(half * 5 + 0) * 64 + tq] = pk;
   }
   sync_for_issue();
   LETHE_PHASE("epi1");
@@ -161,13 +165,12 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   wait_products(bar_mma, ph, ctl, 423);
   LETHE_PHASE("g2");
-  if (tid < 64) {
-    float d[64];
-    tmem_ld32(R1 + lane_base, d);
-    tmem_ld32(R1 + lane_base + 32, d + 32);
+  if (tq < 64) {
+    float d[32];
+    tmem_ld32(R1 + lane_base + c0, d);
     tmem_ld_wait();
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(W8, tid, s8, 64, pack8_f16(d + 8 * s8));
+    for (int q = 0; q < 4; ++q) tile_st_chunk(W8, tq, half * 4 + q, 64, pack8_f16(d + 8 * q));
   }
   sync_for_issue();
   LETHE_PHASE("epi2");
@@ -180,46 +183,56 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   wait_products(bar_mma, ph, ctl, 424);
   LETHE_PHASE("g3");
-  float rowsum_e = 0.f, colsum_e = 0.f, dbeta_m = 0.f, dgv = 0.f;
-  float kk[64];
-  if (tid < 64) {
-    const int r = tid;
-    float dm[64];
-    tmem_ld32(R1 + lane_base, dm);
-    tmem_ld32(R1 + lane_base + 32, dm + 32);
-    tmem_ld32(R0 + lane_base, kk);
-    tmem_ld32(R0 + lane_base + 32, kk + 32);
-    tmem_ld_wait();
-    const float Gr = Gs[r];
-    const bool upper = (warp & 1) != 0;   // rows 0-31 (warp 0) have nothing right of column 31
+  float kk[32];
+  if (tq < 64) {
+    const int r = tq;
+    float rowsum_e = 0.f, dbeta_m = 0.f;
+    float dm[32];
+    if (live) {
+      tmem_ld32(R1 + lane_base + c0, dm);
+      tmem_ld32(R0 + lane_base + c0, kk);
+      tmem_ld_wait();
+    }
+    const float Gr = Gs[r], bval_r = betas[r];
 #pragma unroll
-    for (int s = 0; s < 64; ++s) {
+    for (int j = 0; j < 32; ++j) {
+      const int s = c0 + j;
       float dkk = 0.f;
-      if (s < 32 || upper) {
-        const float x = (s < r) ? dm[s] * __expf(Gr - Gs[s]) : 0.f;      // dM * ratio, strictly lower
-        dbeta_m += x * kk[s];
-        dkk = x * bval;
-        rowsum_e += dkk * kk[s];
+      if (live) {
+        const float x = (s < r) ? dm[j] * __expf(Gr - Gs[s]) : 0.f;      // dM * ratio, strictly lower
+        dbeta_m += x * kk[j];
+        dkk = x * bval_r;
+        rowsum_e += dkk * kk[j];
       }
       DK[r * 64 + (s ^ (r & 31))] = dkk;
     }
+    prt[(half * 5 + 1) * 64 + r] = dbeta_m;
+    prt[(half * 5 + 2) * 64 + r] = rowsum_e;
   }
   __syncthreads();
   LETHE_PHASE("epi3a");
-  if (tid < 64) {
-    const int r = tid;
+  if (tq < 64) {
+    const int r = tq;
+    float colsum_e = 0.f;
+    // column sums need KK[s, r] = KK[r, s] for s > r: rows 32-63 of the lower half's columns are not
+    // loaded above (cut), so take them from the symmetric entry only where this thread holds it
+    if (!live) {
+      tmem_ld32(R0 + lane_base + c0, kk);
+      tmem_ld_wait();
+    }
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
+    for (int q = 0; q < 4; ++q) {
       float y[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int s = s8 * 8 + i;
+        const int s = c0 + q * 8 + i;
         const float up = DK[s * 64 + (r ^ (s & 31))];          // dkk[s, r], non-zero for s > r
         y[i] = DK[r * 64 + (s ^ (r & 31))] + up;
-        colsum_e += up * kk[s];                                // KK is symmetric
+        colsum_e += up * kk[q * 8 + i];                        // KK is symmetric
       }
-      tile_st_chunk(W8, r, s8, 64, pack8_f16(y));
+      tile_st_chunk(W8, r, half * 4 + q, 64, pack8_f16(y));
     }
+    prt[(half * 5 + 3) * 64 + r] = colsum_e;
   }
   sync_for_issue();
   LETHE_PHASE("epi3b");
@@ -242,12 +255,13 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   // leave by tensor-map stores
   unsigned char* SKo = T1;            // dk: 64 x 128, two atoms
   unsigned char* SV = T1 + 16384;     // dv: 64 x V
-  if (tid < 64) {
-    const int r = tid;
-    const float gam = __expf(Gs[r]);
+  if (tq < 64) {
+    const int r = tq;
+    const float bval_r = betas[r];
     float rv = 0.f;
 #pragma unroll
-    for (int jb = 0; jb < V / 32; ++jb) {
+    for (int jj = 0; jj < V / 64; ++jj) {
+      const int jb = half * (V / 64) + jj;
       float d[32];
       tmem_ld32(R2 + lane_base + jb * 32, d);
       tmem_ld_wait();
@@ -258,15 +272,16 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           rv += d[8 * i + e] * vv[e];
-          o8[e] = bval * d[8 * i + e];
+          o8[e] = bval_r * d[8 * i + e];
         }
         tile_st_chunk(SV, r, jb * 4 + i, 64, pack8_bf16(o8));
       }
     }
+    prt[(half * 5 + 4) * 64 + r] = rv;
     const float* dkb_s = reinterpret_cast<const float*>(GK) + r * 32;
     mbar_wait_warp(bar_dkb, 0, ctl, 426);
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jb = 2 * half; jb < 2 * half + 2; ++jb) {
       float sk[32];
       tmem_ld32(R0 + lane_base + jb * 32, sk);
       tmem_ld_wait();
@@ -281,13 +296,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
         tile_st_chunk(SKo, r, jb * 4 + i, 64, pack8_bf16(o8));
       }
     }
-    if (p.dbeta_w) {
-      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
-      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = gam * pk + dbeta_m;
-    } else {
-      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + gam * pk + dbeta_m;
-    }
-    dgv = dgb + rowsum_e - colsum_e + bval * pk * gam;
   }
   fence_proxy_async();
   __syncthreads();
@@ -297,6 +305,23 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     bulk_commit();
   }
   LETHE_PHASE("epi4");
+  float dgv = 0.f;
+  if (tid < 64) {
+    const int r = tid;
+    const float gam = __expf(Gs[r]);
+    const float pks = prt[0 * 64 + r] + prt[5 * 64 + r];
+    const float dbm = prt[1 * 64 + r] + prt[6 * 64 + r];
+    const float rse = prt[2 * 64 + r] + prt[7 * 64 + r];
+    const float cse = prt[3 * 64 + r] + prt[8 * 64 + r];
+    const float rvs = prt[4 * 64 + r] + prt[9 * 64 + r];
+    if (p.dbeta_w) {
+      p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rvs;
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = gam * pks + dbm;
+    } else {
+      p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rvs + gam * pks + dbm;
+    }
+    dgv = dgb + rse - cse + bval * pks * gam;
+  }
   {
     const float acc = chunk_rev_cumsum(dgv, tid, tmp);
     if (tid < 64 && p.gate == LETHE_GATE_SCALAR) p.dg[tok0 + static_cast<size_t>(tid) * p.H] = acc;
@@ -311,10 +336,10 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
 template <int V>
 static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, const OutMaps& mo,
                         cudaStream_t st) {
-  const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 264 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 904 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   if (cudaFuncSetAttribute(bwd_wy2_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return kErrLaunch;
-  bwd_wy2_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv, mo.dk, mo.dv);
+  bwd_wy2_kernel<V><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mk, mv, mo.dk, mo.dv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
