@@ -190,7 +190,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
-    mbar_init(bar_mma, 1);
+    mbar_init(bar_mma, 2);     // two issuing warps commit every product group
     fence_mbar_init();
     fence_proxy_async();
     mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
@@ -228,17 +228,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 411);
   LETHE_PHASE("loaded");
-  // exp(G_last) <dh, h>: the two tile images share the swizzle, so the product is elementwise
-  float dhh = 0.f;
-  for (int idx = tid; idx < kK * V / 8; idx += 256) {
-    float x[8], y[8];
-    unpack8_f16(*reinterpret_cast<const uint4*>(DHt + idx * 16), x);
-    unpack8_f16(*reinterpret_cast<const uint4*>(Ht + idx * 16), y);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) dhh += x[i] * y[i];
-  }
-  dhh = cta_sum256(dhh, tid, tmp + 2) * __expf(Glast);
-  LETHE_PHASE("dhh");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
@@ -269,14 +258,29 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   // ---- group 1: kd dh (rows 64-127 of cD), A^T do (rows 64-127 of cA), dA = do v_new^T (rows 0-63 of cC)
-  if (warp == 0) {
+  // (two warps issue, half of the group's products each: issuing is what the group costs)
+  if (warp == 0 || warp == 4) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
-    issue_product_led(leader, cD, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
-    issue_product_led(leader, cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
-    issue_product_led(leader, cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 128, false}, 64, V, 0u);
+    if (warp == 0) {
+      issue_product_led(leader, cD, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
+    } else {
+      issue_product_led(leader, cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
+      issue_product_led(leader, cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 128, false}, 64, V, 0u);
+    }
     umma_commit_led(leader, bar_mma);
   }
+  // in the shadow of the products: exp(G_last) <dh, h>; the two tile images share the swizzle, so the
+  // product is elementwise (the tiles are only read)
+  float dhh = 0.f;
+  for (int idx = tid; idx < kK * V / 8; idx += 256) {
+    float x[8], y[8];
+    unpack8_f16(*reinterpret_cast<const uint4*>(DHt + idx * 16), x);
+    unpack8_f16(*reinterpret_cast<const uint4*>(Ht + idx * 16), y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dhh += x[i] * y[i];
+  }
+  dhh = cta_sum256(dhh, tid, tmp + 2) * __expf(Glast);
   LETHE_PHASE("issue1");
   wait_products(bar_mma, ph, ctl, 412);
   LETHE_PHASE("g1");
@@ -335,13 +339,16 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("epi1");
 
   // ---- group 2: cB = [do; dv2] h^T;  cA = dAr k (rows 0-63 dq_intra);  cD = dAr^T q + (dec v_new) dh^T
-  if (warp == 0) {
+  if (warp == 0 || warp == 4) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
-    issue_product_led(leader, cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
-    issue_product_led(leader, cA, Tile{smem_u32(DS), 128, false}, Tile{smem_u32(X1), 128, true}, 128, 64, 0u);
-    issue_product_led(leader, cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
-    issue_product_led(leader, cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
+    if (warp == 0) {
+      issue_product_led(leader, cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
+      issue_product_led(leader, cA, Tile{smem_u32(DS), 128, false}, Tile{smem_u32(X1), 128, true}, 128, 64, 0u);
+    } else {
+      issue_product_led(leader, cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
+      issue_product_led(leader, cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
+    }
     umma_commit_led(leader, bar_mma);
     if (DELTA && tid == 0) {   // dv2 record: rows 64-127 of each DD atom are one atom of the 64-row image
       unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;

@@ -47,12 +47,14 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
   uint64_t* bar_dkb = &cs->bar[2];
+  uint64_t* bar_g1 = &cs->bar[3];     // first product group: two issuing warps
   constexpr uint32_t kCols = (V == 64) ? 256u : 512u;
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     mbar_init(bar_dkb, 1);
+    mbar_init(bar_g1, 2);
     fence_mbar_init();
     fence_proxy_async();
     mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u);
@@ -121,16 +123,23 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   // ---- group 1: [KK | k dw^T], dT / beta_s, T^T du
-  if (warp == 0) {
+  // (24 products: two warps issue half each, issuing is what the group costs)
+  if (warp == 0 || warp == 4) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
-    issue_product_led(leader, R0, Tile{smem_u32(T1), 128, false}, Tile{smem_u32(T1), 128, false}, 128, 128, 0u);
-    issue_product_led(leader, R1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(VT), 64, false}, 64, V, 0u);
-    issue_product_led(leader, R1, Tile{smem_u32(T1) + 8192, 128, false}, Tile{smem_u32(GK), 64, false}, 64, 128, 1u);
-    issue_product_led(leader, R2, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V, 64, 0u);
-    umma_commit_led(leader, bar_mma);
+    if (warp == 0) {
+      issue_product_led(leader, R0, Tile{smem_u32(T1), 128, false}, Tile{smem_u32(T1), 128, false}, 128, 128, 0u);
+      issue_product_led(leader, R2, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DV2t), 64, true}, V, 64, 0u);
+    } else {
+      issue_product_led(leader, R1, Tile{smem_u32(DV2t), 64, false}, Tile{smem_u32(VT), 64, false}, 64, V, 0u);
+      issue_product_led(leader, R1, Tile{smem_u32(T1) + 8192, 128, false}, Tile{smem_u32(GK), 64, false}, 64, 128, 1u);
+    }
+    umma_commit_led(leader, bar_g1);
   }
-  wait_products(bar_mma, ph, ctl, 422);
+  {
+    uint32_t ph1 = 0;
+    wait_products(bar_g1, ph1, ctl, 422);
+  }
   LETHE_PHASE("g1");
   const int c0 = half * 32;           // this half's 32 columns of every 64-column accumulator
   const bool live = (half == 0) || ((warp & 1) != 0);   // rows 0-31 have nothing right of column 31 in a triangle
