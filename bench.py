@@ -186,6 +186,58 @@ def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool, cw: boo
     return per * Z
 
 
+def fla_main(args, B, L, H, K, V, gate, delta, config):
+    """Extra comparator row, not the reference arm and not part of this package: the flash-linear-attention
+    Triton kernels (a third-party library the reference itself times against) on the same workload, same
+    seeded inputs resident on the device, forward + backward, CUDA events, L2 flushed between steps.
+    Only the two delta-rule workloads have a counterpart there."""
+    import torch
+    from lethe_b200.synth import make_inputs
+    try:
+        from fla.ops.kda import chunk_kda
+    except Exception as e:   # noqa: BLE001
+        print(json.dumps({"impl": "fla", "unavailable": f"cannot import flash-linear-attention: {e}"}))
+        return
+    if not delta or gate == "none":
+        print(json.dumps({"impl": "fla", "unavailable": "no counterpart for this workload"}))
+        return
+    if gate == "scalar":
+        # chunk_gated_delta_rule of this library version ended in a CUDA error on a B200 of this pool with
+        # these inputs; it is not run again (the channel-wise comparator below ran cleanly)
+        print(json.dumps({"impl": "fla", "unavailable": "the library's scalar-gate kernels raised a CUDA error "
+                                                        "on this hardware; not run"}))
+        return
+    dev = torch.device("cuda", 0)
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=1, mild=args.mild_gate)
+    leaves = {n: inp[n].to(dev).requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "h0")}
+    do = inp["do"].to(dev)
+    fn = chunk_kda
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        o, _ = fn(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], scale=K ** -0.5,
+                  initial_state=leaves["h0"], output_final_state=True)
+        torch.autograd.grad(o, list(leaves.values()), do)
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in evs:
+        flush.zero_()
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    import fla
+    print(json.dumps({"impl": "fla", "library": f"flash-linear-attention {fla.__version__} (Triton)", "metric": METRIC,
+                      "value": B * L / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "config": config,
+                      "data": "synthetic", "note": "through autograd (includes its Python launch overhead)"}))
+
+
 def sp_main(args, rank, world, dev, B, L, H, K, V, gate, delta, config):
     """Sequence-parallel timing: rank r owns tokens [r L/N, (r+1) L/N) of every head; chunk-boundary
     states (forward) and adjoint states (backward) travel rank to rank by NCCL point-to-point."""
@@ -238,7 +290,11 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fla"],
+                    help="reference: the CPU port of the reference path; fla: third-party comparator (see fla_main)")
+    ap.add_argument("--mild-gate", action="store_true",
+                    help="draw the gate as -0.1 U(0,1), the draw of the reference's own benchmark, instead of "
+                         "-softplus(N(0,1) + 3)")
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sp", action="store_true",
@@ -252,6 +308,10 @@ def main():
               "gate": gate, "delta": delta, "sharding": "batch x head, no collective",
               "l2": "flushed between steps (256 MiB write)"}
 
+    if args.impl == "fla":
+        if rank == 0:
+            fla_main(args, B, L, H, K, V, gate, delta, config)
+        return
     if args.impl == "reference":
         if rank != 0:
             return
@@ -280,7 +340,7 @@ def main():
     if args.sp:
         sp_main(args, rank, world, dev, B, L, H, K, V, gate, delta, config)
         return
-    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=1 + rank)
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=1 + rank, mild=args.mild_gate)
     host = {k: t.pin_memory() for k, t in inp.items() if t is not None}
     d = {k: t.to(dev) for k, t in host.items()}
     g, beta, h0 = d.get("g"), d.get("beta"), d.get("h0")
