@@ -8,8 +8,8 @@ Both callables take and return head-major chunked fp32 tensors ``[B, H, NT, C, .
 d_k = 128) and return fresh tensors, like the reference's.  They stage their arguments into the
 per-chunk records the kernels read (PyTorch is used for that restaging only) and run exactly one
 kernel of the backward call each: the adjoint state scan for K#1, the WY / triangular-inverse VJP for
-K#2.  The channel-wise ``K2FnCW`` with independent erase / write gates is not provided (the kernels
-tie both gates to one beta).
+K#2 (``k2_fn`` for the scalar gate, ``k2_fn_cw`` for the channel-wise gate with independent erase and
+write gates).
 """
 
 from __future__ import annotations
@@ -61,12 +61,18 @@ def _layout(B, H, L, V, gate):
     for n in ("ta", "w", "u", "p", "r", "hc", "vn", "ad"):
         off[n] = o
         o = al(o + (Z + B * H if n == "hc" else Z) * sz[n])
+    if gate == ops.GATE_CHANNEL:
+        sz["gt"], off["gt"] = 64 * 128 * 4, o
     sz2 = dict(rb=128 * V * 2, dh=128 * V * 2, dv2=64 * V * 2, dw=16384, dkb=64 * 128 * 4,
                dgb=(64 * 128 if gate == ops.GATE_CHANNEL else 64) * 4)
     off2, o = {}, 0
     for n in ("rb", "dh", "dv2", "dw", "dkb", "dgb"):
         off2[n] = o
         o = al(o + Z * sz2[n])
+    if gate == ops.GATE_CHANNEL:
+        for n, size in (("da", 8192), ("dm", 8192), ("dqp", 64 * 128 * 4)):
+            sz2[n], off2[n] = size, o
+            o = al(o + Z * size)
     return Z, sz, off, sz2, off2
 
 
@@ -157,3 +163,49 @@ def k2_fn(k: Tensor, v: Tensor, beta: Tensor, g2: Tensor, t_mat: Tensor, dw: Ten
     db = _tok(buf.dbeta[..., None])[..., 0]
     dg = _tok(buf.dg[..., None])[..., 0]
     return dk2.clone(), dv.clone(), db.clone(), dg.clone()
+
+
+def _gate_tile_image(G: Tensor) -> Tensor:
+    """[Z, 64, 128] fp32 cumulative log decay -> the record image the kernels read: element (row, col) at
+    row * 128 + (col ^ (row & 31))."""
+    Z = G.shape[0]
+    row = torch.arange(64, device=G.device)[:, None]
+    col = torch.arange(128, device=G.device)[None, :]
+    dst = (row * 128 + (col ^ (row & 31))).reshape(-1)
+    img = torch.empty(Z, 64 * 128, dtype=torch.float32, device=G.device)
+    img[:, dst] = G.reshape(Z, -1)
+    return img
+
+
+def k2_fn_cw(k: Tensor, v: Tensor, b: Tensor, w: Tensor, g2: Tensor, t_mat: Tensor, dwy: Tensor, du: Tensor
+             ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Channel-wise K#2 with independent per-channel erase gate ``b`` and write gate ``w`` (reference
+    ``k2_wy_vjp_cw_ref``, ``gdn2_assemble.py:407-473``): returns ``(dk2, dv, db, dw, dg)``, ``dg`` after the
+    in-chunk reverse cumulative sum, all head-major chunked.  ``g2 [B,H,NT,C,K]`` is the in-chunk cumulative
+    decay in log2 units."""
+    B, H, NT, C, K = k.shape
+    V = v.shape[-1]
+    if C != 64 or K != 128 or V not in (64, 128) or g2.dim() != 5:
+        raise ops.GdnError("lethe_gdn: k2_fn_cw needs the channel-wise gate, C = 64, d_k = 128, d_v in {64, 128}")
+    dev, f32 = k.device, torch.float32
+    L = NT * C
+    buf = ops.GdnBuffers(B, L, H, K, V, ops.GATE_CHANNEL, 2, dev)
+    Z, sz, off, sz2, off2 = _layout(B, H, L, V, ops.GATE_CHANNEL)
+    ta = torch.zeros(B, H, NT, 128, 64, dtype=torch.float16, device=dev)
+    ta[..., :64, :] = t_mat.half()
+    _record_view(buf.saved, off["ta"], sz["ta"], Z, torch.float16).copy_(to_image(ta).reshape(Z, -1))
+    _record_view(buf.saved, off["gt"], sz["gt"], Z, f32).copy_(_gate_tile_image((g2.to(f32) * LN2).reshape(Z, C, K)))
+    _record_view(buf.scratch, off2["dv2"], sz2["dv2"], Z, torch.float16).copy_(to_image(du.half()).reshape(Z, -1))
+    _record_view(buf.scratch, off2["dw"], sz2["dw"], Z, torch.float16).copy_(to_image(dwy.half()).reshape(Z, -1))
+    _record_view(buf.scratch, off2["dkb"], sz2["dkb"], Z, f32).zero_()
+    _record_view(buf.scratch, off2["dgb"], sz2["dgb"], Z, f32).zero_()
+    k16 = _untok(k).to(torch.bfloat16)
+    v16 = _untok(v).to(torch.bfloat16)
+    g_cum = g2.to(f32) * LN2
+    g_tok = torch.diff(g_cum, dim=-2, prepend=torch.zeros_like(g_cum[..., :1, :]))
+    g_t = _untok(g_tok)
+    b_t, w_t = _untok(b.to(f32)), _untok(w.to(f32))
+    dov = torch.zeros(B, L, H, V, dtype=torch.bfloat16, device=dev)
+    ops.backward_into(buf, k16, k16, v16, g_t, None, None, dov, None, 1.0, kernel_mask=8, b_gate=b_t, w_gate=w_t)
+    return (_tok(buf.dk.to(f32)).clone(), _tok(buf.dv.to(f32)).clone(), _tok(buf.db).clone(), _tok(buf.dw).clone(),
+            _tok(buf.dg).clone())

@@ -234,3 +234,40 @@ def test_kernel_plugins_k1_k2():
                 dg=scale_rel(dg.cpu(), dg_ref))
     report("plugins k1/k2", errs)
     assert max(errs.values()) <= 5e-3, errs
+
+
+def test_kernel_plugin_k2_cw_full_gates():
+    """The channel-wise K2FnCW adapter (independent erase / write gates) against autograd through the
+    WY transform it differentiates (reference ``k2_wy_vjp_cw_ref``, ``gdn2_assemble.py:407-473``)."""
+    import math
+
+    from lethe_b200.plugins import k2_fn_cw
+
+    B, H, NT, C, K, V = 1, 2, 2, 64, 128, 64
+    gen = torch.Generator().manual_seed(41)
+    f64 = torch.float64
+    k = torch.randn(B, H, NT, C, K, generator=gen, dtype=f64)
+    k = (k / k.norm(dim=-1, keepdim=True)).bfloat16().double()
+    v = torch.randn(B, H, NT, C, V, generator=gen, dtype=f64).bfloat16().double()
+    b = torch.randn(B, H, NT, C, K, generator=gen, dtype=f64).sigmoid().float().double()
+    w = torch.randn(B, H, NT, C, V, generator=gen, dtype=f64).sigmoid().float().double()
+    g = -0.1 * torch.rand(B, H, NT, C, K, generator=gen, dtype=f64)
+    g2 = (torch.cumsum(g, dim=-2) / math.log(2.0)).float().double()
+    du = torch.randn(B, H, NT, C, V, generator=gen, dtype=f64).half().double()
+    dwy = torch.randn(B, H, NT, C, K, generator=gen, dtype=f64).half().double()
+    leaves = [t.clone().requires_grad_(True) for t in (k, v, b, w, g2)]
+    kl, vl, bl, wl, gl = leaves
+    rel = torch.exp2(torch.clamp(gl[..., :, None, :] - gl[..., None, :, :], max=0.0))      # [.., i, s, d], s <= i used
+    M = torch.tril(torch.einsum("...id,...sd,...isd->...is", bl * kl, kl, rel), -1)
+    T = torch.linalg.inv(torch.eye(C, dtype=f64) + M)
+    u = T @ (wl * vl)
+    wy = T @ (bl * torch.exp2(gl) * kl)
+    grads = torch.autograd.grad((u * du).sum() + (wy * dwy).sum(), leaves)
+    dg_ref = torch.flip(torch.cumsum(torch.flip(grads[4], [-2]), -2), [-2]) / math.log(2.0)
+    cu = lambda t: t.float().cuda()  # noqa: E731
+    dk2, dv, db, dw, dg = k2_fn_cw(cu(k), cu(v), cu(b), cu(w), cu(g2), cu(T.detach()), cu(dwy), cu(du))
+    errs = {"dk2": scale_rel(dk2.double().cpu(), grads[0]), "dv": scale_rel(dv.double().cpu(), grads[1]),
+            "db": scale_rel(db.double().cpu(), grads[2]), "dw": scale_rel(dw.double().cpu(), grads[3]),
+            "dg": scale_rel(dg.double().cpu(), dg_ref)}
+    report("plugin k2 cw (full gates)", errs)
+    assert max(errs.values()) <= 5e-3, errs
