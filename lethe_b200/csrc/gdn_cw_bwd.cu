@@ -709,14 +709,30 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     float* __restrict__ dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
     float* __restrict__ dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
     constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
+    // the records of the next eight rows are requested before the current eight are worked on
+    float npart[8], ndgb[8], ndkb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      npart[j] = dqp_g[ridx(ibase + j, d)];
+      ndgb[j] = dgb_g[ridx(ibase + j, d)];
+      ndkb[j] = dkb_g[ridx(ibase + j, d)];
+    }
 #pragma unroll 1
     for (int i0 = ibase; i0 < ibase + 32; i0 += 8) {
       float part8[8], dgb8[8], dkb8[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        part8[j] = dqp_g[ridx(i0 + j, d)];
-        dgb8[j] = dgb_g[ridx(i0 + j, d)];
-        dkb8[j] = dkb_g[ridx(i0 + j, d)];
+        part8[j] = npart[j];
+        dgb8[j] = ndgb[j];
+        dkb8[j] = ndkb[j];
+      }
+      if (i0 + 8 < ibase + 32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          npart[j] = dqp_g[ridx(i0 + 8 + j, d)];
+          ndgb[j] = dgb_g[ridx(i0 + 8 + j, d)];
+          ndkb[j] = dkb_g[ridx(i0 + 8 + j, d)];
+        }
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
