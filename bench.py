@@ -40,6 +40,8 @@ WORKLOADS = {
     "gdn_scalar_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "scalar", True),
     "gdn_scalar_B4_H8_L4096_dk128_dv64": (4, 4096, 8, 128, 64, "scalar", True),     # > L2: for ncu DRAM figures
     "kda_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "channel", True),          # configuration 2
+    # the reference's full six-input op: independent per-channel erase gate b and write gate w (delta = 2)
+    "gdn2full_B2_H8_L2048_dk128_dv128": (2, 2048, 8, 128, 128, "channel", 2),
     "gla_B4_H16_L4096_dk128_dv128": (4, 4096, 16, 128, 128, "channel", False),       # configuration 3
     "kda_B4_H8_L4096_dk128_dv128": (4, 4096, 8, 128, 128, "channel", True),          # > L2: for ncu DRAM figures
     "kda_B2_H32_L8192_dk128_dv128": (2, 8192, 32, 128, 128, "channel", True),        # configuration 4a, one GPU's share
@@ -111,7 +113,8 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 
     B, L, H, K, V, gate, delta = WORKLOADS[workload]
     hs = 1
-    inp = make_inputs(1, L, hs, K, V, gate=gate, delta=delta, seed=0)
+    # (the full six-input op is timed as its one-beta special case: same chunkwise work on the CPU)
+    inp = make_inputs(1, L, hs, K, V, gate=gate, delta=bool(delta), seed=0)
     f = {k: (None if t is None else t.float()) for k, t in inp.items()}
 
     def run():
@@ -140,11 +143,11 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 # every kernel's traffic grows in proportion to its chunks).  Keyed by (kernel, gate, d_v, delta); the
 # channel-wise "stageb" and "wy" are two launches each, summed.  Absent combinations report null.
 NCU_DRAM_BYTES_PER_CHUNK = {
-    ("stageb", "scalar", 64, True): (201.9e6 + 111.8e6) / 2048,
-    ("prepare", "scalar", 64, True): (85.0e6 + 128.3e6) / 2048,
-    ("wy", "scalar", 64, True): (203.0e6 + 34.6e6) / 2048,
-    ("scan_bwd", "scalar", 64, True): (101.7e6 + 13.9e6) / 2048,
-    ("prepare", "channel", 128, True): (168.4e6 + 248.4e6) / 2048,
+    ("stageb", "scalar", 64, True): (202.0e6 + 115.6e6) / 2048,
+    ("prepare", "scalar", 64, True): (85.0e6 + 128.7e6) / 2048,
+    ("wy", "scalar", 64, True): (203.0e6 + 33.5e6) / 2048,
+    ("scan_bwd", "scalar", 64, True): (101.7e6 + 13.7e6) / 2048,
+    ("prepare", "channel", 128, True): (168.4e6 + 247.2e6) / 2048,
 }
 
 
@@ -340,7 +343,8 @@ def main():
     if args.sp:
         sp_main(args, rank, world, dev, B, L, H, K, V, gate, delta, config)
         return
-    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=1 + rank, mild=args.mild_gate)
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=bool(delta), seed=1 + rank, mild=args.mild_gate,
+                      full=(delta == 2))
     host = {k: t.pin_memory() for k, t in inp.items() if t is not None}
     d = {k: t.to(dev) for k, t in host.items()}
     g, beta, h0 = d.get("g"), d.get("beta"), d.get("h0")
@@ -349,9 +353,11 @@ def main():
     buf = ops.GdnBuffers(B, L, H, K, V, gate_code, delta, dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    gates = dict(b_gate=d.get("b"), w_gate=d.get("w"))     # per-channel gates of the full op, else None
+
     def step(mask_f=0, mask_b=0):
-        ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, mask_f)
-        ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale, mask_b)
+        ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, mask_f, **gates)
+        ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale, mask_b, **gates)
 
     def barrier():
         torch.cuda.synchronize()
@@ -386,14 +392,14 @@ def main():
     names_b = [("bwd_pre", 1), ("scan_bwd", 2), ("stageb", 4)] + ([("wy", 8)] if delta else [])
     step()
     for name, m in names_f:
-        kern[name] = timed(lambda m=m: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, m),
+        kern[name] = timed(lambda m=m: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, m, **gates),
                            max(args.steps, 10), 3)
     for name, m in names_b:
         kern[name] = timed(lambda m=m: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"],
-                                                         None, scale, m), max(args.steps, 10), 3)
-    fwd_ms = timed(lambda: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale), args.steps, 3)
-    bwd_ms = timed(lambda: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale),
-                   args.steps, 3)
+                                                         None, scale, m, **gates), max(args.steps, 10), 3)
+    fwd_ms = timed(lambda: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, **gates), args.steps, 3)
+    bwd_ms = timed(lambda: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale,
+                                             **gates), args.steps, 3)
     ops.check_status(buf.status)
 
     # ---- end to end through the public host API: pinned host buffers in, pinned host buffers out, every
@@ -431,8 +437,14 @@ def main():
         for n in ("q", "k", "v", "g", "beta", "h0"):
             leaves[n] = host[n].to(dev, non_blocking=True).requires_grad_(True) if n in host else None
         do_d = host["do"].to(dev, non_blocking=True)
-        o, hT = ops.gdn_chunk(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], leaves["h0"],
-                              scale=scale)
+        if delta == 2:
+            for n in ("b", "w"):
+                leaves[n] = host[n].to(dev, non_blocking=True).requires_grad_(True)
+            o, hT = ops.gdn_chunk_full(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["b"], leaves["w"],
+                                       leaves["h0"], scale=scale)
+        else:
+            o, hT = ops.gdn_chunk(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], leaves["h0"],
+                                  scale=scale)
         names = [n for n in leaves if leaves[n] is not None]
         grads = torch.autograd.grad(o, [leaves[n] for n in names], do_d)
         res = [("o", o.detach()), ("hT", hT.detach())] + [("d" + n, t) for n, t in zip(names, grads)]

@@ -32,7 +32,10 @@ class _Slot:
         if gate != ops.GATE_NONE:
             gshape = (B, L, H, K) if gate == ops.GATE_CHANNEL else (B, L, H)
             self.inp["g"] = torch.empty(gshape, dtype=f32, device=device)
-        if delta:
+        if int(delta) == 2:
+            self.inp["b"] = torch.empty(B, L, H, K, dtype=f32, device=device)
+            self.inp["w"] = torch.empty(B, L, H, V, dtype=f32, device=device)
+        elif delta:
             self.inp["beta"] = torch.empty(B, L, H, dtype=f32, device=device)
         if has_h0:
             self.inp["h0"] = torch.empty(B, H, K, V, dtype=f32, device=device)
@@ -50,6 +53,8 @@ class _Slot:
             out["dg"] = b.dg
         if b.dbeta is not None:
             out["dbeta"] = b.dbeta
+        if b.db is not None:
+            out["db"], out["dw"] = b.db, b.dw
         return out
 
 
@@ -58,8 +63,10 @@ class HostPipeline:
 
     * ``host_in``: pinned host tensors ``q, k [B,L,H,K]``, ``v, do [B,L,H,V]`` (bf16), ``g`` (fp32,
       ``[B,L,H]`` or ``[B,L,H,K]``; absent for no gate), ``beta [B,L,H]`` (fp32; absent drops the delta
-      term), optional ``h0``, ``dhT`` ``[B,H,K,V]`` fp32.  The set of names must be the same for every step.
-    * ``host_out``: pinned host tensors that receive ``o, hT, dq, dk, dv, dg, dbeta, dh0`` (any subset).
+      term) or, for a pipeline made with ``delta=2``, the per-channel gates ``b [B,L,H,K]``, ``w [B,L,H,V]``;
+      optional ``h0``, ``dhT`` ``[B,H,K,V]`` fp32.  The set of names must be the same for every step.
+    * ``host_out``: pinned host tensors that receive ``o, hT, dq, dk, dv, dg, dbeta`` (``db, dw`` with
+      ``delta=2``), ``dh0`` (any subset).
 
     A host buffer handed to ``submit`` must not be touched until ``drain()`` returns.  Steps complete
     in submission order.
@@ -108,9 +115,10 @@ class HostPipeline:
                     self.s_run.wait_event(slot.stored)
                 if self.pre_run is not None:
                     self.pre_run()
-                ops.forward_into(slot.buf, i["q"], i["k"], i["v"], i.get("g"), i.get("beta"), i.get("h0"), self.scale)
+                ops.forward_into(slot.buf, i["q"], i["k"], i["v"], i.get("g"), i.get("beta"), i.get("h0"), self.scale,
+                                 b_gate=i.get("b"), w_gate=i.get("w"))
                 ops.backward_into(slot.buf, i["q"], i["k"], i["v"], i.get("g"), i.get("beta"), i.get("h0"), i["do"],
-                                  i.get("dhT"), self.scale)
+                                  i.get("dhT"), self.scale, b_gate=i.get("b"), w_gate=i.get("w"))
                 slot.computed.record(self.s_run)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(slot.computed)

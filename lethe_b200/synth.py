@@ -10,7 +10,7 @@ import torch
 import torch.nn.functional as F
 
 
-def make_inputs(B, L, H, K, V, *, gate="scalar", delta=True, with_h0=True, seed=0, mild=False):
+def make_inputs(B, L, H, K, V, *, gate="scalar", delta=True, with_h0=True, seed=0, mild=False, full=False):
     """Returns a dict of CPU tensors: q, k, v, do (bf16); g, beta, h0 (fp32; None when absent)."""
     gen = torch.Generator().manual_seed(seed)
     q = torch.randn(B, L, H, K, generator=gen)
@@ -26,6 +26,11 @@ def make_inputs(B, L, H, K, V, *, gate="scalar", delta=True, with_h0=True, seed=
         g = -F.softplus(torch.randn(*gshape, generator=gen) + 3.0)
     do = torch.randn(B, L, H, V, generator=gen)
     h0 = 0.1 * torch.randn(B, H, K, V, generator=gen)
-    return dict(q=q.bfloat16(), k=k.bfloat16(), v=v.bfloat16(), do=do.bfloat16(),
-                g=None if gate == "none" else g, beta=beta if delta else None,
-                h0=h0 if with_h0 else None)
+    out = dict(q=q.bfloat16(), k=k.bfloat16(), v=v.bfloat16(), do=do.bfloat16(),
+               g=None if gate == "none" else g, beta=beta if delta else None,
+               h0=h0 if with_h0 else None)
+    if full:   # independent per-channel erase gate b [B,L,H,K] and write gate w [B,L,H,V] instead of beta
+        out["beta"] = None
+        out["b"] = torch.randn(B, L, H, K, generator=gen).sigmoid()
+        out["w"] = torch.randn(B, L, H, V, generator=gen).sigmoid()
+    return out
