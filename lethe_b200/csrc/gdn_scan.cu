@@ -37,7 +37,9 @@ scan_kernel(const Problem p) {
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                        ~static_cast<uintptr_t>(1023));
   unsigned char* Pst = sm;                          // kStages x 32 KB
-  unsigned char* XB = sm + kStages * 32768;         // 4 KB: x as a (16 x 128) operand, 2 atoms of 2 KB
+  // 4 KB: x as the B operand, contracted along its rows (row k = key channel k, 16 columns = 32 bytes):
+  // atoms of 8 rows x 32 bytes with the 32-byte swizzle, so that thread k stores its row as two 16-byte pieces
+  unsigned char* XB = sm + kStages * 32768;
   CtaShared* cs = reinterpret_cast<CtaShared*>(XB + 4096);
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -88,8 +90,8 @@ scan_kernel(const Problem p) {
       const uint32_t leader = elect_leader();
       // A = the P stage (contracted along its columns forward, along its rows for the adjoint),
       // B = the state operand; one 16-element contraction step moves each by a fixed amount
-      const uint64_t b_desc0 = make_desc(smem_u32(XB), 16u, 1024u);
-      const uint32_t idesc = make_idesc(128, kVs, ADJOINT, false);
+      const uint64_t b_desc0 = make_desc_sw32(smem_u32(XB), 16u, 256u);
+      const uint32_t idesc = make_idesc(128, kVs, ADJOINT, true);
       const uint32_t acc = tmem + static_cast<uint32_t>(m * kVs);
       for (int it = 0; it < NT; ++it) {
         const int st = it % kStages;
@@ -104,7 +106,7 @@ scan_kernel(const Problem p) {
           // byte offsets of contraction step j, in the descriptors' 16-byte units
           const uint32_t aoff = ADJOINT ? static_cast<uint32_t>(j * 2048) >> 4
                                         : static_cast<uint32_t>((j >> 2) * 16384 + (j & 3) * 32) >> 4;
-          const uint32_t boff = static_cast<uint32_t>((j >> 2) * 2048 + (j & 3) * 32) >> 4;
+          const uint32_t boff = static_cast<uint32_t>(j * 512) >> 4;     // 16 rows of 32 bytes per step
           umma_led(leader, acc, a_desc0 + aoff, b_desc0 + boff, idesc, jj > 0 ? 1u : 0u);
         }
         umma_commit_led(leader, bar_mma);
@@ -146,9 +148,11 @@ scan_kernel(const Problem p) {
       ST(0)
       if (has_p) {
         // critical path: the state as a tensor-core operand
-#pragma unroll
-        for (int n = 0; n < kVs; ++n)
-          *reinterpret_cast<__half*>(XB + sw128_off(n, tid, kVs)) = __float2half_rn(x[n]);
+        {
+          const int sw = (tid >> 2) & 1;     // 32-byte swizzle: the two 16-byte pieces of rows 4-7 of an atom swap
+          *reinterpret_cast<uint4*>(XB + tid * 32 + (sw << 4)) = pack8_f16(x);
+          *reinterpret_cast<uint4*>(XB + tid * 32 + ((sw ^ 1) << 4)) = pack8_f16(x + 8);
+        }
         fence_proxy_async();
         tc_fence_before();
         step_arrive();
