@@ -153,8 +153,15 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
 }
 
 // ---------------------------------------------------------------------------------------------
-// Stage B.  Accumulator regions (TMEM columns): cA [0,128) dv2 then dq_intra; cB [128,256)
-// [do; dv2] h^T; cC [256,320) do v_new^T; cD [320,448) Stage-B dk.
+// Stage B in three product groups, so that 256 TMEM columns and 107 KB of shared memory suffice at
+// d_v = 64 and two CTAs share an SM (the loads and the stores of one chunk overlap the other's work):
+//   group 1 : k dh (lanes 64-127), A^T do (lanes 64-127), dA = do v_new^T (lanes 0-63)
+//   group 2a: [do; dv2] h^T (dq_inter | -dw), dAr k (dq_intra)
+//   group 2b: dAr^T q, v_new dh^T  ->  Stage-B dk = dAr^T q + dec_end (v_new dh^T)
+// The decay to the chunk end is applied in the epilogues in fp32 (kd = k dec_end and dec_end v_new are
+// never formed as operands).  Operands that have to land in lanes 64-127 are 64-row tiles read through a
+// 128-row view that starts 64 rows early; rows 0-63 of such a view are the neighbouring tile, and what
+// they produce (lanes 0-63 of that accumulator) is never read.
 // ---------------------------------------------------------------------------------------------
 template <int V, bool DELTA>
 __global__ void __launch_bounds__(256)
@@ -163,20 +170,21 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
                   const __grid_constant__ CUtensorMap mdk) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024(smem_raw);
-  unsigned char* X1 = sm;                       // 32 KB: rows 0-63 k, rows 64-127 kd
-  unsigned char* QT = X1 + 32768;               // 16 KB: q (64 x 128)
-  unsigned char* DD = QT + 16384;               // V*256: rows 0-63 do, rows 64-127 dv2
-  unsigned char* TAt = DD + V * 256;            // 16 KB: [T | A]
-  unsigned char* VNt = TAt + 16384;             // V*256: rows 0-63 v_new, rows 64-127 dec_end * v_new
-  unsigned char* Ht = VNt + V * 256;            // V*256: h entering the chunk
+  unsigned char* QT = sm;                       // 16 KB: q (64 x 128)
+  unsigned char* KT = QT + 16384;               // 16 KB: k (64 x 128), directly behind q (early view reads q)
+  unsigned char* DD = KT + 16384;               // V*256: rows 0-63 do, rows 64-127 dv2
+  unsigned char* DS = DD + V * 256;             // 8 KB: scale * dA * ratio (64 x 64)
+  unsigned char* AT = DS + 8192;                // 8 KB: A (64 x 64), directly behind DS (early view reads DS)
+  unsigned char* VN = AT + 8192;                // V*128: v_new (64 x V); 128-row views run on into Ht
+  unsigned char* Ht = VN + V * 128;             // V*256: h entering the chunk
   unsigned char* DHt = Ht + V * 256;            // V*256: dh
-  unsigned char* DS = DHt + V * 256;            // 16 KB: rows 0-63 scale*dA*ratio, rows 64-127 zero
-  float* fs = reinterpret_cast<float*>(DS + 16384);
+  float* fs = reinterpret_cast<float*>(DHt + V * 256);
   float* Gs = fs;            // [64]
   float* t3p = fs + 64;      // [2][64] per column half: column sum of E plus dde row sum
   float* ddep = fs + 192;    // [2][64] per column half: dde row sums
   float* t2p = fs + 320;     // [2][64] per column half: row sums of dA o A
   float* t1p = fs + 448;     // [2][64] per column half: <dq_inter, q>
+  float* decs = fs + 576;    // [64] exp(G_last - G_i)
   float* tmp = fs + 640;     // [16]
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 656);
 
@@ -187,27 +195,29 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  constexpr uint32_t kCols = (V == 64) ? 256u : 512u;
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 2);     // two issuing warps commit every product group
     fence_mbar_init();
     fence_proxy_async();
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u);
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 8192u + V * 128u + V * 256u + V * 256u);
     for (int a = 0; a < 2; ++a) {
-      tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(KT + a * 8192, &mk, bar_load, a * 64, h, c * kC, b);
       tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
     }
     for (int a = 0; a < V / 64; ++a) {
       tma_load_4d(DD + a * 16384, &mdo, bar_load, a * 64, h, c * kC, b);
-      bulk_g2s(VNt + a * 16384, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn + a * 8192, 8192, bar_load);
+      bulk_g2s(VN + a * 8192, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn + a * 8192, 8192, bar_load);
     }
-    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    // the [T; A] record is 128 rows of one 64-column atom: its second half is the image of A
+    bulk_g2s(AT, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta + 8192, 8192, bar_load);
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
   }
   if (warp == 0) {
-    tmem_alloc(&cs->tmem_slot, 512);
+    tmem_alloc(&cs->tmem_slot, kCols);
     tmem_relinquish();
   }
   LETHE_PHASE_INIT();
@@ -218,55 +228,47 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
-  const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
+  // group 1: k dh, A^T do, dA;  group 2a: [do; dv2] h^T, dAr k;  group 2b: dAr^T q, v_new dh^T
+  const uint32_t g1D = tmem, g1A = tmem + V, g1C = tmem + 2 * V;
+  const uint32_t cB = tmem, cA2 = tmem + 128, cD1 = tmem, cD2 = tmem + 128;
 
   const float G = chunk_cumsum(gval, tid, tmp);
   if (tid < 64) Gs[tid] = G;
   __syncthreads();
   const float Glast = Gs[63];
+  if (tid < 64) decs[tid] = __expf(Glast - G);
 
   LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 411);
   LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
-    float x[8], y[8];
-    unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
-    tile_st_chunk(X1, r, ch, 128, pack8_f16(x));
-    const float de = __expf(Glast - Gs[r]);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) y[i] = x[i] * de;
-    tile_st_chunk(X1, 64 + r, ch, 128, pack8_f16(y));
+    float x[8];
+    unpack8_bf16(tile_ld_chunk(KT, r, ch, 64), x);
+    tile_st_chunk(KT, r, ch, 64, pack8_f16(x));
     unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
-    if (ch < 8) tile_st_chunk(DS, 64 + r, ch, 128, make_uint4(0, 0, 0, 0));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(DD, r, ch, 128), x);
     tile_st_chunk(DD, r, ch, 128, pack8_f16(x));
-    unpack8_f16(tile_ld_chunk(VNt, r, ch, 128), x);
-    const float de = __expf(Glast - Gs[r]);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] *= de;
-    tile_st_chunk(VNt, 64 + r, ch, 128, pack8_f16(x));
   }
   sync_for_issue();
   LETHE_PHASE("convert");
 
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  // ---- group 1: kd dh (rows 64-127 of cD), A^T do (rows 64-127 of cA), dA = do v_new^T (rows 0-63 of cC)
-  // (two warps issue, half of the group's products each: issuing is what the group costs)
+  // ---- group 1 (two warps issue, half of the group's products each)
   if (warp == 0 || warp == 4) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
     if (warp == 0) {
-      issue_product_led(leader, cD, Tile{smem_u32(X1), 128, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
+      issue_product_led(leader, g1D, Tile{smem_u32(KT) - 8192, 64, false}, Tile{smem_u32(DHt), 128, true}, V, 128, 0u);
     } else {
-      issue_product_led(leader, cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
-      issue_product_led(leader, cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 128, false}, 64, V, 0u);
+      issue_product_led(leader, g1A, Tile{smem_u32(AT) - 8192, 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 0u);
+      issue_product_led(leader, g1C, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VN), 64, false}, 64, V, 0u);
     }
     umma_commit_led(leader, bar_mma);
   }
@@ -286,24 +288,26 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("g1");
   if (tq >= 64) {
     const int r = tq - 64;
+    const float de = decs[r];
     float t3 = 0.f, dde = 0.f;
     __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
 #pragma unroll
     for (int jj = 0; jj < V / 64; ++jj) {
       const int jb = half * (V / 64) + jj;
       float d[32], d1[32];
-      tmem_ld32(cA + lane_base + jb * 32, d);
-      tmem_ld32(cD + lane_base + jb * 32, d1);
+      tmem_ld32(g1A + lane_base + jb * 32, d);
+      tmem_ld32(g1D + lane_base + jb * 32, d1);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float vn[8];
-        unpack8_f16(tile_ld_chunk(VNt, r, jb * 4 + i, 128), vn);
+        unpack8_f16(tile_ld_chunk(VN, r, jb * 4 + i, 64), vn);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
+          const float kd_dh = de * d1[8 * i + e];            // (k dec_end) dh
           t3 += vn[e] * d[8 * i + e];
-          dde += vn[e] * d1[8 * i + e];
-          d[8 * i + e] += d1[8 * i + e];
+          dde += vn[e] * kd_dh;
+          d[8 * i + e] += kd_dh;
         }
         const uint4 pk = pack8_f16(d + 8 * i);
         tile_st_chunk(DD, 64 + r, jb * 4 + i, 128, pk);
@@ -315,7 +319,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   } else {
     const int r = tq;
     float d[32];
-    tmem_ld32(cC + lane_base + half * 32, d);
+    tmem_ld32(g1C + lane_base + half * 32, d);
     tmem_ld_wait();
     const float Gr = Gs[r];
     float t2 = 0.f;
@@ -323,7 +327,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     for (int q = 0; q < 4; ++q) {
       const int s8 = half * 4 + q;
       float a[8], y[8];
-      unpack8_f16(tile_ld_chunk(TAt, 64 + r, s8, 128), a);   // A[r, s] (already holds scale * ratio)
+      unpack8_f16(tile_ld_chunk(AT, r, s8, 64), a);          // A[r, s] (already holds scale * ratio)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int s = s8 * 8 + i;
@@ -331,23 +335,21 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
         t2 += da * a[i];
         y[i] = (s <= r) ? p.scale * __expf(Gr - Gs[s]) * da : 0.f;
       }
-      tile_st_chunk(DS, r, s8, 128, pack8_f16(y));
+      tile_st_chunk(DS, r, s8, 64, pack8_f16(y));
     }
     t2p[half * 64 + r] = t2;
   }
   sync_for_issue();
   LETHE_PHASE("epi1");
 
-  // ---- group 2: cB = [do; dv2] h^T;  cA = dAr k (rows 0-63 dq_intra);  cD = dAr^T q + (dec v_new) dh^T
+  // ---- group 2a: cB = [do; dv2] h^T;  cA2 = dAr k (lanes 0-63: dq_intra)
   if (warp == 0 || warp == 4) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
     if (warp == 0) {
       issue_product_led(leader, cB, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(Ht), 128, false}, 128, V, 0u);
-      issue_product_led(leader, cA, Tile{smem_u32(DS), 128, false}, Tile{smem_u32(X1), 128, true}, 128, 64, 0u);
     } else {
-      issue_product_led(leader, cD, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
-      issue_product_led(leader, cD, Tile{smem_u32(VNt) + 8192, 128, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 1u);
+      issue_product_led(leader, cA2, Tile{smem_u32(DS), 64, false}, Tile{smem_u32(KT), 64, true}, 128, 64, 0u);
     }
     umma_commit_led(leader, bar_mma);
     if (DELTA && tid == 0) {   // dv2 record: rows 64-127 of each DD atom are one atom of the 64-row image
@@ -359,26 +361,21 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   LETHE_PHASE("issue2");
   wait_products(bar_mma, ph, ctl, 413);
   LETHE_PHASE("g2");
-  // Every operand tile is dead now: the outputs are staged in them as the images their consumers read
-  // and leave by bulk / tensor-map stores (row-per-thread stores straight from registers would touch
-  // 32 lines per instruction).
+  // The operand tiles of this group are dead now: dq and dw are staged in them as the images their
+  // consumers read and leave by tensor-map / bulk stores.
   if (tid == 0) bulk_wait_read();
   __syncthreads();
-  unsigned char* SQ = X1;            // dq, bf16 64 x 128 (two atoms)
-  unsigned char* SK = DD;            // delta: fp32 dk partial, 32 KB (runs on into the next tiles); else dk bf16
-  unsigned char* SW = Ht;            // dw, fp16 64 x 128
+  unsigned char* SQ = KT;            // dq, bf16 64 x 128 (two atoms)
+  unsigned char* SW = DD;            // dw, fp16 64 x 128
   if (tq < 64) {
     const int r = tq;
     const float sg = p.scale * __expf(Gs[r]);
     float t1 = 0.f;
-    // fp32 dk partial for the WY kernel: four 32-column blocks of [row][eight 16-byte pieces], piece c
-    // of row r stored at c ^ (r & 7), so that the record can be read back from shared memory row-wise
-    float* dkb_s = reinterpret_cast<float*>(SK) + r * 32;
 #pragma unroll 1
     for (int jb = 2 * half; jb < 2 * half + 2; ++jb) {
       float dqg[32], dqi[32];
       tmem_ld32(cB + lane_base + jb * 32, dqg);
-      tmem_ld32(cA + lane_base + jb * 32, dqi);
+      tmem_ld32(cA2 + lane_base + jb * 32, dqi);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -391,18 +388,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
           o8[e] = a + dqi[8 * i + e];
         }
         tile_st_chunk(SQ, r, jb * 4 + i, 64, pack8_bf16(o8));
-      }
-      float dkv[32];
-      tmem_ld32(cD + lane_base + jb * 32, dkv);
-      tmem_ld_wait();
-      if (DELTA) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<float4*>(dkb_s + jb * 2048 + 4 * (i ^ (r & 7))) =
-              make_float4(dkv[4 * i], dkv[4 * i + 1], dkv[4 * i + 2], dkv[4 * i + 3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) tile_st_chunk(SK, r, jb * 4 + i, 64, pack8_bf16(dkv + 8 * i));
       }
     }
     t1p[half * 64 + r] = t1;
@@ -419,19 +404,65 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
       for (int i = 0; i < 4; ++i) tile_st_chunk(SW, r, jb * 4 + i, 64, pack8_f16(d + 8 * i));
     }
   }
+  sync_for_issue();
+  LETHE_PHASE("epi2a");
+
+  // ---- group 2b: cD1 = dAr^T q;  cD2 = v_new dh^T  (lanes 0-63)
+  if (warp == 0 || warp == 4) {
+    tc_fence_after();
+    const uint32_t leader = elect_leader();
+    if (warp == 0) {
+      issue_product_led(leader, cD1, Tile{smem_u32(DS), 64, true}, Tile{smem_u32(QT), 64, true}, 128, 64, 0u);
+    } else {
+      issue_product_led(leader, cD2, Tile{smem_u32(VN), 64, false}, Tile{smem_u32(DHt), 128, false}, 128, V, 0u);
+    }
+    umma_commit_led(leader, bar_mma);
+    if (tid == 0) {
+      for (int a = 0; a < 2; ++a) tma_store_4d(&mdq, SQ + a * 8192, a * 64, h, c * kC, b);
+      if (DELTA) bulk_s2g(p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, SW, 16384);
+      bulk_commit();
+    }
+  }
+  wait_products(bar_mma, ph, ctl, 414);
+  LETHE_PHASE("g2b");
+  __syncthreads();                   // every thread is past the products: h / dh become the dk staging tile
+  unsigned char* SK = Ht;            // delta: fp32 dk partial, 32 KB (runs on into dh); else dk bf16
+  if (tq < 64) {
+    const int r = tq;
+    const float de = decs[r];
+    // fp32 dk partial for the WY kernel: four 32-column blocks of [row][eight 16-byte pieces], piece c
+    // of row r stored at c ^ (r & 7), so that the record can be read back from shared memory row-wise
+    float* dkb_s = reinterpret_cast<float*>(SK) + r * 32;
+#pragma unroll 1
+    for (int jb = 2 * half; jb < 2 * half + 2; ++jb) {
+      float dkv[32], dkd[32];
+      tmem_ld32(cD1 + lane_base + jb * 32, dkv);
+      tmem_ld32(cD2 + lane_base + jb * 32, dkd);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) dkv[e] += de * dkd[e];
+      if (DELTA) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<float4*>(dkb_s + jb * 2048 + 4 * (i ^ (r & 7))) =
+              make_float4(dkv[4 * i], dkv[4 * i + 1], dkv[4 * i + 2], dkv[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tile_st_chunk(SK, r, jb * 4 + i, 64, pack8_bf16(dkv + 8 * i));
+      }
+    }
+  }
   fence_proxy_async();
   __syncthreads();
   if (tid == 0) {
-    for (int a = 0; a < 2; ++a) tma_store_4d(&mdq, SQ + a * 8192, a * 64, h, c * kC, b);
     if (DELTA) {
       bulk_s2g(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb, SK, 32768);
-      bulk_s2g(p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, SW, 16384);
     } else {
       for (int a = 0; a < 2; ++a) tma_store_4d(&mdk, SK + a * 8192, a * 64, h, c * kC, b);
     }
     bulk_commit();
   }
-  LETHE_PHASE("epi2");
+  LETHE_PHASE("epi2b");
   // ---- Stage-B gate gradient of the chunk (before the reverse cumulative sum)
   float dG = 0.f;
   {
@@ -454,7 +485,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   tc_fence_before();
   __syncthreads();
   LETHE_PHASE_DUMP();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -475,7 +506,8 @@ static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
 template <int V, bool DELTA>
 static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo,
                            const OutMaps& mo, cudaStream_t st) {
-  const int smem = 32768 + 16384 + V * 256 * 4 + 16384 * 2 + 656 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  const int smem = 16384 + 16384 + V * 256 + 8192 + 8192 + V * 128 + V * 256 * 2 + 656 * 4 +
+                   static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
   bwd_stageb_kernel<V, DELTA><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mdo, mo.dq, mo.dk);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
