@@ -59,7 +59,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
     }
   }
   if (warp == 0) {
-    tmem_alloc(&cs->tmem_slot, 256);
+    tmem_alloc(&cs->tmem_slot, 2 * V);     // two accumulators of V columns: three CTAs fit an SM at d_v = 64
     tmem_relinquish();
   }
   float gval = 0.f;
@@ -101,7 +101,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
       tc_fence_after();
       const uint32_t leader = elect_leader();
       issue_product_led(leader, tmem, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
-      issue_product_led(leader, tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+      issue_product_led(leader, tmem + V, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
       umma_commit_led(leader, bar_mma);
     }
     wait_products(bar_mma, ph, ctl, 402);
@@ -119,13 +119,13 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
     if (warp == 0) {
       tc_fence_after();
       const uint32_t leader = elect_leader();
-      issue_product_led(leader, tmem + 128, Tile{smem_u32(Wt), 64, true}, Tile{smem_u32(DVL), 64, true}, V, 64, 1u, true);
+      issue_product_led(leader, tmem + V, Tile{smem_u32(Wt), 64, true}, Tile{smem_u32(DVL), 64, true}, V, 64, 1u, true);
       umma_commit_led(leader, bar_mma);
     }
   } else if (warp == 0) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
-    issue_product_led(leader, tmem + 128, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
+    issue_product_led(leader, tmem + V, Tile{smem_u32(QG), 64, true}, Tile{smem_u32(DO), 64, true}, V, 64, 0u);
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 403);
@@ -134,7 +134,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
 #pragma unroll
     for (int jb = 0; jb < V / 32; ++jb) {
       float d[32];
-      tmem_ld32(tmem + 128 + lane_base + jb * 32, d);
+      tmem_ld32(tmem + V + lane_base + jb * 32, d);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tid, jb * 4 + i)) = pack8_f16(d + 8 * i);
@@ -149,7 +149,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (warp == 0) tmem_dealloc(tmem, 2 * V);
 }
 
 // ---------------------------------------------------------------------------------------------
