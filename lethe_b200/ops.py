@@ -140,6 +140,40 @@ def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, 
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
+class GdnStepGraph:
+    """Forward + backward of one fixed problem, captured once into a CUDA graph and replayed.
+
+    A training step at fixed shapes calls the library with the same pointers every time; replaying the
+    captured kernels removes the launch gaps between them (seven kernels of 12-40 microseconds each at
+    B=2, H=8, L=2048).  Inputs are read from, and results written to, the tensors given here: copy new
+    data into them between replays.  Results land in ``buf`` as with ``forward_into`` / ``backward_into``.
+    """
+
+    def __init__(self, buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, *, b_gate=None, w_gate=None):
+        self.buf = buf
+        self._keep = (q, k, v, g, beta, h0, do, dhT, b_gate, w_gate)
+        dev = q.device
+
+        def step():
+            forward_into(buf, q, k, v, g, beta, h0, scale, b_gate=b_gate, w_gate=w_gate)
+            backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, b_gate=b_gate, w_gate=w_gate)
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()                      # first call outside the capture: one-time driver look-ups and attributes
+            side.synchronize()
+            check_status(buf.status)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    def replay(self) -> None:
+        """Enqueue the captured step on the current stream."""
+        self.graph.replay()
+
+
 def _gate_code(g: Tensor | None) -> int:
     return GATE_NONE if g is None else (GATE_SCALAR if g.dim() == 3 else GATE_CHANNEL)
 
