@@ -195,14 +195,16 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  uint64_t* bar_dh = &cs->bar[2];       // dh, loaded once the adjoint scan before this kernel is complete
   constexpr uint32_t kCols = (V == 64) ? 256u : 512u;
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 2);     // two issuing warps commit every product group
+    mbar_init(bar_dh, 1);
     fence_mbar_init();
     fence_proxy_async();
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 8192u + V * 128u + V * 256u + V * 256u);
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 8192u + V * 128u + V * 256u);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(KT + a * 8192, &mk, bar_load, a * 64, h, c * kC, b);
       tma_load_4d(QT + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
@@ -214,7 +216,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     // the [T; A] record is 128 rows of one 64-column atom: its second half is the image of A
     bulk_g2s(AT, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta + 8192, 8192, bar_load);
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
-    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
+    // (dh, written by the adjoint scan just before this kernel, is loaded after griddep_wait)
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, kCols);
@@ -257,6 +259,14 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   sync_for_issue();
   LETHE_PHASE("convert");
+  // everything above used inputs and records older than the adjoint scan; its dh image is fetched now
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_dh, V * 256u);
+    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_dh);
+  }
+  mbar_wait_warp(bar_dh, 0, ctl, 415);
 
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -509,7 +519,8 @@ static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtens
   const int smem = 16384 + 16384 + V * 256 + 8192 + 8192 + V * 128 + V * 256 * 2 + 656 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
-  bwd_stageb_kernel<V, DELTA><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mdo, mo.dq, mo.dk);
+  if (launch_dependent(bwd_stageb_kernel<V, DELTA>, dim3(p.B * p.H * p.NT), dim3(256), smem, st, p, mq, mk, mdo,
+                       mo.dq, mo.dk) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 int launch_bwd_pre(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {

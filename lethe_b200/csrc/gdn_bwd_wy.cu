@@ -48,6 +48,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   uint64_t* bar_mma = &cs->bar[1];
   uint64_t* bar_dkb = &cs->bar[2];
   uint64_t* bar_g1 = &cs->bar[3];     // first product group: two issuing warps
+  uint64_t* bar_post = &cs->bar[4];   // dw and du, loaded once Stage B before this kernel is complete
   constexpr uint32_t kCols = (V == 64) ? 256u : 512u;
   if (tid == 0) {
     cs->abort_flag = 0;
@@ -55,17 +56,14 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     mbar_init(bar_mma, 1);
     mbar_init(bar_dkb, 1);
     mbar_init(bar_g1, 2);
+    mbar_init(bar_post, 1);
     fence_mbar_init();
     fence_proxy_async();
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u);
-    for (int a = 0; a < 2; ++a) {
-      tma_load_4d(T1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
-               bar_load);
-    }
+    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u);
+    for (int a = 0; a < 2; ++a) tma_load_4d(T1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
     for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
     bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
+    // (dw, du and the Stage-B parts of dk and dG, written just before this kernel, come after griddep_wait)
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, kCols);
@@ -77,7 +75,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   if (tid < 64) {
     if (p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
     bval = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
-    dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid];
   }
   tc_fence_before();
   __syncthreads();
@@ -119,6 +116,18 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   sync_for_issue();
   LETHE_PHASE("convert");
+  // everything above used inputs and records older than Stage B; what Stage B wrote is fetched now
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_post, 16384u + V * 128u);
+    for (int a = 0; a < 2; ++a)
+      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
+               bar_post);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_post);
+  }
+  if (tid < 64) dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid];
+  mbar_wait_warp(bar_post, 0, ctl, 427);
 
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -348,7 +357,8 @@ static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
   const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 904 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   if (cudaFuncSetAttribute(bwd_wy2_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return kErrLaunch;
-  bwd_wy2_kernel<V><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mk, mv, mo.dk, mo.dv);
+  if (launch_dependent(bwd_wy2_kernel<V>, dim3(p.B * p.H * p.NT), dim3(256), smem, st, p, mk, mv, mo.dk, mo.dv) !=
+      cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -325,14 +325,16 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   const unsigned char* Ug = p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u;
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  uint64_t* bar_ht = &cs->bar[2];       // the state image, loaded once the scan before this kernel is complete
 
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
+    mbar_init(bar_ht, 1);
     fence_mbar_init();
     fence_proxy_async();
-    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + V * 256u + 16384u + (CW ? 32768u : 0u));
+    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + 16384u + (CW ? 32768u : 0u));
     if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(WQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
@@ -340,8 +342,8 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
         bulk_g2s(WQ + a * 16384, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w + a * 8192, 8192, bar_load);
     }
     if (!DELTA) bulk_g2s(VN, Ug, V * 128, bar_load);   // v_new = u = v
-    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    // (the state image, written by the scan just before this kernel, is loaded after griddep_wait)
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, V);
@@ -383,6 +385,14 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   }
   fence_proxy_async();
   __syncthreads();
+  // everything above used inputs and records older than the scan; its state image is fetched now
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_ht, V * 256u);
+    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_ht);
+  }
+  mbar_wait_warp(bar_ht, 0, ctl, 214);
 
   if (warp == 0) {
     tc_fence_after();
@@ -465,7 +475,7 @@ static int launch_output_t(const Problem& p, const CUtensorMap& mq, cudaStream_t
   const int smem = 32768 + V * 256 + 16384 + V * 128 + 128 * 4 + (CW ? 32768 : 0) + 1024;
   auto kern = output_kernel<V, DELTA, CW>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
-  kern<<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq);
+  if (launch_dependent(kern, dim3(p.B * p.H * p.NT), dim3(128), smem, st, p, mq) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -69,6 +69,12 @@ scan_kernel(const Problem p) {
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
   auto chunk_of = [&](int it) { return ADJOINT ? NT - 1 - it : it; };
+  // The kernel before this one wrote R (forward) or Rb (adjoint); P comes from the same kernel in the
+  // forward and from the forward call in the adjoint, whose producer may start at once.
+  if (!(ADJOINT && warp == 4)) {
+    griddep_wait();
+    griddep_launch();
+  }
 
   if (warp == 4) {
     // ---- producer: keeps the ring of P stages full
@@ -230,11 +236,11 @@ int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
   if (adjoint) {
     if (cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return kErrLaunch;
-    scan_kernel<true><<<grid, kScanThreads, smem, st>>>(p);
+    if (launch_dependent(scan_kernel<true>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
   } else {
     if (cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return kErrLaunch;
-    scan_kernel<false><<<grid, kScanThreads, smem, st>>>(p);
+    if (launch_dependent(scan_kernel<false>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
   }
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -83,6 +83,17 @@ __device__ __forceinline__ void mbar_wait_warp(uint64_t* bar, uint32_t parity, c
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel
+// before it in the stream is still running; `griddep_wait` blocks until that kernel has completed and
+// its writes are visible (a no-op for a plain launch), `griddep_launch` lets the next kernel of the
+// stream start its own prologue.  Every kernel here triggers only after its own wait, so when a
+// kernel starts, everything older than its immediate predecessor is complete: before the wait it
+// may read anything except what the immediate predecessor writes.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // proxy fences
 // ---------------------------------------------------------------------------------------------
 // Make this thread's earlier shared-memory writes visible to the asynchronous proxy (TMA, tcgen05).
