@@ -241,6 +241,14 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   if (tid < 64) decs[tid] = __expf(Glast - G);
 
   LETHE_PHASE("setup");
+  // the loads above fetch inputs and records older than the adjoint scan; once it is complete (at once,
+  // except for the CTAs that started early) its dh image is fetched too
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_dh, V * 256u);
+    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_dh);
+  }
   mbar_wait_warp(bar_load, 0, ctl, 411);
   LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
@@ -259,13 +267,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   sync_for_issue();
   LETHE_PHASE("convert");
-  // everything above used inputs and records older than the adjoint scan; its dh image is fetched now
-  griddep_wait();
-  griddep_launch();
-  if (tid == 0) {
-    mbar_expect_tx(bar_dh, V * 256u);
-    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_dh);
-  }
   mbar_wait_warp(bar_dh, 0, ctl, 415);
 
   uint32_t ph = 0;

@@ -89,6 +89,18 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   __syncthreads();
   LETHE_PHASE("setup");
+  // the loads above fetch inputs and records older than Stage B; once Stage B is complete (at once, except
+  // for the CTAs that started early) what it wrote is fetched too
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_post, 16384u + V * 128u);
+    for (int a = 0; a < 2; ++a)
+      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
+               bar_post);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_post);
+  }
+  if (tid < 64) dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid];
   mbar_wait_warp(bar_load, 0, ctl, 421);
   LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
@@ -116,17 +128,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   sync_for_issue();
   LETHE_PHASE("convert");
-  // everything above used inputs and records older than Stage B; what Stage B wrote is fetched now
-  griddep_wait();
-  griddep_launch();
-  if (tid == 0) {
-    mbar_expect_tx(bar_post, 16384u + V * 128u);
-    for (int a = 0; a < 2; ++a)
-      bulk_g2s(T1 + a * 16384 + 8192, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw + a * 8192, 8192,
-               bar_post);
-    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_post);
-  }
-  if (tid < 64) dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid];
   mbar_wait_warp(bar_post, 0, ctl, 427);
 
   uint32_t ph = 0;

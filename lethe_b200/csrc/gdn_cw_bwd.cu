@@ -60,10 +60,12 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  uint64_t* bar_dh = &cs->bar[2];       // dh, loaded once the adjoint scan before this kernel is complete
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
+    mbar_init(bar_dh, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -77,7 +79,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   const uint32_t tmem = cs->tmem_slot;
   const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + V * 256u + 32768u);
+    mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + 32768u);
     bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(X1 + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
@@ -87,24 +89,20 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(VNt, p.saved + p.lay.vn + static_cast<size_t>(z) * p.lay.sz_vn, V * 128, bar_load);
     bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
-    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_load);
+    // (dh, written by the adjoint scan just before this kernel, is loaded after griddep_wait)
   }
   LETHE_PHASE_INIT();
   __syncthreads();
+  // the loads above fetch inputs and records older than the adjoint scan; once it is complete (at once,
+  // except for the CTAs that started early) its dh image is fetched too
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_dh, V * 256u);
+    bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_dh);
+  }
   mbar_wait_warp(bar_load, 0, ctl, 601);
   LETHE_PHASE("loaded");
-  if (tid < 128) {  // exp(G_last,d) sum_v dh[d,v] h[d,v]: thread d owns row d of both images
-    float acc = 0.f;
-#pragma unroll
-    for (int ch = 0; ch < V / 8; ++ch) {
-      float x[8], y[8];
-      unpack8_f16(tile_ld_chunk(DHt, tid, ch, 128), x);
-      unpack8_f16(tile_ld_chunk(Ht, tid, ch, 128), y);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc += x[e] * y[e];
-    }
-    hh[tid] = acc * __expf(Gt[gidx(63, tid)]);
-  }
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
@@ -123,6 +121,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     tile_st_chunk(DD, r, ch, 128, pack8_f16(x));
   }
   sync_for_issue();
+  mbar_wait_warp(bar_dh, 0, ctl, 604);
 
   LETHE_PHASE("built");
   uint32_t ph = 0;
@@ -134,6 +133,19 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     issue_product_led(leader, cA, Tile{smem_u32(TAt), 64, true}, Tile{smem_u32(DD), 128, true}, V, 64, 1u);
     issue_product_led(leader, cC, Tile{smem_u32(DD), 128, false}, Tile{smem_u32(VNt), 64, false}, 64, V, 0u);
     umma_commit_led(leader, bar_mma);
+  }
+  // in the shadow of the products (both images are only read)
+  if (tid < 128) {  // exp(G_last,d) sum_v dh[d,v] h[d,v]: thread d owns row d of both images
+    float acc = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < V / 8; ++ch) {
+      float x[8], y[8];
+      unpack8_f16(tile_ld_chunk(DHt, tid, ch, 128), x);
+      unpack8_f16(tile_ld_chunk(Ht, tid, ch, 128), y);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += x[e] * y[e];
+    }
+    hh[tid] = acc * __expf(Gt[gidx(63, tid)]);
   }
   wait_products(bar_mma, ph, ctl, 602);
   LETHE_PHASE("g1");
@@ -404,6 +416,10 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 614);
+  // Everything read so far is older than the kernel before this one (the Stage-B pair kernel), which
+  // still reads the dq-part record that is overwritten below: wait for it before writing anything.
+  griddep_wait();
+  griddep_launch();
   if (tid < 64) {
     const int r = tid;
     {  // dM, strictly lower -> record
@@ -517,10 +533,12 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  uint64_t* bar_c = &cs->bar[2];        // C (dA or dM), written by the kernel just before this one
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
+    mbar_init(bar_c, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -535,17 +553,24 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
   if (tid == 0) {
-    mbar_expect_tx(bar_load, 32768u + 8192u + 32768u);
+    mbar_expect_tx(bar_load, 32768u + 32768u);
     bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(KX + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
       tma_load_4d(KX + a * 16384 + 8192, MODE == 0 ? &mq : &mk, bar_load, a * 64, h, c * kC, b);
     }
-    bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_load);
   }
   LETHE_PHASE_INIT();
   __syncthreads();
   LETHE_PHASE("gate");
+  // the loads above fetch inputs and the gate record; C and the fp32 records come from the kernels just
+  // before this one
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_c, 8192u);
+    bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_c);
+  }
   mbar_wait_warp(bar_load, 0, ctl, 621);
   LETHE_PHASE("loaded");
   // ---- decayed operand rows
@@ -582,6 +607,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
   }
   LETHE_PHASE("rows");
+  mbar_wait_warp(bar_c, 0, ctl, 623);
   // ---- masked copies of C and its diagonal blocks
   for (int idx = tid; idx < 64 * 8; idx += 256) {
     const int r = idx >> 3, s8 = idx & 7, blk = r >> 4, cb = s8 >> 1;
@@ -795,7 +821,8 @@ static int launch_sb1_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
   const int smem = 32768 + 16384 + V * 256 + 16384 + V * 128 + V * 512 + 32768 + 128 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem_cw(bwd_cw_sb1_kernel<V, DELTA>, smem)) return kErrLaunch;
-  bwd_cw_sb1_kernel<V, DELTA><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mdo);
+  if (launch_dependent(bwd_cw_sb1_kernel<V, DELTA>, dim3(p.B * p.H * p.NT), dim3(256), smem, st, p, mq, mk, mdo) !=
+      cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V>
@@ -803,14 +830,16 @@ static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
   const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 + 16384 + 32768 + 64 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem_cw(bwd_cw_wy1_kernel<V>, smem)) return kErrLaunch;
-  bwd_cw_wy1_kernel<V><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mk, mv);
+  if (launch_dependent(bwd_cw_wy1_kernel<V>, dim3(p.B * p.H * p.NT), dim3(128), smem, st, p, mk, mv) != cudaSuccess)
+    return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int MODE, bool FINAL_G>
 static int launch_pair_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, cudaStream_t st) {
   const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1216 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem_cw(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
-  bwd_cw_pair_kernel<MODE, FINAL_G><<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk);
+  if (launch_dependent(bwd_cw_pair_kernel<MODE, FINAL_G>, dim3(p.B * p.H * p.NT), dim3(256), smem, st, p, mq, mk) !=
+      cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -367,6 +367,14 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   if (tid < 64) Gs[tid] = G;
   __syncthreads();
 
+  // the loads above fetch inputs and records older than the scan; once the scan is complete (at once,
+  // except for the CTAs that started early) its state image is fetched too
+  griddep_wait();
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(bar_ht, V * 256u);
+    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_ht);
+  }
   mbar_wait_warp(bar_load, 0, ctl, 211);
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
@@ -385,13 +393,6 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   }
   fence_proxy_async();
   __syncthreads();
-  // everything above used inputs and records older than the scan; its state image is fetched now
-  griddep_wait();
-  griddep_launch();
-  if (tid == 0) {
-    mbar_expect_tx(bar_ht, V * 256u);
-    bulk_g2s(HT, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_ht);
-  }
   mbar_wait_warp(bar_ht, 0, ctl, 214);
 
   if (warp == 0) {
