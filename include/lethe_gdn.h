@@ -91,6 +91,11 @@ typedef struct LetheGdnArgs {
   const float* w_gate;
   float* db_gate;
   float* dw_gate;
+  /* The (batch, head) pairs this call works on: pairs [bh_begin, bh_begin + bh_count) in b * H + h order;     */
+  /* bh_count = 0 means all of them.  Pairs are independent recurrences: calls on disjoint ranges may run     */
+  /* concurrently on different streams with the same tensors and workspaces (no counterpart in the reference). */
+  uint32_t bh_begin;
+  uint32_t bh_count;
 } LetheGdnArgs;
 
 /* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */

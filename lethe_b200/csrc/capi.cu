@@ -64,6 +64,15 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
   if (!aligned16(a->saved) || (reinterpret_cast<uintptr_t>(a->saved) & 1023u)) return kErrAlign;
   if (backward && (reinterpret_cast<uintptr_t>(a->scratch) & 1023u)) return kErrAlign;
   p->B = d.B; p->H = d.H; p->L = d.L; p->NT = d.L / kC; p->V = d.V; p->gate = d.gate; p->delta = d.delta ? 1 : 0;
+  if (a->bh_count == 0) {
+    if (a->bh_begin != 0) return kErrDims;
+    p->bh0 = 0;
+    p->nbh = d.B * d.H;
+  } else {
+    if (static_cast<uint64_t>(a->bh_begin) + a->bh_count > static_cast<uint64_t>(d.B) * d.H) return kErrDims;
+    p->bh0 = static_cast<int>(a->bh_begin);
+    p->nbh = static_cast<int>(a->bh_count);
+  }
   p->scale = a->scale;
   p->q = static_cast<const __nv_bfloat16*>(a->q);
   p->k = static_cast<const __nv_bfloat16*>(a->k);

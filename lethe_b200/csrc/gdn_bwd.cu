@@ -39,7 +39,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   float* Gt = fs + 128;     // channel-wise gate only
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -191,7 +191,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves
   // take the same rows and split the columns of every epilogue.
   const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
-  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -511,7 +511,7 @@ template <int V, bool DELTA, bool CW>
 static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
   const int smem = 16384 * 3 + V * 256 + 128 * 4 + (CW ? 32768 : 0) + 1024;
   if (set_smem(bwd_pre_kernel<V, DELTA, CW>, smem)) return kErrLaunch;
-  bwd_pre_kernel<V, DELTA, CW><<<p.B * p.H * p.NT, 128, smem, st>>>(p, mq, mdo);
+  bwd_pre_kernel<V, DELTA, CW><<<p.nbh * p.NT, 128, smem, st>>>(p, mq, mdo);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V, bool DELTA>
@@ -520,7 +520,7 @@ static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtens
   const int smem = 16384 + 16384 + V * 256 + 8192 + 8192 + V * 128 + V * 256 * 2 + 656 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   if (set_smem(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_stageb_kernel<V, DELTA>, dim3(p.B * p.H * p.NT), dim3(256), smem, st, p, mq, mk, mdo,
+  if (launch_dependent(bwd_stageb_kernel<V, DELTA>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk, mdo,
                        mo.dq, mo.dk) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -126,6 +126,7 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
 // Everything a kernel needs besides its tensor maps.
 struct Problem {
   int B, H, L, NT, V, gate, delta;
+  int bh0, nbh;      // the (batch, head) pairs this call works on: [bh0, bh0 + nbh) of the B * H pairs
   float scale;
   const __nv_bfloat16 *q, *k, *v, *d_o;
   const float *g, *beta, *h0, *dhT;

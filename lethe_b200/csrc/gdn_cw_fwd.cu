@@ -43,7 +43,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   unsigned char* WU = KQ;
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -351,7 +351,7 @@ static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CU
   const int smem = 32768 * 4 + 16384 + V * 128 + 16384 + 16384 + 2112 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_cw_kernel<V, DELTA>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
-  kern<<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.nbh * p.NT, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -47,7 +47,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves take
   // the same rows and split the columns of every epilogue.
   const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
-  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -320,7 +320,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   float* Gt = fs + 128;     // channel-wise gate only: cumulative log decay [64][128]
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   const unsigned char* Ug = p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u;
   uint64_t* bar_load = &cs->bar[0];
@@ -468,7 +468,7 @@ static int launch_prepare_t(const Problem& p, const CUtensorMap& mq, const CUten
   const int smem = 32768 + 16384 + V * 128 + 16384 + 16384 + 264 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_kernel<V, DELTA>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
-  kern<<<p.B * p.H * p.NT, 256, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.nbh * p.NT, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V, bool DELTA, bool CW>
@@ -476,7 +476,7 @@ static int launch_output_t(const Problem& p, const CUtensorMap& mq, cudaStream_t
   const int smem = 32768 + V * 256 + 16384 + V * 128 + 128 * 4 + (CW ? 32768 : 0) + 1024;
   auto kern = output_kernel<V, DELTA, CW>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
-  if (launch_dependent(kern, dim3(p.B * p.H * p.NT), dim3(128), smem, st, p, mq) != cudaSuccess) return kErrLaunch;
+  if (launch_dependent(kern, dim3(p.nbh * p.NT), dim3(128), smem, st, p, mq) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -43,7 +43,7 @@ scan_kernel(const Problem p) {
   CtaShared* cs = reinterpret_cast<CtaShared*>(XB + 4096);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int v0 = blockIdx.x * kVs, bh = blockIdx.y;
+  const int v0 = blockIdx.x * kVs, bh = blockIdx.y + p.bh0;
   const int V = p.V, NT = p.NT;
   const bool has_p = p.delta != 0;
   CtaCtl ctl{p.status, &cs->abort_flag};
@@ -232,7 +232,7 @@ scan_kernel(const Problem p) {
 
 int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
   const int smem = kStages * 32768 + 4096 + static_cast<int>(sizeof(CtaShared)) + 1024;
-  dim3 grid(p.V / kVs, p.B * p.H);
+  dim3 grid(p.V / kVs, p.nbh);
   if (adjoint) {
     if (cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return kErrLaunch;

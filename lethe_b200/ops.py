@@ -41,6 +41,7 @@ class _Args(ctypes.Structure):
         ("dbeta_write", ctypes.c_void_p),
         ("b_gate", ctypes.c_void_p), ("w_gate", ctypes.c_void_p),
         ("db_gate", ctypes.c_void_p), ("dw_gate", ctypes.c_void_p),
+        ("bh_begin", ctypes.c_uint32), ("bh_count", ctypes.c_uint32),
     ]
 
 
@@ -117,18 +118,19 @@ class GdnBuffers:
 
 
 def forward_into(buf: GdnBuffers, q, k, v, g, beta, h0, scale: float, kernel_mask: int = 0, *,
-                 b_gate=None, w_gate=None) -> None:
+                 b_gate=None, w_gate=None, bh_range: tuple[int, int] = (0, 0)) -> None:
     """Enqueue the forward kernels on the current stream; results land in ``buf.o`` / ``buf.hT``.
-    ``b_gate [B,L,H,K]`` / ``w_gate [B,L,H,V]`` (fp32) replace ``beta`` for buffers made with ``delta=2``."""
+    ``b_gate [B,L,H,K]`` / ``w_gate [B,L,H,V]`` (fp32) replace ``beta`` for buffers made with ``delta=2``.
+    ``bh_range = (begin, count)`` restricts the call to those (batch, head) pairs (count 0: all)."""
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
               h0=_ptr(h0), o=_ptr(buf.o), hT=_ptr(buf.hT), saved=_ptr(buf.saved),
               saved_bytes=buf.saved.numel(), status=_ptr(buf.status), kernel_mask=kernel_mask,
-              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate))
+              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), bh_begin=bh_range[0], bh_count=bh_range[1])
     _check(native.lib().lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
 def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, kernel_mask: int = 0, *,
-                  b_gate=None, w_gate=None) -> None:
+                  b_gate=None, w_gate=None, bh_range: tuple[int, int] = (0, 0)) -> None:
     """Enqueue the backward kernels; gradients land in ``buf.dq`` ... ``buf.dh0`` (``buf.db`` / ``buf.dw``
     for the per-channel gates of buffers made with ``delta=2``)."""
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
@@ -136,7 +138,8 @@ def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, 
               dg=_ptr(buf.dg), dbeta=_ptr(buf.dbeta), dh0=_ptr(buf.dh0), saved=_ptr(buf.saved),
               saved_bytes=buf.saved.numel(), scratch=_ptr(buf.scratch), scratch_bytes=buf.scratch.numel(),
               status=_ptr(buf.status), kernel_mask=kernel_mask, dbeta_write=_ptr(buf.dbeta_write),
-              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), db_gate=_ptr(buf.db), dw_gate=_ptr(buf.dw))
+              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), db_gate=_ptr(buf.db), dw_gate=_ptr(buf.dw),
+              bh_begin=bh_range[0], bh_count=bh_range[1])
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
@@ -144,24 +147,56 @@ class GdnStepGraph:
     """Forward + backward of one fixed problem, captured once into a CUDA graph and replayed.
 
     A training step at fixed shapes calls the library with the same pointers every time; replaying the
-    captured kernels removes the launch gaps between them (seven kernels of 12-40 microseconds each at
-    B=2, H=8, L=2048).  Inputs are read from, and results written to, the tensors given here: copy new
-    data into them between replays.  Results land in ``buf`` as with ``forward_into`` / ``backward_into``.
+    captured kernels removes the launch gaps between them.  With ``groups > 1`` the (batch, head) pairs
+    are cut into that many ranges and every range runs its own kernel chain on its own stream inside the
+    graph: the pairs are independent recurrences, so while the serial state scan of one range occupies a
+    few SMs, the chunk-parallel kernels of the other ranges use the rest.  Results are bitwise the same
+    for every ``groups``.  Inputs are read from, and results written to, the tensors given here: copy
+    new data into them between replays.  Results land in ``buf`` as with ``forward_into`` /
+    ``backward_into``.
     """
 
-    def __init__(self, buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, *, b_gate=None, w_gate=None):
+    def __init__(self, buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, *, b_gate=None, w_gate=None,
+                 groups: int = 1):
         self.buf = buf
         self._keep = (q, k, v, g, beta, h0, do, dhT, b_gate, w_gate)
         dev = q.device
+        BH = buf.dims.B * buf.dims.H
+        groups = max(1, min(int(groups), BH))
+        bounds = [BH * i // groups for i in range(groups + 1)]
+        ranges = [(bounds[i], bounds[i + 1] - bounds[i]) for i in range(groups)]
+        self.groups = groups
 
-        def step():
-            forward_into(buf, q, k, v, g, beta, h0, scale, b_gate=b_gate, w_gate=w_gate)
-            backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, b_gate=b_gate, w_gate=w_gate)
+        def chain(rng):
+            forward_into(buf, q, k, v, g, beta, h0, scale, b_gate=b_gate, w_gate=w_gate, bh_range=rng)
+            backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, b_gate=b_gate, w_gate=w_gate, bh_range=rng)
 
         side = torch.cuda.Stream(device=dev)
+        self._streams = [torch.cuda.Stream(device=dev) for _ in range(groups - 1)]
+
+        def step():
+            if groups == 1:
+                chain((0, 0))
+                return
+            fork = torch.cuda.Event()
+            fork.record(side)
+            joins = []
+            for i, rng in enumerate(ranges):
+                st = side if i == 0 else self._streams[i - 1]
+                if i:
+                    st.wait_event(fork)
+                with torch.cuda.stream(st):
+                    chain(rng)
+                if i:
+                    e = torch.cuda.Event()
+                    e.record(st)
+                    joins.append(e)
+            for e in joins:
+                side.wait_event(e)
+
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            step()                      # first call outside the capture: one-time driver look-ups and attributes
+            chain((0, 0))               # first call outside the capture: one-time driver look-ups and attributes
             side.synchronize()
             check_status(buf.status)
             self.graph = torch.cuda.CUDAGraph()

@@ -35,3 +35,30 @@ def test_graph_replay_matches_plain_launches(gate, delta, V):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(buf.o, ref.o)
+
+
+def test_head_ranges_and_groups_give_the_same_bits():
+    """Calls restricted to (batch, head) ranges, and the graph that runs the ranges as concurrent chains,
+    must reproduce the full call bit for bit (the pairs are independent recurrences)."""
+    B, L, H, K, V = 2, 256, 3, 128, 64
+    dev = torch.device("cuda")
+    inp = make_inputs(B, L, H, K, V, gate="scalar", delta=True, seed=8)
+    d = {n: (None if t is None else t.to(dev)) for n, t in inp.items()}
+    args = (d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"])
+    ref = ops.GdnBuffers(B, L, H, K, V, ops.GATE_SCALAR, True, dev)
+    ops.forward_into(ref, *args, K ** -0.5)
+    ops.backward_into(ref, *args, d["do"], None, K ** -0.5)
+    part = ops.GdnBuffers(B, L, H, K, V, ops.GATE_SCALAR, True, dev)
+    for rng in ((4, 2), (0, 1), (1, 3)):                     # out of order, uneven
+        ops.forward_into(part, *args, K ** -0.5, bh_range=rng)
+        ops.backward_into(part, *args, d["do"], None, K ** -0.5, bh_range=rng)
+    grp = ops.GdnBuffers(B, L, H, K, V, ops.GATE_SCALAR, True, dev)
+    graph = ops.GdnStepGraph(grp, *args, d["do"], None, K ** -0.5, groups=4)
+    graph.replay()
+    torch.cuda.synchronize()
+    for b in (part, grp):
+        ops.check_status(b.status)
+        for n in ("o", "hT", "dq", "dk", "dv", "dg", "dbeta", "dh0"):
+            assert torch.equal(getattr(b, n), getattr(ref, n)), n
+    with pytest.raises(ops.GdnError):
+        ops.forward_into(part, *args, K ** -0.5, bh_range=(5, 2))     # beyond B * H = 6
