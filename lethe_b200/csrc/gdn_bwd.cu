@@ -137,7 +137,10 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
       tmem_ld32(tmem + V + lane_base + jb * 32, d);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tid, jb * 4 + i)) = pack8_f16(d + 8 * i);
+      for (int i = 0; i < 4; ++i) {
+        if (DELTA) *reinterpret_cast<uint4*>(SR + rrec_off(tid, jb * 4 + i)) = pack8_f16(d + 8 * i);
+        else tile_st_chunk(SR, tid, jb * 4 + i, 128, pack8_f16(d + 8 * i));     // no delta term: plain tile image
+      }
     }
     fence_proxy_async();
     __syncthreads();

@@ -230,9 +230,10 @@ __device__ __forceinline__ void st8(float* p, const float* v) {
   *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
-// The scan's input records R / Rb (128 rows x V columns, fp16) are stored as V / 16 column blocks of
+// With the delta term the scan's input records R / Rb (128 rows x V columns, fp16) are stored as V / 16 column blocks of
 // [128 rows][16 columns]: one contiguous 4 KB block per scan CTA, 32 bytes per thread.  Byte offset of
-// the 8-column piece `col8` of `row`:
+// the 8-column piece `col8` of `row` (without the delta term they are plain 128-row tile images, read by
+// scan_nodelta_kernel with full-line accesses):
 __device__ __forceinline__ uint32_t rrec_off(int row, int col8) {
   return static_cast<uint32_t>((col8 >> 1) * 4096 + row * 32 + (col8 & 1) * 16);
 }

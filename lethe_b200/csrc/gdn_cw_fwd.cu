@@ -326,7 +326,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       } else {
         const int c8 = (jb - (DELTA ? 4 : 0)) * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(SR + rrec_off(tq, c8 + i)) = pack8_f16(d + 8 * i);
+        for (int i = 0; i < 4; ++i) {
+          if (DELTA) *reinterpret_cast<uint4*>(SR + rrec_off(tq, c8 + i)) = pack8_f16(d + 8 * i);
+          else tile_st_chunk(SR, tq, c8 + i, 128, pack8_f16(d + 8 * i));     // no delta term: plain tile image
+        }
       }
     }
     fence_proxy_async();

@@ -230,7 +230,76 @@ scan_kernel(const Problem p) {
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Without the delta term the recurrence is x <- a x + R per element: no product, nothing serial but the
+// chunk order, and the kernel is bound by reading R and writing the state records once.  Every thread
+// owns one 16-byte piece (8 columns) of one row of the state; a warp covers four whole 128-byte rows
+// of a record atom, so every access is a full line.  R / Rb and the state records are 128-row tile images.
+// Grid: (V / 64 atoms x 4 row blocks, pairs) x 256 threads.
+// ---------------------------------------------------------------------------------------------
+template <bool ADJOINT>
+__global__ void __launch_bounds__(256)
+scan_nodelta_kernel(const Problem p) {
+  const int tid = threadIdx.x;
+  const int atom = blockIdx.x >> 2, d = (blockIdx.x & 3) * 32 + (tid >> 3), c8 = tid & 7;
+  const int bh = blockIdx.y + p.bh0, V = p.V, NT = p.NT;
+  const int col0 = atom * 64 + c8 * 8;
+  griddep_wait();
+  griddep_launch();
+  const unsigned char* Rg = ADJOINT ? p.scratch + p.lay.rb : p.saved + p.lay.r;
+  const float* ADg = reinterpret_cast<const float*>(p.saved + p.lay.ad);
+  unsigned char* Xg = ADJOINT ? p.scratch + p.lay.dh : p.saved + p.lay.hc;
+  const size_t szx = p.lay.sz_hc;
+  const uint32_t off = sw128_chunk(d, atom * 8 + c8, 128);     // this thread's piece inside any 128-row image
+  auto chunk_of = [&](int it) { return ADJOINT ? NT - 1 - it : it; };
+
+  float x[8];
+  {
+    const float* x0 = ADJOINT ? p.dhT : p.h0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = x0 ? x0[(static_cast<size_t>(bh) * kK + d) * V + col0 + j] : 0.f;
+  }
+  constexpr int kBatch = 8;
+  for (int it0 = 0; it0 < NT; it0 += kBatch) {
+    uint4 rb[kBatch];
+    float ab[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (it0 + j < NT) {
+        const size_t zj = static_cast<size_t>(bh) * NT + chunk_of(it0 + j);
+        rb[j] = *reinterpret_cast<const uint4*>(Rg + zj * p.lay.sz_r + off);
+        ab[j] = ADg[zj * kK + d];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (it0 + j < NT) {
+        const size_t zj = static_cast<size_t>(bh) * NT + chunk_of(it0 + j);
+        *reinterpret_cast<uint4*>(Xg + (ADJOINT ? zj : zj + bh) * szx + off) = pack8_f16(x);
+        float rr[8];
+        unpack8_f16(rb[j], rr);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) x[n] = fmaf(ab[j], x[n], rr[n]);
+      }
+    }
+  }
+  if (!ADJOINT)   // the final state as one more record
+    *reinterpret_cast<uint4*>(Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx + off) = pack8_f16(x);
+  float* xT = ADJOINT ? p.dh0 : p.hT;
+  if (xT) {
+    float* dst = xT + (static_cast<size_t>(bh) * kK + d) * V + col0;
+    *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(x[4], x[5], x[6], x[7]);
+  }
+}
+
 int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
+  if (!p.delta) {
+    const dim3 g((p.V / 64) * 4, p.nbh);
+    const cudaError_t e = adjoint ? launch_dependent(scan_nodelta_kernel<true>, g, dim3(256), 0, st, p)
+                                  : launch_dependent(scan_nodelta_kernel<false>, g, dim3(256), 0, st, p);
+    return e == cudaSuccess ? kOk : kErrLaunch;
+  }
   const int smem = kStages * 32768 + 4096 + static_cast<int>(sizeof(CtaShared)) + 1024;
   dim3 grid(p.V / kVs, p.nbh);
   if (adjoint) {

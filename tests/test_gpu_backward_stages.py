@@ -38,7 +38,10 @@ def test_backward_records(V, delta, mild, gate):
     NT = L // 64
     shp = (B, H, NT)
     errs = {}
-    errs["Rb"] = scale_rel(rrecords(scratch, off2["rb"], sz2["rb"], Z, V).reshape(*shp, 128, V).double(), it["Rb"])
+    # with the delta term Rb is stored in per-scan-CTA column blocks, without it as a plain tile image
+    rb_rec = (rrecords(scratch, off2["rb"], sz2["rb"], Z, V) if delta
+              else unswizzle(records(scratch, off2["rb"], sz2["rb"], Z), 128, V))
+    errs["Rb"] = scale_rel(rb_rec.reshape(*shp, 128, V).double(), it["Rb"])
     errs["dh"] = scale_rel(unswizzle(records(scratch, off2["dh"], sz2["dh"], Z), 128, V).reshape(*shp, 128, V).double(),
                            it["dh"])
     if delta:

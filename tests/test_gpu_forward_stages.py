@@ -44,7 +44,10 @@ def test_forward_records(V, delta, mild, gate):
     # the chunk decay exp(G_last) underflows fp32 under the strong gate draw: compare absolutely
     ad = records(saved, off["ad"], sz["ad"], Z, torch.float32).reshape(*shp, 128).double()
     errs["ad"] = float((ad - st.a).abs().max())
-    errs["R"] = scale_rel(rrecords(saved, off["r"], sz["r"], Z, V).reshape(*shp, 128, V).double(), st.R)
+    # with the delta term R is stored in per-scan-CTA column blocks, without it as a plain tile image
+    r_rec = (rrecords(saved, off["r"], sz["r"], Z, V) if delta
+             else unswizzle(records(saved, off["r"], sz["r"], Z), 128, V))
+    errs["R"] = scale_rel(r_rec.reshape(*shp, 128, V).double(), st.R)
     errs["h"] = scale_rel(unswizzle(records(saved, off["hc"], sz["hc"], Z + B * H), 128, V)
                           .reshape(B, H, NT + 1, 128, V).double(), st.h)
     errs["vn"] = scale_rel(unswizzle(records(saved, off["vn"], sz["vn"], Z), 64, V).reshape(*shp, 64, V).double(),
