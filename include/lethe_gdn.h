@@ -147,6 +147,20 @@ typedef struct LetheGdnDecodeArgs {
 } LetheGdnDecodeArgs;
 int lethe_gdn_decode_step(const LetheGdnDecodeArgs* args, void* cuda_stream);
 
+/* L2 normalisation of q and k before the recurrence, and its vector-Jacobian product after the
+ * backward (reference src/lethe/kernels/references/gdn_backward.py:9-10, applied at :29-31 when
+ * use_qk_l2norm is set; the reference differentiates it by autograd,
+ * src/lethe/kernels/references/gdn2_assemble.py:300-312):
+ *   y = x * rsqrt(sum_d x_d^2 + eps);      dx = r (dy - y (y . dy)),  r = rsqrt(sum_d x_d^2 + eps).
+ * q, k: [rows, D] contiguous, bf16 (in_f32 == 0) or fp32 (in_f32 != 0); D in {64, 128}; rows = B L H.
+ * qn, kn: bf16 [rows, D], the tensors lethe_gdn_forward / lethe_gdn_backward then read.
+ * dqn, dkn: bf16 [rows, D], the dq / dk lethe_gdn_backward wrote; dq, dk: [rows, D] in the type of
+ * q, k (may alias dqn, dkn when that type is bf16).  One launch each; every pointer 16-byte aligned. */
+int lethe_gdn_l2norm_qk(const void* q, const void* k, void* qn, void* kn, int64_t rows, int32_t D,
+                        int32_t in_f32, float eps, void* cuda_stream);
+int lethe_gdn_l2norm_qk_vjp(const void* q, const void* k, const void* dqn, const void* dkn, void* dq, void* dk,
+                            int64_t rows, int32_t D, int32_t in_f32, float eps, void* cuda_stream);
+
 /* Text for a return code of the calls above or for a device status code. */
 const char* lethe_gdn_strerror(int code);
 

@@ -45,7 +45,6 @@ scan_kernel(const Problem p) {
   const int tid = threadIdx.x, warp = tid >> 5;
   const int v0 = blockIdx.x * kVs, bh = blockIdx.y + p.bh0;
   const int V = p.V, NT = p.NT;
-  const bool has_p = p.delta != 0;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_full = &cs->bar[0];                 // [kStages] P stage loaded
   uint64_t* bar_free = &cs->bar[kStages];           // [kStages] the products reading the stage are done
@@ -78,7 +77,7 @@ scan_kernel(const Problem p) {
 
   if (warp == 4) {
     // ---- producer: keeps the ring of P stages full
-    if (has_p && tid == 128) {
+    if (tid == 128) {
       const unsigned char* Pg = p.saved + p.lay.p;
       for (int it = 0; it < NT; ++it) {
         const int st = it % kStages;
@@ -90,34 +89,32 @@ scan_kernel(const Problem p) {
   } else if (warp > 4) {
     // ---- product issue: warp m takes contraction steps [m * 8 / kMmaWarps, ...) into accumulator m.
     // All lanes stay on the path (uniform descriptors); the elected lane issues.
-    if (has_p) {
-      const int m = warp - 5;
-      constexpr int kPer = 8 / kMmaWarps;
-      const uint32_t leader = elect_leader();
-      // A = the P stage (contracted along its columns forward, along its rows for the adjoint),
-      // B = the state operand; one 16-element contraction step moves each by a fixed amount
-      const uint64_t b_desc0 = make_desc_sw32(smem_u32(XB), 16u, 256u);
-      const uint32_t idesc = make_idesc(128, kVs, ADJOINT, true);
-      const uint32_t acc = tmem + static_cast<uint32_t>(m * kVs);
-      for (int it = 0; it < NT; ++it) {
-        const int st = it % kStages;
-        mbar_wait_warp(&bar_full[st], static_cast<uint32_t>((it / kStages) & 1), ctl, 301);
-        step_sync();
-        tc_fence_after();
-        const uint32_t pa = smem_u32(Pst + st * 32768);
-        const uint64_t a_desc0 = ADJOINT ? make_desc(pa, 16384u, 1024u) : make_desc(pa, 16u, 1024u);
+    const int m = warp - 5;
+    constexpr int kPer = 8 / kMmaWarps;
+    const uint32_t leader = elect_leader();
+    // A = the P stage (contracted along its columns forward, along its rows for the adjoint),
+    // B = the state operand; one 16-element contraction step moves each by a fixed amount
+    const uint64_t b_desc0 = make_desc_sw32(smem_u32(XB), 16u, 256u);
+    const uint32_t idesc = make_idesc(128, kVs, ADJOINT, true);
+    const uint32_t acc = tmem + static_cast<uint32_t>(m * kVs);
+    for (int it = 0; it < NT; ++it) {
+      const int st = it % kStages;
+      mbar_wait_warp(&bar_full[st], static_cast<uint32_t>((it / kStages) & 1), ctl, 301);
+      step_sync();
+      tc_fence_after();
+      const uint32_t pa = smem_u32(Pst + st * 32768);
+      const uint64_t a_desc0 = ADJOINT ? make_desc(pa, 16384u, 1024u) : make_desc(pa, 16u, 1024u);
 #pragma unroll
-        for (int jj = 0; jj < kPer; ++jj) {
-          const int j = m * kPer + jj;
-          // byte offsets of contraction step j, in the descriptors' 16-byte units
-          const uint32_t aoff = ADJOINT ? static_cast<uint32_t>(j * 2048) >> 4
-                                        : static_cast<uint32_t>((j >> 2) * 16384 + (j & 3) * 32) >> 4;
-          const uint32_t boff = static_cast<uint32_t>(j * 512) >> 4;     // 16 rows of 32 bytes per step
-          umma_led(leader, acc, a_desc0 + aoff, b_desc0 + boff, idesc, jj > 0 ? 1u : 0u);
-        }
-        umma_commit_led(leader, bar_mma);
-        umma_commit_led(leader, &bar_free[st]);
+      for (int jj = 0; jj < kPer; ++jj) {
+        const int j = m * kPer + jj;
+        // byte offsets of contraction step j, in the descriptors' 16-byte units
+        const uint32_t aoff = ADJOINT ? static_cast<uint32_t>(j * 2048) >> 4
+                                      : static_cast<uint32_t>((j >> 2) * 16384 + (j & 3) * 32) >> 4;
+        const uint32_t boff = static_cast<uint32_t>(j * 512) >> 4;     // 16 rows of 32 bytes per step
+        umma_led(leader, acc, a_desc0 + aoff, b_desc0 + boff, idesc, jj > 0 ? 1u : 0u);
       }
+      umma_commit_led(leader, bar_mma);
+      umma_commit_led(leader, &bar_free[st]);
     }
   } else {
     // ---- the state: thread d holds row d of x (16 columns) in fp32
@@ -152,17 +149,15 @@ scan_kernel(const Problem p) {
     for (int it = 0; it < NT; ++it) {
       const size_t z = static_cast<size_t>(bh) * NT + chunk_of(it);
       ST(0)
-      if (has_p) {
-        // critical path: the state as a tensor-core operand
-        {
-          const int sw = (tid >> 2) & 1;     // 32-byte swizzle: the two 16-byte pieces of rows 4-7 of an atom swap
-          *reinterpret_cast<uint4*>(XB + tid * 32 + (sw << 4)) = pack8_f16(x);
-          *reinterpret_cast<uint4*>(XB + tid * 32 + ((sw ^ 1) << 4)) = pack8_f16(x + 8);
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        step_arrive();
+      // critical path: the state as a tensor-core operand
+      {
+        const int sw = (tid >> 2) & 1;     // 32-byte swizzle: the two 16-byte pieces of rows 4-7 of an atom swap
+        *reinterpret_cast<uint4*>(XB + tid * 32 + (sw << 4)) = pack8_f16(x);
+        *reinterpret_cast<uint4*>(XB + tid * 32 + ((sw ^ 1) << 4)) = pack8_f16(x + 8);
       }
+      fence_proxy_async();
+      tc_fence_before();
+      step_arrive();
       ST(1)
       // in the shadow of the product: this chunk's input and decay, the next chunk's loads, the record
       const float a = a_next;
@@ -186,28 +181,23 @@ scan_kernel(const Problem p) {
         *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
       }
       ST(4)
-      if (has_p) {
-        mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
-        ST(5)
-        tc_fence_after();
-        float acc[kMmaWarps * kVs];
-        if (kMmaWarps == 1) tmem_ld16(tmem + lane_base, acc);
-        if (kMmaWarps >= 2) tmem_ld32(tmem + lane_base, acc);
-        if (kMmaWarps == 4) tmem_ld32(tmem + lane_base + 32, acc + 32);
-        tmem_ld_wait();
-        ST(6)
+      mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
+      ST(5)
+      tc_fence_after();
+      float acc[kMmaWarps * kVs];
+      if (kMmaWarps == 1) tmem_ld16(tmem + lane_base, acc);
+      if (kMmaWarps >= 2) tmem_ld32(tmem + lane_base, acc);
+      if (kMmaWarps == 4) tmem_ld32(tmem + lane_base + 32, acc + 32);
+      tmem_ld_wait();
+      ST(6)
 #pragma unroll
-        for (int j = 0; j < kVs; ++j) {
-          float s = acc[j];
-          if (kMmaWarps >= 2) s += acc[kVs + j];
-          if (kMmaWarps == 4) s += acc[2 * kVs + j] + acc[3 * kVs + j];
-          x[j] = rr[j] - s;
-        }
-        ST(7)
-      } else {
-#pragma unroll
-        for (int j = 0; j < kVs; ++j) x[j] = rr[j];
+      for (int j = 0; j < kVs; ++j) {
+        float s = acc[j];
+        if (kMmaWarps >= 2) s += acc[kVs + j];
+        if (kMmaWarps == 4) s += acc[2 * kVs + j] + acc[3 * kVs + j];
+        x[j] = rr[j] - s;
       }
+      ST(7)
     }
 #ifdef LETHE_PHASE_TIMING
     if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 3) printf("SCAN adj=%d total %lld | top %lld write %lld unpack %lld pref %lld rec %lld mmawait %lld ld %lld fma %lld\n", (int)ADJOINT, clock64()-tstart, ph[0],ph[1],ph[2],ph[3],ph[4],ph[5],ph[6],ph[7]);

@@ -41,6 +41,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.lethe_gdn_forward_static_capacity.argtypes = []
     L.lethe_gdn_decode_step.restype = c_int
     L.lethe_gdn_decode_step.argtypes = [c_void_p, c_void_p]
+    L.lethe_gdn_l2norm_qk.restype = c_int
+    L.lethe_gdn_l2norm_qk.argtypes = [c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
+                                                      ctypes.c_float, c_void_p]
+    L.lethe_gdn_l2norm_qk_vjp.restype = c_int
+    L.lethe_gdn_l2norm_qk_vjp.argtypes = [c_void_p] * 6 + [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
+                                                          ctypes.c_float, c_void_p]
     L.lethe_gdn_strerror.restype = ctypes.c_char_p
     L.lethe_gdn_strerror.argtypes = [c_int]
     L.lethe_probe_umma.restype = c_int

@@ -231,9 +231,61 @@ def gdn_backward_raw(q, k, v, g, beta, h0, do, dhT, saved, status, scale: float)
     return buf.dq, buf.dk, buf.dv, buf.dg, buf.dbeta, buf.dh0, buf.scratch
 
 
-def _l2norm(x: Tensor, eps: float = 1e-6) -> Tensor:
-    # same epsilon placement as the reference (gdn_backward.py:9-10)
-    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
+def _l2_working(q: Tensor, k: Tensor) -> tuple[Tensor, Tensor, bool]:
+    """q, k as the normalisation kernels read them: both bf16 if both came as bf16, else both fp32."""
+    f32 = not (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16)
+    dt = torch.float32 if f32 else torch.bfloat16
+    return q.to(dt).contiguous(), k.to(dt).contiguous(), f32
+
+
+def l2norm_qk_raw(q: Tensor, k: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+    """``x * rsqrt(sum x^2 + eps)`` over the last axis of q and of k in one launch (epsilon placed as in
+    the reference, ``gdn_backward.py:9-10``).  Returns bf16 tensors, the type the GDN kernels read."""
+    if not q.is_cuda:
+        raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+    if q.shape != k.shape:
+        raise GdnError("lethe_gdn: q and k must have the same shape")
+    qc, kc, f32 = _l2_working(q, k)
+    qn, kn = torch.empty_like(qc, dtype=torch.bfloat16), torch.empty_like(kc, dtype=torch.bfloat16)
+    D = q.shape[-1]
+    _check(native.lib().lethe_gdn_l2norm_qk(qc.data_ptr(), kc.data_ptr(), qn.data_ptr(), kn.data_ptr(),
+                                            qc.numel() // D, D, int(f32), eps,
+                                            torch.cuda.current_stream(q.device).cuda_stream))
+    return qn, kn
+
+
+def l2norm_qk_vjp_raw(q: Tensor, k: Tensor, dqn: Tensor, dkn: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+    """Gradients with respect to q and k given those with respect to the normalised rows (bf16, as the
+    backward kernels write them).  Returned in the working type of q, k (bf16 or fp32)."""
+    qc, kc, f32 = _l2_working(q, k)
+    dqn, dkn = _prep16(dqn), _prep16(dkn)
+    dq, dk = torch.empty_like(qc), torch.empty_like(kc)
+    D = q.shape[-1]
+    _check(native.lib().lethe_gdn_l2norm_qk_vjp(qc.data_ptr(), kc.data_ptr(), dqn.data_ptr(), dkn.data_ptr(),
+                                                dq.data_ptr(), dk.data_ptr(), qc.numel() // D, D, int(f32), eps,
+                                                torch.cuda.current_stream(q.device).cuda_stream))
+    return dq, dk
+
+
+class _L2NormQK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, eps):
+        ctx.save_for_backward(q, k)
+        ctx.eps = eps
+        return l2norm_qk_raw(q, k, eps)
+
+    @staticmethod
+    def backward(ctx, dqn, dkn):
+        q, k = ctx.saved_tensors
+        dqn = torch.zeros_like(q, dtype=torch.bfloat16) if dqn is None else dqn
+        dkn = torch.zeros_like(k, dtype=torch.bfloat16) if dkn is None else dkn
+        dq, dk = l2norm_qk_vjp_raw(q, k, dqn, dkn, ctx.eps)
+        return dq.to(q.dtype), dk.to(k.dtype), None
+
+
+def l2norm_qk(q: Tensor, k: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+    """Differentiable L2 normalisation of q and k over the channel axis (one kernel each way)."""
+    return _L2NormQK.apply(q, k, eps)
 
 
 class _GdnChunk(torch.autograd.Function):
@@ -315,7 +367,7 @@ def gdn_chunk(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | 
     if scale is None:
         scale = q.shape[-1] ** -0.5
     if use_qk_l2norm:
-        q, k = _l2norm(q.float()).to(q.dtype), _l2norm(k.float()).to(k.dtype)
+        q, k = l2norm_qk(q, k)
     return _GdnChunk.apply(q, k, v, g, beta, h0, float(scale))
 
 
@@ -399,7 +451,7 @@ def gdn_chunk_full(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Ten
     if scale is None:
         scale = q.shape[-1] ** -0.5
     if use_qk_l2norm:
-        q, k = _l2norm(q.float()).to(q.dtype), _l2norm(k.float()).to(k.dtype)
+        q, k = l2norm_qk(q, k)
     return _GdnFull.apply(q, k, v, g, b, w, h0, float(scale))
 
 
@@ -443,12 +495,8 @@ class _Gdn2Op(torch.autograd.Function):
             g_in = (g[..., 0] if scalar_gate else g).float().contiguous()
         ctx.meta = (q.dtype, k.dtype, v.dtype, g.dtype, b.dtype, w.dtype, K, V, scalar_gate, beta is not None,
                     use_qk_l2norm)
-        qf, kf = q.float(), k.float()
-        if use_qk_l2norm:
-            qn, kn = _l2norm(qf), _l2norm(kf)
-        else:
-            qn, kn = qf, kf
-        q16, k16, v16 = _prep16(qn), _prep16(kn), _prep16(v)
+        q16, k16 = l2norm_qk_raw(q, k) if use_qk_l2norm else (_prep16(q), _prep16(k))
+        v16 = _prep16(v)
         o, _hT, saved, status = gdn_forward_raw(q16, k16, v16, g_in, beta, None, scale)
         ctx.save_for_backward(q, k, q16, k16, v16, g_in, beta, saved, status)
         ctx.scale = scale
@@ -463,12 +511,9 @@ class _Gdn2Op(torch.autograd.Function):
         if delta:
             buf.dbeta_write = torch.empty(B, L, H, dtype=torch.float32, device=q16.device)
         backward_into(buf, q16, k16, v16, g_in, beta, None, _prep16(do), None, ctx.scale)
-        dq, dk = buf.dq.float(), buf.dk.float()
-        if l2:   # VJP of x / sqrt(|x|^2 + eps), done by autograd like the reference (gdn2_assemble.py:300-312)
-            with torch.enable_grad():
-                ql = q.detach().float().requires_grad_(True)
-                kl = k.detach().float().requires_grad_(True)
-                dq, dk = torch.autograd.grad((_l2norm(ql), _l2norm(kl)), (ql, kl), (dq, dk))
+        dq, dk = buf.dq, buf.dk
+        if l2:   # VJP of x / sqrt(|x|^2 + eps) (the reference gets it by autograd, gdn2_assemble.py:300-312)
+            dq, dk = l2norm_qk_vjp_raw(q, k, dq, dk)
         grad_g = (buf.dg.unsqueeze(-1).expand(B, L, H, K) / K) if scalar_gate else buf.dg
         if delta:
             grad_b = buf.dbeta.unsqueeze(-1).expand(B, L, H, K) / K

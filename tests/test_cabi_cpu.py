@@ -23,7 +23,8 @@ def test_exports_every_declared_symbol(lib):
     hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
     names = set(re.findall(r"\b(lethe_[a-z0-9_]+)\s*\(", hdr))
     assert {"lethe_gdn_forward", "lethe_gdn_backward", "lethe_gdn_saved_bytes", "lethe_gdn_scratch_bytes",
-            "lethe_gdn_strerror", "lethe_gdn_forward_static", "lethe_gdn_decode_step", "lethe_probe_umma"} <= names
+            "lethe_gdn_strerror", "lethe_gdn_forward_static", "lethe_gdn_decode_step", "lethe_gdn_l2norm_qk",
+            "lethe_gdn_l2norm_qk_vjp", "lethe_probe_umma"} <= names
     for n in names:
         assert hasattr(lib, n), n
 
@@ -36,6 +37,15 @@ def test_decode_step_argument_errors(lib):
                         state=0x4000, o=0x5000)
     rc = lib.lethe_gdn_decode_step(ctypes.byref(a), None)
     assert rc != 0 and b"sizes" in lib.lethe_gdn_strerror(rc)
+
+
+def test_l2norm_argument_errors(lib):
+    rc = lib.lethe_gdn_l2norm_qk(None, None, None, None, 4, 128, 0, 1e-6, None)
+    assert rc != 0 and b"null" in lib.lethe_gdn_strerror(rc)
+    rc = lib.lethe_gdn_l2norm_qk(0x1000, 0x2000, 0x3000, 0x4000, 4, 96, 0, 1e-6, None)
+    assert rc != 0 and b"sizes" in lib.lethe_gdn_strerror(rc)
+    rc = lib.lethe_gdn_l2norm_qk_vjp(0x1000, 0x2000, 0x3000, 0x4008, 0x5000, 0x6000, 4, 128, 0, 1e-6, None)
+    assert rc != 0 and b"align" in lib.lethe_gdn_strerror(rc)
 
 
 def test_workspace_sizes(lib):
