@@ -26,7 +26,7 @@ template <int V, bool DELTA, bool CW>
 __global__ void __launch_bounds__(128)
 bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mdo) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024(smem_raw);
+  unsigned char* sm = CW ? align1024(smem_raw) : align1024_generic(smem_raw);   // measured per variant
   unsigned char* QG = sm;                    // 16 KB: scale gamma q (64 x 128)
   unsigned char* Wt = QG + 16384;            // 16 KB: w
   unsigned char* DO = Wt + 16384;            // do (64 x V)
@@ -172,7 +172,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
                   const __grid_constant__ CUtensorMap mdo, const __grid_constant__ CUtensorMap mdq,
                   const __grid_constant__ CUtensorMap mdk) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024(smem_raw);
+  unsigned char* sm = align1024_generic(smem_raw);
   unsigned char* QT = sm;                       // 16 KB: q (64 x 128)
   unsigned char* KT = QT + 16384;               // 16 KB: k (64 x 128), directly behind q (early view reads q)
   unsigned char* DD = KT + 16384;               // V*256: rows 0-63 do, rows 64-127 dv2

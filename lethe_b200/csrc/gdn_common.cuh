@@ -200,7 +200,18 @@ struct CtaShared {
 };
 
 
+// Next 1024-byte boundary of the dynamic shared memory window, two ways.  `align1024` is plain
+// pointer arithmetic on the shared symbol, so the compiler keeps the shared address space and emits
+// shared-memory loads and stores; `align1024_generic` goes through an integer, after which every
+// access is a generic one.  Same addresses, different instruction selection and scheduling: the
+// channel-wise kernels and the WY backward run 6-15 % faster with the first, the scalar prepare and
+// Stage B kernels 4-9 % faster with the second (measured per kernel on a B200), so each kernel
+// names the one it wants.
 __device__ __forceinline__ unsigned char* align1024(unsigned char* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  return p + ((1024u - (a & 1023u)) & 1023u);
+}
+__device__ __forceinline__ unsigned char* align1024_generic(unsigned char* p) {
   return reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
 }
 
@@ -239,120 +250,160 @@ __device__ __forceinline__ uint32_t rrec_off(int row, int col8) {
 }
 
 // T = (I + M)^-1 for a strictly lower-triangular 64 x 64 M (fp32, row stride MS floats, zeros on and
-// above the diagonal), by forward substitution: thread j (0..63) owns column j and works through four
-// blocks of 16 rows.  A block first collects what the finished blocks above it contribute (sixteen
-// independent sums, T read back from `Tsm`, [48][64] fp32), then resolves its own 16 rows in registers.
-// T is written as fp16 into rows 0-63 of the 128-row SW128 tile `TA`.  No synchronisation inside: a
-// thread reads back only what it wrote itself.
-template <int MS>
-__device__ __forceinline__ void unit_lower_inverse64(const float* Msm, float* Tsm, unsigned char* TA, int j) {
-  const int jb = j >> 4;
-#pragma unroll 1
-  for (int blk = 0; blk < 4; ++blk) {
-    float col[16];
+// above the diagonal), by 16 x 16 blocks on all 256 threads of a CTA (every thread must call; four CTA-wide
+// barriers inside).  With D_b the inverses of the four diagonal blocks of I + M and N_ba = D_b M_ba
+// (b > a), I + N is unit block-lower with N^4 = 0, so
+//   X = (I + N)^-1:  X_b,b-1 = -N_b,b-1;  X_20 = -N_20 + N_21 N_10;  X_31 = -N_31 + N_32 N_21;
+//                    X_30 = -N_30 + N_31 N_10 - N_32 X_20
+//   T_bb = D_b,  T_ba = X_ba D_a.
+// Five short stages of independent 16-long dot products replace 64 dependent row steps.  Block rows
+// live at a stride of 20 floats (left factors are read one row per lane, right factors as float4).
+// `scratch`: 3200 floats (D, then N); X overwrites `Msm`, which is dead once N is formed.
+// T leaves as fp16 in rows 0-63 of the 128-row SW128 tile `TA`, blocks above the diagonal zeroed.
+constexpr int kInvBs = 20;                 // row stride of a 16 x 16 block
+constexpr int kInvBlk = 16 * kInvBs;       // floats per block
+constexpr int kInvScratchFloats = 10 * kInvBlk;
+
+// acc[0..W) += sum_k left[k] * right[k][0..W), W in {2, 4, 8}; right rows RS floats apart
+template <int W, int RS>
+__device__ __forceinline__ void blk_mac(float* acc, const float* left, const float* right) {
+#pragma unroll 4
+  for (int k = 0; k < 16; ++k) {
+    const float a = left[k];
+    if (W == 2) {
+      const float2 r = *reinterpret_cast<const float2*>(right + k * RS);
+      acc[0] = fmaf(a, r.x, acc[0]);
+      acc[1] = fmaf(a, r.y, acc[1]);
+    } else {
 #pragma unroll
-    for (int r = 0; r < 16; ++r) col[r] = (blk * 16 + r == j) ? 1.f : 0.f;
-    if (blk >= jb) {
-      const float* Mb = Msm + blk * 16 * MS;
-      for (int s = jb * 16; s < blk * 16; s += 8) {
-        float t[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = Tsm[(s + i) * 64 + j];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const float4 m0 = *reinterpret_cast<const float4*>(Mb + r * MS + s);
-          const float4 m1 = *reinterpret_cast<const float4*>(Mb + r * MS + s + 4);
-          col[r] -= ((m0.x * t[0] + m0.y * t[1]) + (m0.z * t[2] + m0.w * t[3])) +
-                    ((m1.x * t[4] + m1.y * t[5]) + (m1.z * t[6] + m1.w * t[7]));
-        }
-      }
-#pragma unroll
-      for (int r = 1; r < 16; ++r) {
-        float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-        for (int q = 0; q < (r + 3) / 4; ++q) {
-          const float4 m = *reinterpret_cast<const float4*>(Mb + r * MS + blk * 16 + 4 * q);
-          a0 += m.x * col[4 * q];
-          if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
-          if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
-          if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
-        }
-        col[r] -= a0 + a1;
-      }
-      if (blk < 3) {
-#pragma unroll
-        for (int r = 0; r < 16; ++r) Tsm[(blk * 16 + r) * 64 + j] = col[r];
+      for (int q = 0; q < W / 4; ++q) {
+        const float4 r = *reinterpret_cast<const float4*>(right + k * RS + 4 * q);
+        acc[4 * q] = fmaf(a, r.x, acc[4 * q]);
+        acc[4 * q + 1] = fmaf(a, r.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(a, r.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(a, r.w, acc[4 * q + 3]);
       }
     }
-#pragma unroll
-    for (int r = 0; r < 16; ++r)
-      *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(col[r]);
   }
 }
 
-// The same inverse on 128 threads (four warps): warp w owns columns 16 w .. 16 w + 15, lanes l and
-// l + 16 share column 16 w + (l & 15).  Of a block's sixteen sums over the finished rows each lane of
-// the pair takes eight; the upper lane hands its eight to the lower one, which resolves the block's
-// rows and writes them out.  Every lane of the four warps must call (warp-level exchange inside).
+__device__ __forceinline__ int inv_pair(int b, int a) { return b * (b - 1) / 2 + a; }   // (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
+
 template <int MS>
-__device__ __forceinline__ void unit_lower_inverse64_pairs(const float* Msm, float* Tsm, unsigned char* TA, int t) {
-  const int w = t >> 5, lane = t & 31, hh = lane >> 4, j = 16 * w + (lane & 15);
-#pragma unroll 1
-  for (int blk = 0; blk < 4; ++blk) {
-    if (blk < w) {   // rows above the column's own block are zero (uniform per warp)
-      if (hh == 0) {
-#pragma unroll
-        for (int r = 0; r < 16; ++r) *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(0.f);
-      }
-      continue;
-    }
-    const float* Mb = Msm + blk * 16 * MS;
-    float part[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) part[r] = 0.f;
-    const float* Mh = Mb + hh * 8 * MS;
-    for (int s = w * 16; s < blk * 16; s += 8) {
-      float tv[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) tv[i] = Tsm[(s + i) * 64 + j];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float4 m0 = *reinterpret_cast<const float4*>(Mh + r * MS + s);
-        const float4 m1 = *reinterpret_cast<const float4*>(Mh + r * MS + s + 4);
-        part[r] += ((m0.x * tv[0] + m0.y * tv[1]) + (m0.z * tv[2] + m0.w * tv[3])) +
-                   ((m1.x * tv[4] + m1.y * tv[5]) + (m1.z * tv[6] + m1.w * tv[7]));
-      }
-    }
+__device__ __forceinline__ void unit_lower_inverse64_blocked(float* Msm, float* scratch, unsigned char* TA, int tid) {
+  float* Ds = scratch;                     // [4] diagonal-block inverses
+  float* Ns = scratch + 4 * kInvBlk;       // [6] N_ba, pair order of inv_pair
+  float* Xs = Msm;                         // [3] X_20, X_31, X_30 (from stage 3 on)
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+  // ---- stage 1: D_b by forward substitution, one column per thread; the rest clear T above the diagonal
+  if (tid < 64) {
+    const int b = tid >> 4, j = tid & 15;
+    const float* Mb = Msm + (16 * b) * MS + 16 * b;
     float col[16];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const float up = __shfl_down_sync(0xffffffffu, part[r], 16);   // rows 8-15 from the upper lane
-      col[r] = ((blk * 16 + r == j) ? 1.f : 0.f) - part[r];
-      col[8 + r] = ((blk * 16 + 8 + r == j) ? 1.f : 0.f) - up;
-    }
-    if (hh == 0) {
+    for (int r = 0; r < 16; ++r) col[r] = (r == j) ? 1.f : 0.f;
 #pragma unroll
-      for (int r = 1; r < 16; ++r) {
-        float a0 = 0.f, a1 = 0.f;
+    for (int r = 1; r < 16; ++r) {
+      float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int q = 0; q < (r + 3) / 4; ++q) {
-          const float4 m = *reinterpret_cast<const float4*>(Mb + r * MS + blk * 16 + 4 * q);
-          a0 += m.x * col[4 * q];
-          if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
-          if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
-          if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
-        }
-        col[r] -= a0 + a1;
+      for (int q = 0; q < (r + 3) / 4; ++q) {
+        const float4 m = *reinterpret_cast<const float4*>(Mb + r * MS + 4 * q);
+        a0 += m.x * col[4 * q];
+        if (4 * q + 1 < r) a1 += m.y * col[4 * q + 1];
+        if (4 * q + 2 < r) a0 += m.z * col[4 * q + 2];
+        if (4 * q + 3 < r) a1 += m.w * col[4 * q + 3];
       }
-      if (blk < 3) {
-#pragma unroll
-        for (int r = 0; r < 16; ++r) Tsm[(blk * 16 + r) * 64 + j] = col[r];
-      }
-#pragma unroll
-      for (int r = 0; r < 16; ++r)
-        *reinterpret_cast<__half*>(TA + sw128_off(blk * 16 + r, j, 128)) = __float2half_rn(col[r]);
+      col[r] -= a0 + a1;
     }
-    __syncwarp();   // the upper lanes read the rows just written
+#pragma unroll
+    for (int r = 0; r < 16; ++r) Ds[b * kInvBlk + r * kInvBs + j] = col[r];
+  } else {
+    const int u = tid - 64, pu = u >> 5, r = (u >> 1) & 15, ch = u & 1;
+    // blocks (b, a) with a > b: (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+    const int b = pu < 3 ? 0 : (pu < 5 ? 1 : 2);
+    const int a = pu < 3 ? pu + 1 : (pu < 5 ? pu - 1 : 3);
+    tile_st_chunk(TA, 16 * b + r, 2 * a + ch, 128, zero4);
+  }
+  __syncthreads();
+
+  // ---- stage 2: N_ba = D_b M_ba (one warp per block, a lane = one row x 8 columns); T_bb = D_b
+  if (tid < 192) {
+    const int p = tid >> 5, lane = tid & 31, i = lane >> 1, j0 = 8 * (lane & 1);
+    const int b = p < 1 ? 1 : (p < 3 ? 2 : 3), a = p - b * (b - 1) / 2;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    blk_mac<8, MS>(acc, Ds + b * kInvBlk + i * kInvBs, Msm + (16 * b) * MS + 16 * a + j0);
+    float* out = Ns + p * kInvBlk + i * kInvBs + j0;
+    *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(out + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  } else {
+    const int u = tid - 192;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int idx = 2 * u + e, b = idx >> 5, r = (idx >> 1) & 15, ch = idx & 1;
+      tile_st_chunk(TA, 16 * b + r, 2 * b + ch, 128, pack8_f16(Ds + b * kInvBlk + r * kInvBs + 8 * ch));
+    }
+  }
+  __syncthreads();
+
+  // ---- stage 3: X_20, X_31 (a thread = one row x 4 columns); T_b,b-1 = -N_b,b-1 D_b-1
+  if (tid < 128) {
+    const int x = tid >> 6, i = (tid >> 2) & 15, j0 = 4 * (tid & 3);
+    // x = 0: N_21 N_10 - N_20;  x = 1: N_32 N_21 - N_31
+    const float* left = Ns + (x == 0 ? inv_pair(2, 1) : inv_pair(3, 2)) * kInvBlk + i * kInvBs;
+    const float* right = Ns + (x == 0 ? inv_pair(1, 0) : inv_pair(2, 1)) * kInvBlk + j0;
+    const float* sub = Ns + (x == 0 ? inv_pair(2, 0) : inv_pair(3, 1)) * kInvBlk + i * kInvBs + j0;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    blk_mac<4, kInvBs>(acc, left, right);
+    const float4 n = *reinterpret_cast<const float4*>(sub);
+    *reinterpret_cast<float4*>(Xs + x * kInvBlk + i * kInvBs + j0) =
+        make_float4(acc[0] - n.x, acc[1] - n.y, acc[2] - n.z, acc[3] - n.w);
+  } else if (tid < 224) {
+    const int u = tid - 128, b = (u >> 5) + 1, i = (u >> 1) & 15, jh = u & 1;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    blk_mac<8, kInvBs>(acc, Ns + inv_pair(b, b - 1) * kInvBlk + i * kInvBs, Ds + (b - 1) * kInvBlk + 8 * jh);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = -acc[e];
+    tile_st_chunk(TA, 16 * b + i, 2 * (b - 1) + jh, 128, pack8_f16(acc));
+  }
+  __syncthreads();
+
+  // ---- stage 4: X_30 (a thread = one row x 2 columns); T_20 = X_20 D_0, T_31 = X_31 D_1
+  if (tid < 128) {
+    const int i = tid >> 3, j0 = 2 * (tid & 7);
+    float acc[2] = {0.f, 0.f}, acc2[2] = {0.f, 0.f};
+    blk_mac<2, kInvBs>(acc, Ns + inv_pair(3, 1) * kInvBlk + i * kInvBs, Ns + inv_pair(1, 0) * kInvBlk + j0);
+    blk_mac<2, kInvBs>(acc2, Ns + inv_pair(3, 2) * kInvBlk + i * kInvBs, Xs + j0);
+    const float2 n = *reinterpret_cast<const float2*>(Ns + inv_pair(3, 0) * kInvBlk + i * kInvBs + j0);
+    *reinterpret_cast<float2*>(Xs + 2 * kInvBlk + i * kInvBs + j0) =
+        make_float2((acc[0] - acc2[0]) - n.x, (acc[1] - acc2[1]) - n.y);
+  } else if (tid < 192) {
+    const int u = tid - 128, x = u >> 5, i = (u >> 1) & 15, jh = u & 1;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    blk_mac<8, kInvBs>(acc, Xs + x * kInvBlk + i * kInvBs, Ds + x * kInvBlk + 8 * jh);
+    tile_st_chunk(TA, 16 * (x + 2) + i, 2 * x + jh, 128, pack8_f16(acc));
+  }
+  __syncthreads();
+
+  // ---- stage 5: T_30 = X_30 D_0, one element per thread (a lone warp with eight columns per lane
+  // takes more than twice as long)
+  {
+    const int i = tid >> 4, j = tid & 15;
+    const float* left = Xs + 2 * kInvBlk + i * kInvBs;
+    const float* right = Ds + j;
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; k += 2) {
+      a0 = fmaf(left[k], right[k * kInvBs], a0);
+      a1 = fmaf(left[k + 1], right[(k + 1) * kInvBs], a1);
+    }
+    *reinterpret_cast<__half*>(TA + sw128_off(48 + i, j, 128)) = __float2half_rn(a0 + a1);
   }
 }
 

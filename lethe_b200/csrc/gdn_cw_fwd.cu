@@ -255,7 +255,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   LETHE_PHASE("epi1");
   // ---- T = (I + M)^-1 (fp32, CUDA cores)
   if (DELTA) {
-    if (tid < 128) unit_lower_inverse64_pairs<kMsC>(Msm, Msm + 64 * kMsC, TA, tid);
+    unit_lower_inverse64_blocked<kMsC>(Msm, Msm + 64 * kMsC, TA, tid);
   } else if (tid < 64) {
     {
 #pragma unroll

@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(256)
 prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
                const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024(smem_raw);
+  unsigned char* sm = align1024_generic(smem_raw);
   unsigned char* KQ = sm;                      // 32 KB: rows 0-63 k, rows 64-127 q; later M (fp32), then [w | u]
   unsigned char* BGK = sm + 32768;             // 16 KB: beta gamma k   (64 x 128)
   unsigned char* BV = BGK + 16384;             // beta v (64 x V), directly behind BGK: one N = 128 + V operand
@@ -41,7 +41,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   float* tmp = fs + 256;     // [2]
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 264);
   float* Msm = reinterpret_cast<float*>(KQ);           // [64][kMs]
-  float* Tsm = Msm + 64 * kMs;                          // [48][64]: finished rows of T, fp32
+  float* Tsm = Msm + 64 * kMs;                          // scratch of the inverse (kInvScratchFloats)
   unsigned char* WU = KQ;
 
   // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves take
@@ -191,7 +191,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
 
   // ---- T = (I + M)^-1 (fp32, CUDA cores)
   if (DELTA) {
-    if (tid < 128) unit_lower_inverse64_pairs<kMs>(Msm, Tsm, TA, tid);
+    unit_lower_inverse64_blocked<kMs>(Msm, Tsm, TA, tid);
   } else if (tid < 64) {
     {
 #pragma unroll
@@ -311,7 +311,7 @@ template <int V, bool DELTA, bool CW>
 __global__ void __launch_bounds__(128)
 output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024(smem_raw);
+  unsigned char* sm = CW ? align1024(smem_raw) : align1024_generic(smem_raw);   // measured per variant
   unsigned char* WQ = sm;                       // 32 KB: rows 0-63 w, rows 64-127 scale gamma q
   unsigned char* HT = sm + 32768;               // state image 128 x V
   unsigned char* TAt = HT + V * 256;            // 16 KB [T; A]

@@ -34,8 +34,7 @@ template <bool ADJOINT>
 __global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const Problem p) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                                       ~static_cast<uintptr_t>(1023));
+  unsigned char* sm = align1024_generic(smem_raw);
   unsigned char* Pst = sm;                          // kStages x 32 KB
   // 4 KB: x as the B operand, contracted along its rows (row k = key channel k, 16 columns = 32 bytes):
   // atoms of 8 rows x 32 bytes with the 32-byte swizzle, so that thread k stores its row as two 16-byte pieces
