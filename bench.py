@@ -143,11 +143,13 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 # every kernel's traffic grows in proportion to its chunks).  Keyed by (kernel, gate, d_v, delta); the
 # channel-wise "stageb" and "wy" are two launches each, summed.  Absent combinations report null.
 NCU_DRAM_BYTES_PER_CHUNK = {
-    ("stageb", "scalar", 64, True): (185.1e6 + 105.0e6) / 2048,
-    ("prepare", "scalar", 64, True): (85.0e6 + 128.7e6) / 2048,
-    ("wy", "scalar", 64, True): (203.0e6 + 33.5e6) / 2048,
-    ("scan_bwd", "scalar", 64, True): (101.7e6 + 13.7e6) / 2048,
-    ("prepare", "channel", 128, True): (168.4e6 + 247.2e6) / 2048,
+    ("stageb", "scalar", 64, True): (185.1e6 + 105.6e6) / 2048,
+    ("prepare", "scalar", 64, True): (85.0e6 + 127.9e6) / 2048,
+    ("wy", "scalar", 64, True): (203.0e6 + 34.2e6) / 2048,
+    ("scan_bwd", "scalar", 64, True): (101.7e6 + 14.6e6) / 2048,
+    ("prepare", "channel", 128, True): (168.4e6 + 247.3e6) / 2048,
+    ("scan_fwd", "scalar", 128, False): (140.5e6 + 91.5e6) / 4096,
+    ("scan_bwd", "scalar", 128, False): (136.4e6 + 89.0e6) / 4096,
 }
 
 
