@@ -213,12 +213,21 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
       tmem_ld_wait();
     }
     const float Gr = Gs[r], bval_r = betas[r];
+    // the gate values of this thread's 32 columns go to registers first: a shared-memory load the
+    // compiler cannot tell apart from the stores below would wait for the store before it in every
+    // iteration and serialise the loop at the load latency
+    float gcol[32];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 g4 = *reinterpret_cast<const float4*>(Gs + c0 + 4 * q);
+      gcol[4 * q] = g4.x; gcol[4 * q + 1] = g4.y; gcol[4 * q + 2] = g4.z; gcol[4 * q + 3] = g4.w;
+    }
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const int s = c0 + j;
       float dkk = 0.f;
       if (live) {
-        const float x = (s < r) ? dm[j] * __expf(Gr - Gs[s]) : 0.f;      // dM * ratio, strictly lower
+        const float x = (s < r) ? dm[j] * __expf(Gr - gcol[j]) : 0.f;      // dM * ratio, strictly lower
         dbeta_m += x * kk[j];
         dkk = x * bval_r;
         rowsum_e += dkk * kk[j];
