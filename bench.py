@@ -139,7 +139,7 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 
 # ------------------------------------------------------------------------------------------------
 # DRAM traffic per chunk (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture / chunks of that
-# launch), from the captures summarised under profiles/ (2048-chunk workloads, records larger than L2;
+# launch), from the captures summarised under profiles/ (2048- and 4096-chunk workloads, records larger than L2;
 # every kernel's traffic grows in proportion to its chunks).  Keyed by (kernel, gate, d_v, delta); the
 # channel-wise "stageb" and "wy" are two launches each, summed.  Absent combinations report null.
 NCU_DRAM_BYTES_PER_CHUNK = {
