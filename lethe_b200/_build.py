@@ -13,7 +13,11 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(LIBDIR, "liblethe_gdn.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+# -use_fast_math: subnormal results flush to zero and division / square root are the approximate forms.
+# The gate factors go through exp2 with flush-to-zero instead of the longer subnormal-safe sequence, which
+# is worth 3-8 % of a step on the exp-heavy channel-wise kernels; parity against the fp64 oracle does not
+# move (decays that small are zero in the fp16 operands anyway) and results stay bit-deterministic.
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-use_fast_math",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-I", os.path.join(HERE, "..", "include")]
 FLAGS += os.environ.get("LETHE_NVCC_FLAGS", "").split()      # e.g. -DLETHE_PHASE_TIMING for kernel phase stamps
 
