@@ -172,7 +172,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
                   const __grid_constant__ CUtensorMap mdo, const __grid_constant__ CUtensorMap mdq,
                   const __grid_constant__ CUtensorMap mdk) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024_generic(smem_raw);
+  unsigned char* sm = align1024(smem_raw);
   unsigned char* QT = sm;                       // 16 KB: q (64 x 128)
   unsigned char* KT = QT + 16384;               // 16 KB: k (64 x 128), directly behind q (early view reads q)
   unsigned char* DD = KT + 16384;               // V*256: rows 0-63 do, rows 64-127 dv2

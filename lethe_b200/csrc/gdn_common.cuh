@@ -204,15 +204,30 @@ struct CtaShared {
 // pointer arithmetic on the shared symbol, so the compiler keeps the shared address space and emits
 // shared-memory loads and stores; `align1024_generic` goes through an integer, after which every
 // access is a generic one.  Same addresses, different instruction selection and scheduling: the
-// channel-wise kernels and the WY backward run 6-15 % faster with the first, the scalar prepare and
-// Stage B kernels 4-9 % faster with the second (measured per kernel on a B200), so each kernel
-// names the one it wants.
-__device__ __forceinline__ unsigned char* align1024(unsigned char* p) {
+// channel-wise kernels run 10-15 % faster with the first, the scalar kernels 3-5 % except the prepare
+// kernel without the delta term, which is 10 % faster with the second, as are the scans by 1-3 %
+// (measured per kernel on a B200), so each kernel names the one it wants.
+__device__ __forceinline__ unsigned char* align1024_s_(unsigned char* p) {
   const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
   return p + ((1024u - (a & 1023u)) & 1023u);
 }
-__device__ __forceinline__ unsigned char* align1024_generic(unsigned char* p) {
+__device__ __forceinline__ unsigned char* align1024_g_(unsigned char* p) {
   return reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+// (-DLETHE_ALL_SHARED / -DLETHE_ALL_GENERIC force one flavour everywhere, to repeat the comparison)
+__device__ __forceinline__ unsigned char* align1024(unsigned char* p) {
+#ifdef LETHE_ALL_GENERIC
+  return align1024_g_(p);
+#else
+  return align1024_s_(p);
+#endif
+}
+__device__ __forceinline__ unsigned char* align1024_generic(unsigned char* p) {
+#ifdef LETHE_ALL_SHARED
+  return align1024_s_(p);
+#else
+  return align1024_g_(p);
+#endif
 }
 
 // Called by all threads before one thread issues products that read tiles written by this CTA's

@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(256)
 prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
                const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = align1024_generic(smem_raw);
+  unsigned char* sm = DELTA ? align1024(smem_raw) : align1024_generic(smem_raw);   // measured per variant
   unsigned char* KQ = sm;                      // 32 KB: rows 0-63 k, rows 64-127 q; later M (fp32), then [w | u]
   unsigned char* BGK = sm + 32768;             // 16 KB: beta gamma k   (64 x 128)
   unsigned char* BV = BGK + 16384;             // beta v (64 x V), directly behind BGK: one N = 128 + V operand
