@@ -113,6 +113,12 @@ def cpu_baseline(workload: str, budget_s: float = 20.0):
 
     B, L, H, K, V, gate, delta = WORKLOADS[workload]
     hs = 1
+    # all the host threads this process may use (a torchrun launch exports OMP_NUM_THREADS=1, which would
+    # otherwise pin the CPU arm to one core)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     # (the full six-input op is timed as its one-beta special case: same chunkwise work on the CPU)
     inp = make_inputs(1, L, hs, K, V, gate=gate, delta=bool(delta), seed=0)
     f = {k: (None if t is None else t.float()) for k, t in inp.items()}
