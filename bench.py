@@ -13,9 +13,12 @@ Prints ONE JSON line (rank 0).  `value`: inputs resident in HBM, CUDA events aro
 flushed between steps, max over ranks.  `e2e`: the same step through the public op
 (`lethe_b200.ops.gdn_chunk` + autograd) with pinned host buffers, host->device copies of all inputs
 and device->host copies of all results inside the timed region.  `roofline`: the dominant kernel,
-timed alone with CUDA events.  `cpu_baseline`: the CPU oracle (a port of the reference's PyTorch CPU
-chunkwise path) timed on this machine's host cores on a bounded sample.
-`--impl reference` times that CPU path only (rank 0; other ranks exit).
+timed alone with CUDA events, plus the whole step against the algorithmic bytes and FLOPs of the path
+(HBM and tensor-core fractions for forward, backward and both).  `cpu_baseline`: the reference project's
+own PyTorch CPU chunkwise path (its backward assembly, imported from `oracle/_ref`, the reference compiled
+to bytecode) timed on this machine's host cores on a bounded sample; the CPU oracle port stands in only
+where `oracle/_ref` is absent.  `--impl reference` times that CPU path only (rank 0; other ranks exit):
+W warm-up passes, then K timed passes, every pass really executed.
 """
 
 from __future__ import annotations
@@ -57,8 +60,8 @@ def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return d["hbm_gbs"], d["bf16_tflops"], "measured"
-    return 6650.0, 1590.0, "fallback"
+        return d["hbm_gbs"], d["bf16_tflops"], d.get("bf16_tflops_sustained", d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
 
 
 # ------------------------------------------------------------------------------------------------
@@ -103,44 +106,148 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU baseline (oracle port of the reference's PyTorch CPU chunkwise path)
+# CPU arm: the reference's own PyTorch CPU chunkwise path
 # ------------------------------------------------------------------------------------------------
-def cpu_baseline(workload: str, budget_s: float = 20.0):
-    """Times oracle.chunk_fwd_bwd (fp32, all host threads) on a head-subset of the workload and
-    scales to the full head count (heads are independent).  Returns the cpu_baseline object."""
+CPU_TOKEN_HEADS = {"scalar": 32768, "none": 32768, "channel": 8192}     # bounded sample, by gate kind
+
+
+def cpu_sample_shape(workload: str):
+    """(B_s, H_s) of the bounded CPU sample: whole (batch, head) pairs of the workload, as many as fit the
+    token-head budget (the headline configuration fits whole).  Pairs are independent recurrences, so the
+    sample's time scales linearly to the full workload."""
+    B, L, H, K, V, gate, delta = WORKLOADS[workload]
+    pairs = max(1, min(B * H, CPU_TOKEN_HEADS[gate] // L))
+    Hs = min(H, pairs)
+    Bs = max(1, min(B, pairs // Hs))
+    return Bs, Hs
+
+
+def cpu_reference_pass(workload: str):
+    """Returns (run, kind, what): `run()` executes one forward + backward of the workload's bounded
+    sample on the host cores through the reference's own code (kind "reference") or, when `oracle/_ref` is
+    absent, through the CPU oracle port (kind "port")."""
     from lethe_b200.synth import make_inputs
-    from oracle.gdn_oracle import chunk_fwd_bwd
 
     B, L, H, K, V, gate, delta = WORKLOADS[workload]
-    hs = 1
+    Bs, Hs = cpu_sample_shape(workload)
     # all the host threads this process may use (a torchrun launch exports OMP_NUM_THREADS=1, which would
     # otherwise pin the CPU arm to one core)
     try:
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except (AttributeError, RuntimeError):
         pass
-    # (the full six-input op is timed as its one-beta special case: same chunkwise work on the CPU)
-    inp = make_inputs(1, L, hs, K, V, gate=gate, delta=bool(delta), seed=0)
+    inp = make_inputs(Bs, L, Hs, K, V, gate=gate, delta=bool(delta), seed=0, full=(delta == 2))
     f = {k: (None if t is None else t.float()) for k, t in inp.items()}
+    scale = K ** -0.5
+    from oracle import make_ref
+    if make_ref.import_reference() is not None:
+        from lethe.kernels.cute import gdn2_assemble as A
+        from lethe.kernels.cute import gdn2_family as F
+        kw = dict(scale=scale, use_qk_l2norm=False)
+        if delta == 2:
+            fn, what = (lambda: A.assemble_gdn2_backward_channelwise(f["q"], f["k"], f["v"], f["g"], f["b"], f["w"],
+                                                                     f["do"], **kw)), "assemble_gdn2_backward_channelwise"
+        elif delta and gate == "scalar":
+            fn, what = (lambda: A.assemble_gdn2_backward_scalar(f["q"], f["k"], f["v"], f["g"], f["beta"], f["do"],
+                                                                **kw)), "assemble_gdn2_backward_scalar"
+        elif delta:
+            fn, what = (lambda: F.kda_backward(f["q"], f["k"], f["v"], f["g"], f["beta"], f["do"], **kw)), "kda_backward"
+        elif gate == "channel":
+            fn, what = (lambda: F.gla_backward(f["q"], f["k"], f["v"], f["g"], f["do"], **kw)), "gla_backward"
+        elif gate == "scalar":
+            fn, what = (lambda: F.ssd_backward(f["q"], f["k"], f["v"], f["g"], f["do"], **kw)), "ssd_backward"
+        else:
+            fn, what = (lambda: F.la_backward(f["q"], f["k"], f["v"], f["do"], **kw)), "la_backward"
+        return fn, "reference", (f"the reference's own {what} (chunkwise forward + backward assembly, fp32, no "
+                                 "kernels injected, no initial state: its signature has none)")
+    from oracle.gdn_oracle import chunk_fwd_bwd
+    beta = f.get("beta")
+    return (lambda: chunk_fwd_bwd(f["q"], f["k"], f["v"], f["g"], beta, f["h0"], f["do"], scale=scale),
+            "port", "oracle.chunk_fwd_bwd (CPU port of the reference's chunkwise path; oracle/_ref absent)")
 
-    def run():
+
+def cpu_time_passes(workload: str, steps: int, warmup: int, budget_s: float | None = None):
+    """Runs `warmup` + up to `steps` passes (stopping early once `budget_s` of timed work is spent, never
+    before two).  Returns the cpu_baseline object and the per-pass seconds."""
+    B, L, H, K, V, gate, delta = WORKLOADS[workload]
+    Bs, Hs = cpu_sample_shape(workload)
+    run, kind, what = cpu_reference_pass(workload)
+    for _ in range(max(1, warmup)):
+        run()
+    ts = []
+    while len(ts) < steps and (budget_s is None or len(ts) < 2 or sum(ts) < budget_s):
         t0 = time.perf_counter()
-        chunk_fwd_bwd(f["q"], f["k"], f["v"], f["g"], f["beta"], f["h0"], f["do"], scale=K ** -0.5)
-        return time.perf_counter() - t0
+        run()
+        ts.append(time.perf_counter() - t0)
+    t1 = sum(ts) / len(ts)                      # seconds per pass over Bs x Hs pairs
+    frac = (Bs * Hs) / (B * H)
+    tokens_per_s = (B * L) * frac / t1          # a token spans all H heads; pairs scale linearly
+    cb = {"value": tokens_per_s, "unit": "tokens/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+          "kind": kind, "passes": len(ts), "s_per_pass": t1, "sample_fraction": frac,
+          "sample": f"{what} on B={Bs}, H={Hs}, L={L} of {workload} ({100 * frac:.0f} % of its (batch, head) pairs"
+                    f"{', scaled linearly to all of them' if frac < 1 else ''}); mean of {len(ts)} passes of "
+                    f"{t1:.2f} s after {max(1, warmup)} warm-up"}
+    return cb, ts
 
-    run()                                    # warm
-    reps, spent, ts = 0, 0.0, []
-    while reps < 3 or (spent < budget_s * 0.5 and reps < 20):
-        t = run()
-        ts.append(t)
-        spent += t
-        reps += 1
-    t1 = statistics.median(ts)               # seconds for 1 batch row x 1 head
-    tokens_per_s = L / (t1 * H)              # a token spans all H heads
-    return {"value": tokens_per_s, "unit": "tokens/s", "cores": torch.get_num_threads(),
-            "host_cpus": os.cpu_count(), "kind": "port",
-            "sample": f"oracle.chunk_fwd_bwd fp32 on B=1,H={hs},L={L} of {workload}, median of {reps} "
-                      f"runs of {t1:.2f}s, scaled linearly to H={H} heads"}
+
+def cpu_baseline(workload: str, budget_s: float = 12.0):
+    return cpu_time_passes(workload, steps=10, warmup=1, budget_s=budget_s)[0]
+
+
+# ------------------------------------------------------------------------------------------------
+# Algorithmic work of the path (what a perfectly fused implementation must move and compute)
+# ------------------------------------------------------------------------------------------------
+# Whole-configuration figures for forward + backward, (GFLOP, MB), for the benchmark configurations:
+# dense 2mnk counting per 64-token chunk, every tensor touched once per pass, fp32 chunk-entry state
+# written by the forward and read by the backward.  Other workloads use the same formulas (path_model).
+PATH_TABLE = {
+    "gdn_scalar_B2_H8_L2048_dk128_dv64": (11.86, 105.3),
+    "kda_B2_H8_L2048_dk128_dv128": (18.30, 184.7),
+    "gla_B4_H16_L4096_dk128_dv128": (77.31, 1476.0),
+    "ssd_B4_H16_L4096_dk128_dv128": (77.31, 1476.0),
+    "la_B4_H16_L4096_dk128_dv128": (77.31, 1476.0),
+    "kda_B2_H32_L8192_dk128_dv128": (2342.0 / 8, 23648.0 / 8),
+    "kda_B1_H32_L65536_dk128_dv128": (1171.0, 11824.0),
+}
+
+
+def path_model(workload: str):
+    """Algorithmic FLOPs and bytes of forward and backward for a workload: {"fwd": (flop, bytes), "bwd": ...,
+    "source": ...}.  Per chunk (C = 64): with the delta term forward 6C^2K + 4C^2V + 6CKV + C^3/3, backward
+    12C^2K + 8C^2V + 12CKV + 4C^3; without it 2C^2K + 2C^2V + 4CKV and 4C^2K + 4C^2V + 8CKV.  Per token-head:
+    forward 2(2K+V) + 2V + gate bytes, backward 2(2K+V) + 2V + gate bytes + 2(2K+V) + gate-gradient bytes;
+    state 2 * 4KV / C.  Configurations listed in PATH_TABLE use its totals, split forward / backward in the
+    formulas' proportion."""
+    B, L, H, K, V, gate, delta = WORKLOADS[workload]
+    C = 64
+    Z, TH = B * H * (L // C), B * H * L
+    if delta:
+        ff = 6 * C * C * K + 4 * C * C * V + 6 * C * K * V + C ** 3 / 3
+        fb = 12 * C * C * K + 8 * C * C * V + 12 * C * K * V + 4 * C ** 3
+    else:
+        ff = 2 * C * C * K + 2 * C * C * V + 4 * C * K * V
+        fb = 4 * C * C * K + 4 * C * C * V + 8 * C * K * V
+    gbytes = {"none": 0, "scalar": 4, "channel": 4 * K}[gate] + (4 if delta == 1 else (4 * (K + V) if delta == 2 else 0))
+    state = 4 * K * V / C
+    bf = 2 * (2 * K + V) + 2 * V + gbytes + state
+    bb = 2 * (2 * K + V) + 2 * V + gbytes + 2 * (2 * K + V) + gbytes + state
+    fwd, bwd, src = (ff * Z, bf * TH), (fb * Z, bb * TH), "formulas"
+    if workload in PATH_TABLE:
+        gf, mb = PATH_TABLE[workload]
+        sf, sb_ = gf * 1e9 / (fwd[0] + bwd[0]), mb * 1e6 / (fwd[1] + bwd[1])
+        fwd, bwd, src = (fwd[0] * sf, fwd[1] * sb_), (bwd[0] * sf, bwd[1] * sb_), "configuration table"
+    return {"fwd": fwd, "bwd": bwd, "source": src}
+
+
+def path_fractions(workload: str, fwd_ms: float, bwd_ms: float, step_ms: float, hbm: float, tf: float):
+    """HBM and tensor-core fractions of forward, backward and the whole step on the algorithmic counts."""
+    m = path_model(workload)
+    out = {"source": m["source"], "tensor_peak_tflops": tf}
+    for name, (flop, byt), ms in (("fwd", m["fwd"], fwd_ms), ("bwd", m["bwd"], bwd_ms),
+                                  ("step", (m["fwd"][0] + m["bwd"][0], m["fwd"][1] + m["bwd"][1]), step_ms)):
+        out[name] = {"MB": byt / 1e6, "GFLOP": flop / 1e9, "ms": ms,
+                     "hbm_frac": byt / (ms * 1e-3) / 1e9 / hbm, "tensor_frac": flop / (ms * 1e-3) / 1e12 / tf}
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -193,6 +300,27 @@ def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool, cw: boo
         "scan_bwd": (p_ if delta else 0) + r + img + 512,
         "stageb": 2 * qk + vv + ta + vv + 2 * img + qk + (vv + w + f32k if delta else qk + vv),
         "wy": qk + vv + ta + vv + w + f32k + qk + vv,
+    }[kernel]
+    return per * Z
+
+
+def io_bytes(kernel: str, Z: int, V: int, delta, gate: str) -> int:
+    """The part of `algorithmic_bytes` that the path itself requires whatever the kernel decomposition: the
+    first read of each user tensor in a pass, the final outputs, and the chunk-entry state (written once by
+    the forward scan, read once by Stage B).  The rest of a kernel's bytes are records the kernels hand to
+    one another and re-reads of inputs - traffic this design chose, not traffic the path needs."""
+    qk, vv, img = 64 * 128 * 2, 64 * V * 2, 128 * V * 2
+    gin = {"none": 0, "scalar": 64 * 4, "channel": 64 * 128 * 4}[gate]      # gate values of a chunk
+    bin_ = 64 * 4 if delta == 1 else (64 * (128 + V) * 4 if delta == 2 else 0)
+    per = {
+        "prepare": 2 * qk + vv + gin + bin_,                       # q, k, v, g, beta
+        "scan_fwd": img,                                           # state entering every chunk
+        "output": vv,                                              # o
+        "bwd_pre": qk + vv,                                        # q, do (first touch of the backward)
+        "scan_bwd": 0,
+        # k, state; dq; without the delta term also dk, dv, dg
+        "stageb": qk + img + qk + ((qk + vv + gin) if not delta else 0),
+        "wy": vv + qk + vv + gin + bin_,                           # v; dk, dv, dg, dbeta
     }[kernel]
     return per * Z
 
@@ -329,16 +457,19 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        cb = cpu_baseline(args.workload)
+        t_run = time.perf_counter()
+        cb, ts = cpu_time_passes(args.workload, steps=args.steps, warmup=args.warmup)
         line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s",
-                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": 1e3 * B * L / cb["value"], "higher_is_better": True, "scaling": "weak",
+                "n_gpus": args.gpus, "steps": len(ts), "warmup": max(1, args.warmup),
+                "ms_per_step": 1e3 * cb["s_per_pass"], "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "config": config,
                 "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0},
-                "note": "the reference's CPU chunkwise path is Python and does not travel; this is the "
-                        "CPU oracle port of it, timed on this machine's host cores"}
+                "wall_s": time.perf_counter() - t_run,
+                "note": "every step is one executed pass of the CPU sample described in cpu_baseline.sample; "
+                        "ms_per_step is the measured time of such a pass, value scales it to the whole workload "
+                        "by cpu_baseline.sample_fraction"}
         print(json.dumps(line))
         return
 
@@ -469,6 +600,21 @@ def main():
             single_host[n].copy_(t, non_blocking=True)
 
     e2e_single_ms = timed(e2e_single, 3, 3)
+
+    # the call a training loop makes: the autograd op on tensors that already live on the device
+    dev_leaves = {n: (d[n].clone().requires_grad_(True) if n in d else None) for n in ("q", "k", "v", "g", "beta", "h0")}
+    if delta == 2:
+        dev_leaves.update({n: d[n].clone().requires_grad_(True) for n in ("b", "w")})
+
+    def op_step():
+        L_ = dev_leaves
+        if delta == 2:
+            o, _ = ops.gdn_chunk_full(L_["q"], L_["k"], L_["v"], L_["g"], L_["b"], L_["w"], L_["h0"], scale=scale)
+        else:
+            o, _ = ops.gdn_chunk(L_["q"], L_["k"], L_["v"], L_["g"], L_["beta"], L_["h0"], scale=scale)
+        torch.autograd.grad(o, [t for t in L_.values() if t is not None], d["do"])
+
+    op_ms = timed(op_step, max(args.steps, 10), 3)
     clocks = sampler.stop()
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = sum(t.numel() * t.element_size() for t in outs_host.values())
@@ -480,11 +626,15 @@ def main():
     tokens = B * L * world
 
     if rank == 0:
-        hbm, tf, which = peaks()
+        hbm, tf_burst, tf_sustained, which = peaks()
         Z, BH = B * H * (L // 64), B * H
-        top = max(kern, key=kern.get)
-        ab = algorithmic_bytes(top, Z, BH, V, delta, gate == "channel")
+        # the roofline kernel is named, not picked by max() over noisy timings: the forward's prepare kernel is
+        # the longest single launch of the delta-rule variants, Stage B of the variants without the delta term
+        top = "prepare" if delta else "stageb"
+        total_b = algorithmic_bytes(top, Z, BH, V, delta, gate == "channel")
+        ab = io_bytes(top, Z, V, delta, gate)
         achieved = ab / (kern[top] * 1e-3) / 1e9
+        fr = path_fractions(args.workload, fwd_ms, bwd_ms, ms, hbm, tf_sustained)
         line = {
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
@@ -498,12 +648,26 @@ def main():
                     "api": "lethe_b200.host.HostPipeline (copy-in, kernels and copy-out of consecutive steps "
                            "overlap)", "steps": e2e_steps,
                     "single_step_ms": e2e_single_ms, "single_step_api": "lethe_b200.ops.gdn_chunk + autograd"},
+            "autograd_op_ms": op_ms,
             "gpu_launches": args.steps * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
             "clocks": clocks,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "peak_source": which,
                          "traffic": measured_traffic(top, gate, V, delta, Z),
-                         "launch_ms": kern[top], "algorithmic_bytes": ab},
+                         "launch_ms": kern[top], "algorithmic_bytes": ab,
+                         "algorithmic_bytes_note": "inputs / outputs / state the path itself requires of this "
+                                                   "kernel (bench.py::io_bytes); records it writes for later "
+                                                   "kernels are counted separately below",
+                         "record_bytes": total_b - ab,
+                         "with_records": {"bytes": total_b, "achieved": total_b / (kern[top] * 1e-3) / 1e9,
+                                          "frac": total_b / (kern[top] * 1e-3) / 1e9 / hbm},
+                         # the whole path on its algorithmic bytes and FLOPs (sustained bf16 peak: the step
+                         # is timed inside a long loop)
+                         "path": fr,
+                         "kernels": {n: {"ms": kern[n], "io_bytes": io_bytes(n, Z, V, delta, gate),
+                                         "record_bytes": algorithmic_bytes(n, Z, BH, V, delta, gate == "channel")
+                                         - io_bytes(n, Z, V, delta, gate)} for n in kern}},
+            "hbm_frac": fr["step"]["hbm_frac"], "tensor_frac": fr["step"]["tensor_frac"],
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload)

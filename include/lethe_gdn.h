@@ -12,7 +12,8 @@
  *               closed Stage B (:521-585) and the WY / triangular-inverse VJP K#2 (K2Fn, :33-44).
  *
  * Ownership: the caller allocates every buffer (inputs, outputs, the two workspaces and the status
- * word) on the current device; the library allocates nothing and keeps no state between calls.
+ * word) on one GPU; the library works on the GPU that owns `q` (it need not be the calling thread's
+ * current device), allocates nothing and keeps no state between calls.
  * Threading: re-entrant; all work is enqueued on the given stream; no call synchronises.
  * Errors: a non-zero return means nothing was launched (see lethe_gdn_strerror).  Device-side waits
  * are bounded; a wait that gave up leaves a non-zero code in *status, readable once the stream has
@@ -20,6 +21,7 @@
  *
  * Layouts (all row-major, innermost dimension contiguous):
  *   q, k        [B, L, H, K]  bf16          v, o, do, dv [B, L, H, V]  bf16     dq, dk [B, L, H, K] bf16
+ *               (q, k, dq, dk: fp16 when args->qk_f16 is set)
  *   g           [B, L, H] (gate = 1) or [B, L, H, K] (gate = 2), fp32, natural-log decay (<= 0)
  *   beta        [B, L, H] fp32 (delta = 1)
  *   h0, hT, dhT, dh0   [B, H, K, V] fp32
@@ -96,6 +98,11 @@ typedef struct LetheGdnArgs {
   /* concurrently on different streams with the same tensors and workspaces (no counterpart in the reference). */
   uint32_t bh_begin;
   uint32_t bh_count;
+  /* Non-zero: q, k (inputs) and dq, dk (outputs) hold IEEE fp16 instead of bf16.  fp16 is the type of the  */
+  /* tensor-core operands, so a caller that forms q, k in fp32 (the L2 normalisation below) rounds them      */
+  /* once, as the reference does when it stages operands (gdn2_bwd_dhu_l3.py:477-479), instead of twice.     */
+  /* v, o, d_o, dv stay bf16.                                                                               */
+  uint32_t qk_f16;
 } LetheGdnArgs;
 
 /* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */
@@ -119,9 +126,13 @@ int lethe_gdn_backward(const LetheGdnArgs* args, void* cuda_stream);
  *   - the records are not kept for a backward pass (inference / evaluation only);
  *   - all calls on one GPU share the array: calls that could overlap on the GPU must be put on one
  *     stream; nothing needs clearing between calls;
- *   - the first call on each GPU looks up the array's device address; make that call before any
- *     stream capture starts.
- * The call itself allocates nothing (no cudaMalloc, no cudaFree, no library that would). */
+ *   - every GPU has its own copy of the array.  The call works on the GPU that owns args->q,
+ *     whatever device the calling thread has selected, and uses that GPU's copy;
+ *   - the first call for each GPU looks up the array's device address there and may make the driver
+ *     load the library's code onto that GPU (this is when the 16 MiB get reserved); make that call
+ *     before any stream capture starts.
+ * After that first call on a GPU, a call allocates nothing (no cudaMalloc, no cudaFree, no library
+ * that would). */
 int lethe_gdn_forward_static(const LetheGdnArgs* args, void* cuda_stream);
 size_t lethe_gdn_forward_static_capacity(void);
 
@@ -152,22 +163,22 @@ int lethe_gdn_decode_step(const LetheGdnDecodeArgs* args, void* cuda_stream);
  * use_qk_l2norm is set; the reference differentiates it by autograd,
  * src/lethe/kernels/references/gdn2_assemble.py:300-312):
  *   y = x * rsqrt(sum_d x_d^2 + eps);      dx = r (dy - y (y . dy)),  r = rsqrt(sum_d x_d^2 + eps).
- * q, k: [rows, D] contiguous, bf16 (in_f32 == 0) or fp32 (in_f32 != 0); D in {64, 128}; rows = B L H.
- * qn, kn: bf16 [rows, D], the tensors lethe_gdn_forward / lethe_gdn_backward then read.
- * dqn, dkn: bf16 [rows, D], the dq / dk lethe_gdn_backward wrote; dq, dk: [rows, D] in the type of
- * q, k (may alias dqn, dkn when that type is bf16).  One launch each; every pointer 16-byte aligned. */
+ * flags: LETHE_L2_IN_F32  - q, k (and the returned dq, dk) are fp32 instead of bf16;
+ *        LETHE_L2_NORM_F16 - the normalised rows qn, kn and their gradients dqn, dkn are fp16 instead
+ *                            of bf16 (pair it with LetheGdnArgs::qk_f16 on the forward / backward
+ *                            calls: the rows are then rounded once, to the operand type).
+ * q, k: [rows, D] contiguous; D in {64, 128}; rows = B L H.
+ * qn, kn: 16-bit [rows, D], the tensors lethe_gdn_forward / lethe_gdn_backward then read.
+ * dqn, dkn: 16-bit [rows, D], the dq / dk lethe_gdn_backward wrote; dq, dk: [rows, D] in the type of
+ * q, k (may alias dqn, dkn when both are bf16).  One launch each; every pointer 16-byte aligned. */
+enum { LETHE_L2_IN_F32 = 1, LETHE_L2_NORM_F16 = 2 };
 int lethe_gdn_l2norm_qk(const void* q, const void* k, void* qn, void* kn, int64_t rows, int32_t D,
-                        int32_t in_f32, float eps, void* cuda_stream);
+                        int32_t flags, float eps, void* cuda_stream);
 int lethe_gdn_l2norm_qk_vjp(const void* q, const void* k, const void* dqn, const void* dkn, void* dq, void* dk,
-                            int64_t rows, int32_t D, int32_t in_f32, float eps, void* cuda_stream);
+                            int64_t rows, int32_t D, int32_t flags, float eps, void* cuda_stream);
 
 /* Text for a return code of the calls above or for a device status code. */
 const char* lethe_gdn_strerror(int code);
-
-/* Test hook (not part of the GDN interface): one tcgen05 product on one CTA, used by the toolkit
- * self-test.  No counterpart in the reference. */
-int lethe_probe_umma(const void* A, const void* B, float* D, int* status, int a_mn, int b_mn, int N,
-                     int kc, int fill, int a_neg, int twice, void* cuda_stream);
 
 #ifdef __cplusplus
 }

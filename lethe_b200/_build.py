@@ -1,65 +1,120 @@
 """Build recipe for the CUDA library: every ``csrc/*.cu`` is compiled for sm_100a and linked into
-``lethe_b200/_lib/liblethe_gdn.so`` (kept in-tree so that it travels with the checkout)."""
+``lethe_b200/_lib/liblethe_gdn.so`` (kept in-tree so that it travels with the checkout).
+
+``build_probe()`` builds the test-only self-test kernels of ``tests/native/probe.cu`` into
+``tests/native/_lib/libletheprobe.so``; the product library does not contain them.
+
+Several processes may call ``build()`` at once (one rank per GPU under ``torchrun``): the work is done
+under a file lock, objects and libraries are written to temporary names and renamed into place."""
 
 from __future__ import annotations
 
+import fcntl
 import os
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(LIBDIR, "liblethe_gdn.so")
+PROBE_SRC = os.path.join(ROOT, "tests", "native", "probe.cu")
+PROBE_LIBDIR = os.path.join(ROOT, "tests", "native", "_lib")
+PROBE_LIB = os.path.join(PROBE_LIBDIR, "libletheprobe.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 # -use_fast_math: subnormal results flush to zero and division / square root are the approximate forms.
 # The gate factors go through exp2 with flush-to-zero instead of the longer subnormal-safe sequence, which
 # is worth 3-8 % of a step on the exp-heavy channel-wise kernels; parity against the fp64 oracle does not
 # move (decays that small are zero in the fp16 operands anyway) and results stay bit-deterministic.
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-use_fast_math",
-         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-I", os.path.join(HERE, "..", "include")]
-FLAGS += os.environ.get("LETHE_NVCC_FLAGS", "").split()      # e.g. -DLETHE_PHASE_TIMING for kernel phase stamps
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+FLAGS += os.environ.get("LETHE_NVCC_FLAGS", "").split()
 
 
 def _sources():
     return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def _newest_dep():
+def _newest(*roots):
     t = 0.0
-    for root in (CSRC, os.path.join(HERE, "..", "include")):
+    for root in roots:
         for f in os.listdir(root):
-            t = max(t, os.path.getmtime(os.path.join(root, f)))
+            p = os.path.join(root, f)
+            if os.path.isfile(p):
+                t = max(t, os.path.getmtime(p))
     return t
+
+
+class _Lock:
+    def __init__(self, path):
+        self.path = path
+
+    def __enter__(self):
+        self.f = open(self.path, "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+
+    def __exit__(self, *exc):
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+
+
+def _run(cmd, what, verbose):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"{what} failed:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        sys.stderr.write(r.stderr)
+
+
+def _compile(src, obj, verbose):
+    tmp = f"{obj}.{os.getpid()}.tmp"
+    cmd = [NVCC, *FLAGS, "-c", src, "-o", tmp]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    _run(cmd, f"nvcc {os.path.basename(src)}", verbose)
+    os.replace(tmp, obj)
+    return obj
+
+
+def _link(objs, lib):
+    tmp = f"{lib}.{os.getpid()}.tmp"
+    _run([NVCC, "-shared", "-o", tmp, *objs], f"link {os.path.basename(lib)}", False)
+    os.replace(tmp, lib)
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile if any source is newer than the library.  Returns the library path."""
     os.makedirs(LIBDIR, exist_ok=True)
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_dep():
+    fresh = lambda: os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest(CSRC, os.path.join(ROOT, "include"))
+    if not force and fresh():
         return LIB
-    objs = []
-
-    def cc(src):
-        obj = os.path.join(LIBDIR, src[:-3] + ".o")
-        cmd = [NVCC, *FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
-        if verbose:
-            sys.stderr.write(r.stderr)
-        return obj
-
-    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
-        objs = list(ex.map(cc, _sources()))
-    r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs], capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    with _Lock(os.path.join(LIBDIR, ".build.lock")):
+        if not force and fresh():      # another process built it while this one waited
+            return LIB
+        with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+            objs = list(ex.map(lambda s: _compile(os.path.join(CSRC, s), os.path.join(LIBDIR, s[:-3] + ".o"), verbose),
+                               _sources()))
+        _link(objs, LIB)
     return LIB
+
+
+def build_probe(force: bool = False, verbose: bool = False) -> str:
+    """The test-only self-test library (tcgen05 / TMA toolkit probe, starved-wait probe)."""
+    os.makedirs(PROBE_LIBDIR, exist_ok=True)
+    fresh = lambda: (os.path.exists(PROBE_LIB) and
+                     os.path.getmtime(PROBE_LIB) >= max(_newest(CSRC), _newest(os.path.dirname(PROBE_SRC))))
+    if not force and fresh():
+        return PROBE_LIB
+    with _Lock(os.path.join(PROBE_LIBDIR, ".build.lock")):
+        if not force and fresh():
+            return PROBE_LIB
+        obj = _compile(PROBE_SRC, os.path.join(PROBE_LIBDIR, "probe.o"), verbose)
+        _link([obj], PROBE_LIB)
+    return PROBE_LIB
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_probe(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -74,6 +74,7 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
     p->nbh = static_cast<int>(a->bh_count);
   }
   p->scale = a->scale;
+  p->qk16 = a->qk_f16 ? 1 : 0;
   p->q = static_cast<const __nv_bfloat16*>(a->q);
   p->k = static_cast<const __nv_bfloat16*>(a->k);
   p->v = static_cast<const __nv_bfloat16*>(a->v);
@@ -114,7 +115,7 @@ extern "C" int lethe_gdn_forward(const LetheGdnArgs* a, void* stream) {
   int e = fill_problem(a, &p, false);
   if (e) return e;
   DeviceGuard guard(a->q);
-  if (!guard.ok) return kErrDriver;
+  if (!guard.ok) return kErrDevice;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap mq, mk, mv;
   if ((e = token_map(&mq, a->q, a->dims, kK))) return e;
@@ -134,7 +135,7 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
   int e = fill_problem(a, &p, true);
   if (e) return e;
   DeviceGuard guard(a->q);
-  if (!guard.ok) return kErrDriver;
+  if (!guard.ok) return kErrDevice;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap mq, mk, mv, mdo;
   if ((e = token_map(&mq, a->q, a->dims, kK))) return e;
@@ -175,21 +176,38 @@ extern "C" int lethe_gdn_backward(const LetheGdnArgs* a, void* stream) {
 // race on it; callers serialise them on one stream.
 //
 // In host code the array's name is only a handle; the device address comes from
-// cudaGetSymbolAddress, looked up once per device by the first call on that device (with that
-// device current).  That first call should therefore happen before any stream capture begins.
+// cudaGetSymbolAddress.  Every GPU has its own copy of the array, so the address is looked up per
+// device, by the first call whose tensors live on that device, with that device made current for
+// the lookup: the device is the one that owns `q`, not whatever device the calling thread happens
+// to have selected (a worker thread of a multi-GPU process usually has device 0 selected).  That
+// first call may also make the driver load the library's code onto the GPU, which is the moment
+// the 16 MiB are reserved there; it should therefore happen before any stream capture begins.
 // ---------------------------------------------------------------------------------------------
 constexpr size_t kStaticSavedBytes = size_t(16) << 20;
+constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_saved[kStaticSavedBytes + 1024];
-static unsigned char* g_static_saved_ptr[64] = {};
+static unsigned char* g_static_saved_ptr[kMaxDevices] = {};
 static std::mutex g_static_saved_mu;
 
-static int static_saved_address(unsigned char** out) {
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kErrDriver;
+// Device that owns a device pointer, or -1.
+static int device_of(const void* ptr) {
+  cudaPointerAttributes at;
+  if (!ptr || cudaPointerGetAttributes(&at, ptr) != cudaSuccess || at.type != cudaMemoryTypeDevice) {
+    cudaGetLastError();      // a host pointer leaves a sticky-looking error behind on some drivers
+    return -1;
+  }
+  return at.device;
+}
+
+// Address of the built-in workspace on device `dev`, which must be the calling thread's current device.
+static int static_saved_address(int dev, unsigned char** out) {
+  if (dev < 0 || dev >= kMaxDevices) return kErrDevice;
   std::lock_guard<std::mutex> lock(g_static_saved_mu);
   if (!g_static_saved_ptr[dev]) {
     void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_static_saved) != cudaSuccess || !ptr) return kErrDriver;
+    if (cudaGetSymbolAddress(&ptr, g_static_saved) != cudaSuccess || !ptr) return kErrSymbol;
+    const int owner = device_of(ptr);
+    if (owner >= 0 && owner != dev) return kErrSymbol;     // never hand a kernel another GPU's copy
     const uintptr_t a = (reinterpret_cast<uintptr_t>(ptr) + 1023) & ~static_cast<uintptr_t>(1023);
     g_static_saved_ptr[dev] = reinterpret_cast<unsigned char*>(a);   // the records want 1 KiB alignment
   }
@@ -202,9 +220,14 @@ extern "C" size_t lethe_gdn_forward_static_capacity(void) { return kStaticSavedB
 extern "C" int lethe_gdn_forward_static(const LetheGdnArgs* a, void* stream) {
   if (!a) return kErrNull;
   if (!dims_ok(a->dims)) return kErrDims;
+  if (!a->q) return kErrNull;
   if (make_layout(a->dims).saved_total > kStaticSavedBytes) return kErrTooLarge;
+  const int dev = device_of(a->q);
+  if (dev < 0) return kErrDevice;
+  DeviceGuard guard(a->q);            // the lookup below and the launches run with q's device current
+  if (!guard.ok || guard.dev != dev) return kErrDevice;
   unsigned char* ws = nullptr;
-  const int e = static_saved_address(&ws);
+  const int e = static_saved_address(dev, &ws);
   if (e) return e;
   LetheGdnArgs b = *a;
   b.saved = ws;
@@ -220,9 +243,11 @@ extern "C" const char* lethe_gdn_strerror(int code) {
     case kErrDims: return "unsupported sizes (need K = 128, V in {64, 128}, L a multiple of 64)";
     case kErrAlign: return "a pointer is not aligned (16 bytes for tensors, 1024 for workspaces)";
     case kErrWorkspace: return "workspace too small";
-    case kErrDriver: return "tensor-map encoding failed";
+    case kErrDriver: return "tensor-map encoding failed (driver entry point missing or bad tensor geometry)";
     case kErrLaunch: return "kernel launch failed";
     case kErrFlags: return "unsupported gate / delta combination";
+    case kErrDevice: return "the device that owns q could not be made current, or a buffer is not device memory of that GPU";
+    case kErrSymbol: return "the address of the library's built-in workspace could not be looked up on this GPU";
     case kErrTooLarge: return "problem needs more workspace than the library's built-in 16 MiB (use lethe_gdn_forward)";
     default: break;
   }

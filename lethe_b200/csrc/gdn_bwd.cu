@@ -1,5 +1,5 @@
-// Chunk-parallel backward kernels.  One CTA of 128 threads per chunk, tcgen05 products with
-// M = 128 and stacked 64-row operands as in the forward kernels.
+// Chunk-parallel backward kernels.  One CTA per chunk (128 threads in `bwd_pre`, 256 in Stage B),
+// tcgen05 products with M = 128 and stacked 64-row operands as in the forward kernels.
 //
 //   bwd_pre    : Rb = (scale gamma q)^T do - w^T (A^T do)          input of the adjoint state scan
 //   bwd_stageb : dv2, dq, the Stage-B part of dk and of the gate gradient, dw
@@ -75,7 +75,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8];
-    unpack8_bf16(tile_ld_chunk(QG, r, ch, 64), x);
+    unpack8_in(tile_ld_chunk(QG, r, ch, 64), x, p.qk16);
     if (CW) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[gidx(r, ch * 8 + i)]);
@@ -225,7 +225,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     tmem_alloc(&cs->tmem_slot, kCols);
     tmem_relinquish();
   }
-  LETHE_PHASE_INIT();
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;   // token index of row 0 (stride H)
   float gval = 0.f;
   if (tid < 64 && p.gate == LETHE_GATE_SCALAR) gval = p.g[tok0 + static_cast<size_t>(tid) * p.H];
@@ -243,7 +242,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   const float Glast = Gs[63];
   if (tid < 64) decs[tid] = __expf(Glast - G);
 
-  LETHE_PHASE("setup");
   // the loads above fetch inputs and records older than the adjoint scan; once it is complete (at once,
   // except for the CTAs that started early) its dh image is fetched too
   griddep_wait();
@@ -253,13 +251,12 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_dh);
   }
   mbar_wait_warp(bar_load, 0, ctl, 411);
-  LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8];
-    unpack8_bf16(tile_ld_chunk(KT, r, ch, 64), x);
+    unpack8_in(tile_ld_chunk(KT, r, ch, 64), x, p.qk16);
     tile_st_chunk(KT, r, ch, 64, pack8_f16(x));
-    unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
+    unpack8_in(tile_ld_chunk(QT, r, ch, 64), x, p.qk16);
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
@@ -269,7 +266,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     tile_st_chunk(DD, r, ch, 128, pack8_f16(x));
   }
   sync_for_issue();
-  LETHE_PHASE("convert");
   mbar_wait_warp(bar_dh, 0, ctl, 415);
 
   uint32_t ph = 0;
@@ -297,9 +293,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     for (int i = 0; i < 8; ++i) dhh += x[i] * y[i];
   }
   dhh = cta_sum256(dhh, tid, tmp + 2) * __expf(Glast);
-  LETHE_PHASE("issue1");
   wait_products(bar_mma, ph, ctl, 412);
-  LETHE_PHASE("g1");
   if (tq >= 64) {
     const int r = tq - 64;
     const float de = decs[r];
@@ -354,7 +348,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     t2p[half * 64 + r] = t2;
   }
   sync_for_issue();
-  LETHE_PHASE("epi1");
 
   // ---- group 2a: cB = [do; dv2] h^T;  cA2 = dAr k (lanes 0-63: dq_intra)
   if (warp == 0 || warp == 4) {
@@ -372,9 +365,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
       bulk_commit();
     }
   }
-  LETHE_PHASE("issue2");
   wait_products(bar_mma, ph, ctl, 413);
-  LETHE_PHASE("g2");
   // The operand tiles of this group are dead now: dq and dw are staged in them as the images their
   // consumers read and leave by tensor-map / bulk stores.
   if (tid == 0) bulk_wait_read();
@@ -401,7 +392,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
           t1 += a * qv[e];
           o8[e] = a + dqi[8 * i + e];
         }
-        tile_st_chunk(SQ, r, jb * 4 + i, 64, pack8_bf16(o8));
+        tile_st_chunk(SQ, r, jb * 4 + i, 64, pack8_out(o8, p.qk16));
       }
     }
     t1p[half * 64 + r] = t1;
@@ -419,7 +410,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   sync_for_issue();
-  LETHE_PHASE("epi2a");
 
   // ---- group 2b: cD1 = dAr^T q;  cD2 = v_new dh^T  (lanes 0-63)
   if (warp == 0 || warp == 4) {
@@ -438,7 +428,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   wait_products(bar_mma, ph, ctl, 414);
-  LETHE_PHASE("g2b");
   __syncthreads();                   // every thread is past the products: h / dh become the dk staging tile
   unsigned char* SK = Ht;            // delta: fp32 dk partial, 32 KB (runs on into dh); else dk bf16
   if (tq < 64) {
@@ -462,7 +451,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
               make_float4(dkv[4 * i], dkv[4 * i + 1], dkv[4 * i + 2], dkv[4 * i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tile_st_chunk(SK, r, jb * 4 + i, 64, pack8_bf16(dkv + 8 * i));
+        for (int i = 0; i < 4; ++i) tile_st_chunk(SK, r, jb * 4 + i, 64, pack8_out(dkv + 8 * i, p.qk16));
       }
     }
   }
@@ -476,7 +465,6 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
     bulk_commit();
   }
-  LETHE_PHASE("epi2b");
   // ---- Stage-B gate gradient of the chunk (before the reverse cumulative sum)
   float dG = 0.f;
   {
@@ -498,22 +486,17 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-template <typename Kern>
-static int set_smem(Kern kern, int smem) {
-  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess ? kOk : kErrLaunch;
-}
-
 template <int V, bool DELTA, bool CW>
 static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
   const int smem = 16384 * 3 + V * 256 + 128 * 4 + (CW ? 32768 : 0) + 1024;
-  if (set_smem(bwd_pre_kernel<V, DELTA, CW>, smem)) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(bwd_pre_kernel<V, DELTA, CW>, smem)) return kErrLaunch;
   bwd_pre_kernel<V, DELTA, CW><<<p.nbh * p.NT, 128, smem, st>>>(p, mq, mdo);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
@@ -522,7 +505,8 @@ static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtens
                            const OutMaps& mo, cudaStream_t st) {
   const int smem = 16384 + 16384 + V * 256 + 8192 + 8192 + V * 128 + V * 256 * 2 + 656 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (set_smem(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
   if (launch_dependent(bwd_stageb_kernel<V, DELTA>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk, mdo,
                        mo.dq, mo.dk) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;

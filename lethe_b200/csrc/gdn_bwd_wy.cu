@@ -69,7 +69,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     tmem_alloc(&cs->tmem_slot, kCols);
     tmem_relinquish();
   }
-  LETHE_PHASE_INIT();
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
   float gval = 0.f, bval = 0.f, dgb = 0.f;
   if (tid < 64) {
@@ -88,7 +87,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     bgs[tid] = bval * __expf(G);
   }
   __syncthreads();
-  LETHE_PHASE("setup");
   // the loads above fetch inputs and records older than Stage B; once Stage B is complete (at once, except
   // for the CTAs that started early) what it wrote is fetched too
   griddep_wait();
@@ -102,11 +100,10 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   }
   if (tid < 64) dgb = reinterpret_cast<const float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb)[tid];
   mbar_wait_warp(bar_load, 0, ctl, 421);
-  LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
-    unpack8_bf16(tile_ld_chunk(T1, r, ch, 128), x);
+    unpack8_in(tile_ld_chunk(T1, r, ch, 128), x, p.qk16);
     tile_st_chunk(T1, r, ch, 128, pack8_f16(x));
     const float ga = __expf(Gs[r]);
 #pragma unroll
@@ -127,7 +124,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     tile_st_chunk(VT, r, ch, 64, pack8_f16(x));
   }
   sync_for_issue();
-  LETHE_PHASE("convert");
   mbar_wait_warp(bar_post, 0, ctl, 427);
 
   uint32_t ph = 0;
@@ -150,7 +146,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     uint32_t ph1 = 0;
     wait_products(bar_g1, ph1, ctl, 422);
   }
-  LETHE_PHASE("g1");
   const int c0 = half * 32;           // this half's 32 columns of every 64-column accumulator
   const bool live = (half == 0) || ((warp & 1) != 0);   // rows 0-31 have nothing right of column 31 in a triangle
   float pk = 0.f;
@@ -174,7 +169,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     prt[(half * 5 + 0) * 64 + tq] = pk;
   }
   sync_for_issue();
-  LETHE_PHASE("epi1");
   // ---- group 2: X = dT T^T
   if (warp == 0) {
     tc_fence_after();
@@ -183,7 +177,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 423);
-  LETHE_PHASE("g2");
   if (tq < 64) {
     float d[32];
     tmem_ld32(R1 + lane_base + c0, d);
@@ -192,7 +185,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     for (int q = 0; q < 4; ++q) tile_st_chunk(W8, tq, half * 4 + q, 64, pack8_f16(d + 8 * q));
   }
   sync_for_issue();
-  LETHE_PHASE("epi2");
   // ---- group 3: dM = -T^T X
   if (warp == 0) {
     tc_fence_after();
@@ -201,7 +193,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 424);
-  LETHE_PHASE("g3");
   float kk[32];
   if (tq < 64) {
     const int r = tq;
@@ -238,7 +229,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     prt[(half * 5 + 2) * 64 + r] = rowsum_e;
   }
   __syncthreads();
-  LETHE_PHASE("epi3a");
   if (tq < 64) {
     const int r = tq;
     float colsum_e = 0.f;
@@ -263,7 +253,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     prt[(half * 5 + 3) * 64 + r] = colsum_e;
   }
   sync_for_issue();
-  LETHE_PHASE("epi3b");
   // ---- group 4: dk accumulator = (dkk + dkk^T) k + T'^T dw
   if (warp == 0) {
     tc_fence_after();
@@ -278,7 +267,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     }
   }
   wait_products(bar_mma, ph, ctl, 425);
-  LETHE_PHASE("g4");
   // [k; dw] is dead once the last products are done: dk and dv are staged there as bf16 tiles and
   // leave by tensor-map stores
   unsigned char* SKo = T1;            // dk: 64 x 128, two atoms
@@ -321,7 +309,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
         float o8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) o8[e] = bb[e] + sk[8 * i + e];
-        tile_st_chunk(SKo, r, jb * 4 + i, 64, pack8_bf16(o8));
+        tile_st_chunk(SKo, r, jb * 4 + i, 64, pack8_out(o8, p.qk16));
       }
     }
   }
@@ -332,7 +320,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
     for (int a = 0; a < V / 64; ++a) tma_store_4d(&mdv, SV + a * 8192, a * 64, h, c * kC, b);
     bulk_commit();
   }
-  LETHE_PHASE("epi4");
   float dgv = 0.f;
   if (tid < 64) {
     const int r = tid;
@@ -357,7 +344,6 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
@@ -365,8 +351,8 @@ template <int V>
 static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, const OutMaps& mo,
                         cudaStream_t st) {
   const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 904 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (cudaFuncSetAttribute(bwd_wy2_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(bwd_wy2_kernel<V>, smem)) return kErrLaunch;
   if (launch_dependent(bwd_wy2_kernel<V>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mk, mv, mo.dk, mo.dv) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;

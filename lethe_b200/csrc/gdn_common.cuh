@@ -1,7 +1,7 @@
 // Shared definitions of the GDN kernels: problem description, workspace layout, small device helpers.
 //
 // Work decomposition.  A "chunk" is 64 consecutive tokens of one (batch, head) pair; chunks are
-// numbered z = (b*H + h)*NT + c.  Chunk-parallel kernels run one CTA of 128 threads per chunk;
+// numbered z = (b*H + h)*NT + c.  Chunk-parallel kernels run one CTA (128 or 256 threads) per chunk;
 // the scan kernel runs one CTA per (b, h, 16-column slice of V) and walks the chunks in order.
 //
 // Per-chunk records in the workspaces ("image" = the SW128 shared-memory tile image, so that a
@@ -36,40 +36,6 @@
 
 #include "../../include/lethe_gdn.h"
 #include "tiles.cuh"
-
-// Development aid: with -DLETHE_PHASE_TIMING one CTA of every instrumented kernel records clock64()
-// at its phase boundaries and prints the differences when it ends (never enabled in a normal build).
-#ifdef LETHE_PHASE_TIMING
-#include <stdio.h>
-static __device__ long long g_ph_t[32];
-static __device__ const char* g_ph_name[32];
-#define LETHE_PHASE_INIT()                                                                         \
-  int ph_i_ = 0;                                                                                   \
-  const bool ph_on_ = (blockIdx.x == 200 && blockIdx.y == 0 && threadIdx.x == 0);                  \
-  LETHE_PHASE("start")
-#define LETHE_PHASE(name)                                                                          \
-  do {                                                                                             \
-    if (ph_on_ && ph_i_ < 32) {                                                                    \
-      g_ph_t[ph_i_] = clock64();                                                                   \
-      g_ph_name[ph_i_] = name;                                                                     \
-      ++ph_i_;                                                                                     \
-    }                                                                                              \
-  } while (0)
-#define LETHE_PHASE_DUMP()                                                                         \
-  do {                                                                                             \
-    if (ph_on_) {                                                                                  \
-      g_ph_t[ph_i_] = clock64();                                                                   \
-      printf("PHASE %s:", __func__);                                                               \
-      for (int i_ = 1; i_ <= ph_i_; ++i_)                                                          \
-        printf(" %s %lld", i_ < ph_i_ ? g_ph_name[i_] : "end", g_ph_t[i_] - g_ph_t[i_ - 1]);       \
-      printf(" | total %lld\n", g_ph_t[ph_i_] - g_ph_t[0]);                                        \
-    }                                                                                              \
-  } while (0)
-#else
-#define LETHE_PHASE_INIT()
-#define LETHE_PHASE(name)
-#define LETHE_PHASE_DUMP()
-#endif
 
 namespace lg {
 
@@ -127,6 +93,7 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
 struct Problem {
   int B, H, L, NT, V, gate, delta;
   int bh0, nbh;      // the (batch, head) pairs this call works on: [bh0, bh0 + nbh) of the B * H pairs
+  int qk16;          // non-zero: q, k, dq, dk hold fp16 instead of bf16
   float scale;
   const __nv_bfloat16 *q, *k, *v, *d_o;
   const float *g, *beta, *h0, *dhT;

@@ -91,7 +91,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     // (dh, written by the adjoint scan just before this kernel, is loaded after griddep_wait)
   }
-  LETHE_PHASE_INIT();
   __syncthreads();
   // the loads above fetch inputs and records older than the adjoint scan; once it is complete (at once,
   // except for the CTAs that started early) its dh image is fetched too
@@ -102,16 +101,15 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(DHt, p.scratch + p.lay.dh + static_cast<size_t>(z) * p.lay.sz_dh, V * 256, bar_dh);
   }
   mbar_wait_warp(bar_load, 0, ctl, 601);
-  LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
-    unpack8_bf16(tile_ld_chunk(X1, r, ch, 128), x);
+    unpack8_in(tile_ld_chunk(X1, r, ch, 128), x, p.qk16);
     tile_st_chunk(X1, r, ch, 128, pack8_f16(x));
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = x[e] * __expf(Gt[gidx(63, ch * 8 + e)] - Gt[gidx(r, ch * 8 + e)]);
     tile_st_chunk(X1, 64 + r, ch, 128, pack8_f16(y));
-    unpack8_bf16(tile_ld_chunk(QT, r, ch, 64), x);
+    unpack8_in(tile_ld_chunk(QT, r, ch, 64), x, p.qk16);
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
@@ -123,7 +121,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   sync_for_issue();
   mbar_wait_warp(bar_dh, 0, ctl, 604);
 
-  LETHE_PHASE("built");
   uint32_t ph = 0;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   if (warp == 0) {
@@ -148,7 +145,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     hh[tid] = acc * __expf(Gt[gidx(63, tid)]);
   }
   wait_products(bar_mma, ph, ctl, 602);
-  LETHE_PHASE("g1");
   if (tid >= 64 && tid < 128) {
     const int r = tid - 64;
     unsigned char* dv2_g = p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2;
@@ -182,7 +178,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   sync_for_issue();
-  LETHE_PHASE("epi1");
   if (warp == 0) {
     tc_fence_after();
     const uint32_t leader = elect_leader();
@@ -191,7 +186,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 603);
-  LETHE_PHASE("g2");
   __syncthreads();          // every thread is past the products: Ht / DHt may be overwritten (DDE)
   float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
   float* dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
@@ -254,7 +248,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     }
   }
   __syncthreads();
-  LETHE_PHASE("epi2");
   if (tid < 128) {  // last row of the chunk: exp(G_last) <dh, h> + sum_i dde[i, d]   (thread d, column d)
     float acc = hh[tid];
     for (int i = 0; i < 64; ++i) acc += DDE[exi(i, tid)];
@@ -273,7 +266,6 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   }
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -341,7 +333,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
-    unpack8_bf16(tile_ld_chunk(KB, r, ch, 128), x);
+    unpack8_in(tile_ld_chunk(KB, r, ch, 128), x, p.qk16);
     tile_st_chunk(KB, r, ch, 128, pack8_f16(x));
     float bb[8];
     if (full) {
@@ -560,9 +552,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       tma_load_4d(KX + a * 16384 + 8192, MODE == 0 ? &mq : &mk, bar_load, a * 64, h, c * kC, b);
     }
   }
-  LETHE_PHASE_INIT();
   __syncthreads();
-  LETHE_PHASE("gate");
   // the loads above fetch inputs and the gate record; C and the fp32 records come from the kernels just
   // before this one
   griddep_wait();
@@ -572,13 +562,12 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     bulk_g2s(CS, p.scratch + (MODE == 0 ? p.lay.da : p.lay.dm) + static_cast<size_t>(z) * 8192, 8192, bar_c);
   }
   mbar_wait_warp(bar_load, 0, ctl, 621);
-  LETHE_PHASE("loaded");
   // ---- decayed operand rows
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8, blk = r >> 4;
     float kx[8], xx[8], y[8], gr[8];
-    unpack8_bf16(tile_ld_chunk(KX, r, ch, 128), kx);
-    unpack8_bf16(tile_ld_chunk(KX, 64 + r, ch, 128), xx);
+    unpack8_in(tile_ld_chunk(KX, r, ch, 128), kx, p.qk16);
+    unpack8_in(tile_ld_chunk(KX, 64 + r, ch, 128), xx, p.qk16);
     const float be = betas[r];
     if (full) {
       float bb[8];
@@ -606,7 +595,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       tile_st_chunk(XE, off + (r - 16 * (J + 1)), ch, 128, pack8_f16(y));
     }
   }
-  LETHE_PHASE("rows");
   mbar_wait_warp(bar_c, 0, ctl, 623);
   // ---- masked copies of C and its diagonal blocks
   for (int idx = tid; idx < 64 * 8; idx += 256) {
@@ -625,7 +613,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
   }
   sync_for_issue();
-  LETHE_PHASE("built");
   uint32_t ph = 0;
   if (warp == 0) {
     tc_fence_after();
@@ -645,7 +632,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   wait_products(bar_mma, ph, ctl, 622);
   __syncthreads();          // products done for every thread: KR / XE become the exchange tiles
-  LETHE_PHASE("products");
   // ---- diagonal blocks, exact; thread d owns channel d
   {
     const int d = tid & 127;
@@ -679,7 +665,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     }
   }
   __syncthreads();
-  LETHE_PHASE("diag");
   // ---- phase A: row owners fold the tensor-core part (with its decay) into the exchange tiles.
   // Threads 0-127 own accumulator lanes 0-127 and take columns 0-63; threads 128-255 (warps 4-7 reach
   // the same lanes) take columns 64-127.
@@ -725,7 +710,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   __syncthreads();
   if (MODE == 1 && !full && tid < 64) p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid] + red[64 + tid];   // sum_d d(bk)_m k
-  LETHE_PHASE("phaseA");
   // ---- phase B: column owners (thread d; the two halves of the CTA split the rows) combine with the
   // fp32 records; every global access is coalesced and the records of eight rows are requested before
   // any of them is used or overwritten.
@@ -770,7 +754,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
         const size_t tok = (tok0 + static_cast<size_t>(i) * p.H) * kK + d;
         float dk, dG;
         if (MODE == 0) {
-          p.dq[tok] = __float2bfloat16_rn(part + o1);
+          store_out16(p.dq + tok, part + o1, p.qk16);
           dk = dkb + o2;
           dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
         } else {
@@ -784,7 +768,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
           }
           dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
         }
-        if (kFinalK) p.dk[tok] = __float2bfloat16_rn(dk);
+        if (kFinalK) store_out16(p.dk + tok, dk, p.qk16);
         else dkb_g[ridx(i, d)] = dk;
         if (FINAL_G) EX1[exi(i, d)] = dG;                // closed below by the reverse cumulative sum
         else dgb_g[ridx(i, d)] = dG;
@@ -802,25 +786,19 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       }
     }
   }
-  LETHE_PHASE("phaseB");
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
 // ---------------------------------------------------------------------------------------------
-template <typename Kern>
-static int set_smem_cw(Kern kern, int smem) {
-  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess ? kOk : kErrLaunch;
-}
-
 template <int V, bool DELTA>
 static int launch_sb1_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo,
                         cudaStream_t st) {
   const int smem = 32768 + 16384 + V * 256 + 16384 + V * 128 + V * 512 + 32768 + 128 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (set_smem_cw(bwd_cw_sb1_kernel<V, DELTA>, smem)) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(bwd_cw_sb1_kernel<V, DELTA>, smem)) return kErrLaunch;
   if (launch_dependent(bwd_cw_sb1_kernel<V, DELTA>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk, mdo) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
@@ -829,7 +807,8 @@ template <int V>
 static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
   const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 + 16384 + 32768 + 64 * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (set_smem_cw(bwd_cw_wy1_kernel<V>, smem)) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(bwd_cw_wy1_kernel<V>, smem)) return kErrLaunch;
   if (launch_dependent(bwd_cw_wy1_kernel<V>, dim3(p.nbh * p.NT), dim3(128), smem, st, p, mk, mv) != cudaSuccess)
     return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
@@ -837,7 +816,8 @@ static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
 template <int MODE, bool FINAL_G>
 static int launch_pair_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, cudaStream_t st) {
   const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1216 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
-  if (set_smem_cw(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
   if (launch_dependent(bwd_cw_pair_kernel<MODE, FINAL_G>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;

@@ -74,7 +74,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     }
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
-  LETHE_PHASE_INIT();
   if (tid < 128) {
     gate_tile_cw(p.g, tok0, p.H, tid, Gt);
     reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
@@ -82,7 +81,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   __syncthreads();
 
-  LETHE_PHASE("gate");
   if (tid == 0) {   // the gate tile becomes a record: later kernels load it instead of rebuilding it
     bulk_s2g(p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), Gt, 32768);
     bulk_commit();
@@ -93,8 +91,8 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8;
     const int blk = r >> 4;
     float kx[8], qx[8], y[8], gr[8], ga[8], gl[8];
-    unpack8_bf16(tile_ld_chunk(KQ, r, ch, 128), kx);
-    unpack8_bf16(tile_ld_chunk(KQ, 64 + r, ch, 128), qx);
+    unpack8_in(tile_ld_chunk(KQ, r, ch, 128), kx, p.qk16);
+    unpack8_in(tile_ld_chunk(KQ, 64 + r, ch, 128), qx, p.qk16);
     tile_st_chunk(KQ, r, ch, 128, pack8_f16(kx));
     tile_st_chunk(KQ, 64 + r, ch, 128, pack8_f16(qx));
 #pragma unroll
@@ -156,7 +154,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   sync_for_issue();
 
-  LETHE_PHASE("built");
   // ---- off-diagonal blocks on the tensor cores: columns [0,16) I=1, [16,48) I=2, [48,96) I=3
   uint32_t ph = 0;
   if (warp == 0) {
@@ -201,7 +198,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     Mdg[i * 16 + ss] = (DELTA && ss < ii) ? betas[i] * acc_m : 0.f;
   }
   __syncthreads();
-  LETHE_PHASE("diag");
   wait_products(bar_mma, ph, ctl, 502);
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   if (tid < 128) {
@@ -252,7 +248,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   tc_fence_before();
   __syncthreads();
 
-  LETHE_PHASE("epi1");
   // ---- T = (I + M)^-1 (fp32, CUDA cores)
   if (DELTA) {
     unit_lower_inverse64_blocked<kMsC>(Msm, Msm + 64 * kMsC, TA, tid);
@@ -265,7 +260,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   sync_for_issue();
 
-  LETHE_PHASE("inverse");
   if (DELTA) {
     if (warp == 0) {
       tc_fence_after();
@@ -292,7 +286,6 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     bulk_commit();
   }
 
-  LETHE_PHASE("wu");
   constexpr int N3 = DELTA ? 128 + V : V;
   if (warp == 0) {
     tc_fence_after();
@@ -340,11 +333,9 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       bulk_commit();
     }
   }
-  LETHE_PHASE("pr");
   if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -353,7 +344,8 @@ static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CU
                                const CUtensorMap& mv, cudaStream_t st) {
   const int smem = 32768 * 4 + 16384 + V * 128 + 16384 + 16384 + 2112 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_cw_kernel<V, DELTA>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(kern, smem)) return kErrLaunch;
   kern<<<p.nbh * p.NT, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -83,7 +83,7 @@ extern "C" int lethe_gdn_decode_step(const LetheGdnDecodeArgs* a, void* stream) 
   if (a->gate != LETHE_GATE_NONE && !a->g) return kErrNull;
   if (a->delta && !a->beta) return kErrNull;
   DeviceGuard guard(a->state);
-  if (!guard.ok) return kErrDriver;
+  if (!guard.ok) return kErrDevice;
   DecodeProblem p;
   p.BH = a->B * a->H;
   p.H = a->H;

@@ -1,5 +1,6 @@
 // Chunk-parallel forward kernels: `prepare` (UT / WY transform and the per-chunk state map) and
-// `output` (v_new and o from the chunk-entry states).  One CTA of 128 threads per chunk.
+// `output` (v_new and o from the chunk-entry states).  One CTA per chunk: 256 threads in `prepare`,
+// 128 in `output`.
 //
 // All tensor-core products are tcgen05 with M = 128, fp16 operands in SW128 shared-memory tiles and
 // fp32 accumulators in TMEM; two 64-row operands that share the other operand are stacked into one
@@ -69,7 +70,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tmem_alloc(&cs->tmem_slot, 256);
     tmem_relinquish();
   }
-  LETHE_PHASE_INIT();
   float gval = 0.f, bval = 1.f;
   if (tid < 64) {
     const size_t tok = (static_cast<size_t>(b) * p.L + c * kC + tid) * p.H + h;
@@ -98,13 +98,11 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   __syncthreads();
 
   // ---- operands: k, q -> fp16 in place; kd, beta gamma k, beta v
-  LETHE_PHASE("setup");
   mbar_wait_warp(bar_load, 0, ctl, 201);
-  LETHE_PHASE("loaded");
   for (int idx = tid; idx < 64 * 16; idx += 256) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
-    unpack8_bf16(tile_ld_chunk(KQ, r, ch, 128), x);
+    unpack8_in(tile_ld_chunk(KQ, r, ch, 128), x, p.qk16);
     tile_st_chunk(KQ, r, ch, 128, pack8_f16(x));
     const float de = decs[r];
 #pragma unroll
@@ -116,7 +114,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       for (int i = 0; i < 8; ++i) y[i] = x[i] * bg;
       tile_st_chunk(BGK, r, ch, 64, pack8_f16(y));
     }
-    unpack8_bf16(tile_ld_chunk(KQ, 64 + r, ch, 128), x);
+    unpack8_in(tile_ld_chunk(KQ, 64 + r, ch, 128), x, p.qk16);
     tile_st_chunk(KQ, 64 + r, ch, 128, pack8_f16(x));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
@@ -130,7 +128,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   fence_proxy_async();
   __syncthreads();
-  LETHE_PHASE("convert");
 
   // ---- product 1: [KK; QK] = [k; q] k^T
   if (warp == 0) {
@@ -141,7 +138,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   __syncwarp();
   mbar_wait_warp(bar_mma, 0, ctl, 202);
-  LETHE_PHASE("g1");
   tc_fence_after();
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   {
@@ -187,7 +183,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE("epi1");
 
   // ---- T = (I + M)^-1 (fp32, CUDA cores)
   if (DELTA) {
@@ -201,7 +196,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   fence_proxy_async();
   __syncthreads();
-  LETHE_PHASE("inverse");
 
   uint32_t ph = 1;
   if (DELTA) {
@@ -216,12 +210,11 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     }
     __syncwarp();
     mbar_wait_warp(bar_mma, ph, ctl, 203);
-    LETHE_PHASE("g2");
     ph ^= 1;
     tc_fence_after();
     if (tq < 64) {
       constexpr int kHalf2 = (128 + V) / 64;
-#pragma unroll 1
+#pragma unroll
       for (int jb = half * kHalf2; jb < (half + 1) * kHalf2; ++jb) {
         float d[32];
         tmem_ld32(tmem + lane_base + jb * 32, d);
@@ -233,7 +226,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     tc_fence_before();
     fence_proxy_async();
     __syncthreads();
-    LETHE_PHASE("epi2");
   } else if (tid == 0) {
     bulk_s2g(p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, TA, 16384);
     bulk_commit();
@@ -256,7 +248,6 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   __syncwarp();
   mbar_wait_warp(bar_mma, ph, ctl, 204);
-  LETHE_PHASE("g3");
   tc_fence_after();
   // P and R are staged as their record images in tiles nothing reads any more and leave by bulk
   // stores: P behind BGK (beta gamma k, beta v, kd are dead), R where k and q were once the stores
@@ -292,11 +283,9 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       bulk_commit();
     }
   }
-  LETHE_PHASE("epi3");
   if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
-  LETHE_PHASE_DUMP();
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -382,7 +371,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8];
-    unpack8_bf16(tile_ld_chunk(WQ, 64 + r, ch, 128), x);
+    unpack8_in(tile_ld_chunk(WQ, 64 + r, ch, 128), x, p.qk16);
     if (CW) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[gidx(r, ch * 8 + i)]);
@@ -470,7 +459,8 @@ static int launch_prepare_t(const Problem& p, const CUtensorMap& mq, const CUten
                             const CUtensorMap& mv, cudaStream_t st) {
   const int smem = 32768 + 16384 + V * 128 + 16384 + 16384 + 264 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_kernel<V, DELTA>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(kern, smem)) return kErrLaunch;
   kern<<<p.nbh * p.NT, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
@@ -478,7 +468,8 @@ template <int V, bool DELTA, bool CW>
 static int launch_output_t(const Problem& p, const CUtensorMap& mq, cudaStream_t st) {
   const int smem = 32768 + V * 256 + 16384 + V * 128 + 128 * 4 + (CW ? 32768 : 0) + 1024;
   auto kern = output_kernel<V, DELTA, CW>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
+  static SmemAttr attr;
+  if (attr.set(kern, smem)) return kErrLaunch;
   if (launch_dependent(kern, dim3(p.nbh * p.NT), dim3(128), smem, st, p, mq) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -8,8 +8,10 @@
 // One launch covers q and k.  A row of D channels is held by D / 8 neighbouring lanes, 8 channels
 // (one 16-byte piece of bf16) each; the row sum is a butterfly over those lanes.  HBM-bound: the
 // forward moves 2 D + 2 D bytes per row and tensor (4 D + 2 D for fp32 inputs), the backward
-// reads x and dy and writes dx.  The normalised rows leave as bf16, the type the GDN kernels read.
+// reads x and dy and writes dx.  The normalised rows leave as bf16 or as fp16 (the operand type of
+// the GDN kernels: one rounding instead of two), and their gradients come back in the same type.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "../../include/lethe_gdn.h"
 #include "host_util.h"
@@ -50,6 +52,41 @@ __device__ __forceinline__ void store8(void* base, size_t idx, const float* x) {
   }
 }
 
+// 16-bit rows: bf16 or fp16, chosen at run time
+__device__ __forceinline__ void load8_16(const void* base, size_t idx, float* x, int f16) {
+  const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + idx);
+  if (f16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h[j]);
+      x[2 * j] = f.x;
+      x[2 * j + 1] = f.y;
+    }
+  } else {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      x[2 * j] = f.x;
+      x[2 * j + 1] = f.y;
+    }
+  }
+}
+__device__ __forceinline__ void store8_16(void* base, size_t idx, const float* x, int f16) {
+  uint4 u;
+  if (f16) {
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(x[2 * j], x[2 * j + 1]);
+  } else {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+  }
+  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + idx) = u;
+}
+
 template <int LANES>
 __device__ __forceinline__ float row_sum(float s) {
 #pragma unroll
@@ -59,10 +96,11 @@ __device__ __forceinline__ float row_sum(float s) {
 
 struct L2Problem {
   const void* x[2];     // q, k
-  const void* dy[2];    // backward: gradients of the normalised rows (bf16)
-  void* out[2];         // forward: normalised rows (bf16); backward: dx in the type of x
+  const void* dy[2];    // backward: gradients of the normalised rows (bf16 or fp16)
+  void* out[2];         // forward: normalised rows (bf16 or fp16); backward: dx in the type of x
   long long rows;
   float eps;
+  int norm_f16;         // the normalised rows and their gradients are fp16
 };
 
 // grid.y selects the tensor; LANES = D / 8 lanes per row
@@ -85,10 +123,10 @@ l2norm_qk_kernel(const L2Problem p) {
   if (!BACKWARD) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] *= r;
-    if (live) store8<false>(p.out[t], idx, x);
+    if (live) store8_16(p.out[t], idx, x, p.norm_f16);
   } else {
     float dy[8];
-    load8<false>(p.dy[t], idx, dy);
+    load8_16(p.dy[t], idx, dy, p.norm_f16);
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) dot = fmaf(x[j], dy[j], dot);
@@ -119,19 +157,19 @@ inline bool aligned16(const void* a) { return (reinterpret_cast<uintptr_t>(a) & 
 }  // namespace lg
 
 extern "C" int lethe_gdn_l2norm_qk(const void* q, const void* k, void* qn, void* kn, int64_t rows, int32_t D,
-                                   int32_t in_f32, float eps, void* stream) {
+                                   int32_t flags, float eps, void* stream) {
   using namespace lg;
   if (!q || !k || !qn || !kn) return kErrNull;
   if (rows <= 0 || (D != 64 && D != 128)) return kErrDims;
   if (!aligned16(q) || !aligned16(k) || !aligned16(qn) || !aligned16(kn)) return kErrAlign;
   DeviceGuard guard(q);
-  if (!guard.ok) return kErrDriver;
-  L2Problem p{{q, k}, {nullptr, nullptr}, {qn, kn}, rows, eps};
-  return launch_l2norm<false>(p, D, in_f32 != 0, static_cast<cudaStream_t>(stream));
+  if (!guard.ok) return kErrDevice;
+  L2Problem p{{q, k}, {nullptr, nullptr}, {qn, kn}, rows, eps, (flags & LETHE_L2_NORM_F16) ? 1 : 0};
+  return launch_l2norm<false>(p, D, (flags & LETHE_L2_IN_F32) != 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int lethe_gdn_l2norm_qk_vjp(const void* q, const void* k, const void* dqn, const void* dkn, void* dq,
-                                       void* dk, int64_t rows, int32_t D, int32_t in_f32, float eps,
+                                       void* dk, int64_t rows, int32_t D, int32_t flags, float eps,
                                        void* stream) {
   using namespace lg;
   if (!q || !k || !dqn || !dkn || !dq || !dk) return kErrNull;
@@ -139,7 +177,7 @@ extern "C" int lethe_gdn_l2norm_qk_vjp(const void* q, const void* k, const void*
   if (!aligned16(q) || !aligned16(k) || !aligned16(dqn) || !aligned16(dkn) || !aligned16(dq) || !aligned16(dk))
     return kErrAlign;
   DeviceGuard guard(q);
-  if (!guard.ok) return kErrDriver;
-  L2Problem p{{q, k}, {dqn, dkn}, {dq, dk}, rows, eps};
-  return launch_l2norm<true>(p, D, in_f32 != 0, static_cast<cudaStream_t>(stream));
+  if (!guard.ok) return kErrDevice;
+  L2Problem p{{q, k}, {dqn, dkn}, {dq, dk}, rows, eps, (flags & LETHE_L2_NORM_F16) ? 1 : 0};
+  return launch_l2norm<true>(p, D, (flags & LETHE_L2_IN_F32) != 0, static_cast<cudaStream_t>(stream));
 }

@@ -13,7 +13,6 @@
 // gdn2_assemble.py:71-99 of the reference project, after substituting v_new / dv2.
 #include "gdn_common.cuh"
 #include "host_util.h"
-#include <stdio.h>
 
 namespace lg {
 
@@ -139,15 +138,8 @@ scan_kernel(const Problem p) {
     }
     float a_next = ADg[(static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid];
 
-#ifdef LETHE_PHASE_TIMING
-    long long ph[8] = {0,0,0,0,0,0,0,0}; long long tl = clock64(); const long long tstart = tl;
-#define ST(i) { long long tn = clock64(); ph[i] += tn - tl; tl = tn; }
-#else
-#define ST(i)
-#endif
     for (int it = 0; it < NT; ++it) {
       const size_t z = static_cast<size_t>(bh) * NT + chunk_of(it);
-      ST(0)
       // critical path: the state as a tensor-core operand
       {
         const int sw = (tid >> 2) & 1;     // 32-byte swizzle: the two 16-byte pieces of rows 4-7 of an atom swap
@@ -157,7 +149,6 @@ scan_kernel(const Problem p) {
       fence_proxy_async();
       tc_fence_before();
       step_arrive();
-      ST(1)
       // in the shadow of the product: this chunk's input and decay, the next chunk's loads, the record
       const float a = a_next;
       float rr[kVs];
@@ -165,7 +156,6 @@ scan_kernel(const Problem p) {
       unpack8_f16(rnext[1], rr + 8);
 #pragma unroll
       for (int j = 0; j < kVs; ++j) rr[j] = fmaf(a, x[j], rr[j]);
-      ST(2)
       if (it + 1 < NT) {
         const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
         const __half* r = Rg + zn * kK * V + rofs;
@@ -173,22 +163,18 @@ scan_kernel(const Problem p) {
         rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
         a_next = ADg[zn * kK + tid];
       }
-      ST(3)
       {
         unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
         *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
         *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
       }
-      ST(4)
       mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
-      ST(5)
       tc_fence_after();
       float acc[kMmaWarps * kVs];
       if (kMmaWarps == 1) tmem_ld16(tmem + lane_base, acc);
       if (kMmaWarps >= 2) tmem_ld32(tmem + lane_base, acc);
       if (kMmaWarps == 4) tmem_ld32(tmem + lane_base + 32, acc + 32);
       tmem_ld_wait();
-      ST(6)
 #pragma unroll
       for (int j = 0; j < kVs; ++j) {
         float s = acc[j];
@@ -196,11 +182,7 @@ scan_kernel(const Problem p) {
         if (kMmaWarps == 4) s += acc[2 * kVs + j] + acc[3 * kVs + j];
         x[j] = rr[j] - s;
       }
-      ST(7)
     }
-#ifdef LETHE_PHASE_TIMING
-    if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 3) printf("SCAN adj=%d total %lld | top %lld write %lld unpack %lld pref %lld rec %lld mmawait %lld ld %lld fma %lld\n", (int)ADJOINT, clock64()-tstart, ph[0],ph[1],ph[2],ph[3],ph[4],ph[5],ph[6],ph[7]);
-#endif
     if (!ADJOINT) {   // the final state as one more record
       unsigned char* rec = Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx;
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
@@ -292,12 +274,12 @@ int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
   const int smem = kStages * 32768 + 4096 + static_cast<int>(sizeof(CtaShared)) + 1024;
   dim3 grid(p.V / kVs, p.nbh);
   if (adjoint) {
-    if (cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return kErrLaunch;
+    static SmemAttr attr;
+    if (attr.set(scan_kernel<true>, smem)) return kErrLaunch;
     if (launch_dependent(scan_kernel<true>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
   } else {
-    if (cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return kErrLaunch;
+    static SmemAttr attr;
+    if (attr.set(scan_kernel<false>, smem)) return kErrLaunch;
     if (launch_dependent(scan_kernel<false>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
   }
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;

@@ -3,8 +3,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdio.h>
-#include <stdlib.h>
+
+#include <atomic>
+#include <mutex>
 
 namespace lg {
 
@@ -18,6 +19,8 @@ enum : int {
   kErrLaunch = 6,      // kernel launch failed
   kErrFlags = 7,       // unsupported flag combination
   kErrTooLarge = 8,    // problem larger than a fixed-capacity entry point accepts
+  kErrDevice = 9,      // the device that owns the tensors could not be made current, or a buffer lives elsewhere
+  kErrSymbol = 10,     // the address of the library's built-in workspace could not be looked up
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -25,18 +28,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
+// Looked up once per process; safe to call from several threads at once.
 inline EncodeTiledFn encode_tiled_fn() {
+  static std::once_flag once;
   static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  std::call_once(once, [] {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess) {
       fn = reinterpret_cast<EncodeTiledFn>(p);
     }
-  }
+  });
   return fn;
 }
 
@@ -59,13 +62,6 @@ inline int make_tmap_16bit(CUtensorMap* map, const void* ptr, int rank, const ui
                   const_cast<void*>(ptr), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS && getenv("LETHE_GDN_DEBUG")) {
-    fprintf(stderr, "lethe_gdn: cuTensorMapEncodeTiled failed (%d): ptr %p rank %d dims", static_cast<int>(r), ptr, rank);
-    for (int i = 0; i < rank; ++i) fprintf(stderr, " %llu", static_cast<unsigned long long>(dims[i]));
-    fprintf(stderr, " strides");
-    for (int i = 0; i + 1 < rank; ++i) fprintf(stderr, " %llu", static_cast<unsigned long long>(strides_bytes[i]));
-    fprintf(stderr, "\n");
-  }
   return r == CUDA_SUCCESS ? kOk : kErrDriver;
 }
 
@@ -90,6 +86,21 @@ struct DeviceGuard {
   }
   ~DeviceGuard() {
     if (ok && prev >= 0 && prev != dev) cudaSetDevice(prev);
+  }
+};
+
+// Opt-in to more than 48 KB of dynamic shared memory, done once per kernel and device instead of on
+// every launch.  One object per kernel instantiation (a function-local static of its launcher).
+struct SmemAttr {
+  std::atomic<uint64_t> done{0};     // bit d: the attribute is set on device ordinal d
+  template <typename Kern>
+  int set(Kern kern, int smem) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return kErrLaunch;
+    if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1u) return kOk;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrLaunch;
+    if (dev < 64) done.fetch_or(uint64_t(1) << dev, std::memory_order_release);
+    return kOk;
   }
 };
 

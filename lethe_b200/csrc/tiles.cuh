@@ -49,16 +49,20 @@ __device__ __forceinline__ void issue_product_led(uint32_t leader, uint32_t tmem
 // ---------------------------------------------------------------------------------------------
 // register <-> tile helpers (16-bit elements, 8 per 16-byte chunk)
 // ---------------------------------------------------------------------------------------------
+// Two floats to one fp16 pair (lo in the low half), round to nearest, SATURATING: a magnitude beyond
+// the fp16 range becomes +-65504 instead of infinity, so that an out-of-range activation or gradient
+// degrades a result instead of turning it (and, through 0 * inf, its neighbours) into NaN.  NaN stays NaN.
+__device__ __forceinline__ uint32_t f16x2_sat(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 __device__ __forceinline__ uint4 pack8_f16(const float* v) {
-  __half2 h0 = __floats2half2_rn(v[0], v[1]);
-  __half2 h1 = __floats2half2_rn(v[2], v[3]);
-  __half2 h2 = __floats2half2_rn(v[4], v[5]);
-  __half2 h3 = __floats2half2_rn(v[6], v[7]);
   uint4 u;
-  u.x = *reinterpret_cast<uint32_t*>(&h0);
-  u.y = *reinterpret_cast<uint32_t*>(&h1);
-  u.z = *reinterpret_cast<uint32_t*>(&h2);
-  u.w = *reinterpret_cast<uint32_t*>(&h3);
+  u.x = f16x2_sat(v[0], v[1]);
+  u.y = f16x2_sat(v[2], v[3]);
+  u.z = f16x2_sat(v[4], v[5]);
+  u.w = f16x2_sat(v[6], v[7]);
   return u;
 }
 __device__ __forceinline__ void unpack8_f16(const uint4& u, float* v) {
@@ -90,6 +94,18 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* v) {
   u.z = *reinterpret_cast<uint32_t*>(&h2);
   u.w = *reinterpret_cast<uint32_t*>(&h3);
   return u;
+}
+
+// q and k arrive, and dq and dk leave, as bf16 or - when the caller says so (LetheGdnArgs::qk_f16) - as
+// fp16, the type of the tensor-core operands (a caller that normalises q, k in fp32 then rounds once).
+__device__ __forceinline__ void unpack8_in(const uint4& u, float* v, int f16) {
+  if (f16) unpack8_f16(u, v);
+  else unpack8_bf16(u, v);
+}
+__device__ __forceinline__ uint4 pack8_out(const float* v, int f16) { return f16 ? pack8_f16(v) : pack8_bf16(v); }
+__device__ __forceinline__ void store_out16(__nv_bfloat16* dst, float x, int f16) {
+  if (f16) *reinterpret_cast<__half*>(dst) = __float2half_rn(x);
+  else *dst = __float2bfloat16_rn(x);
 }
 
 // chunk access on a tile given as a generic pointer to its first byte

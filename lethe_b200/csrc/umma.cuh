@@ -22,12 +22,13 @@ namespace lg {
 // ---------------------------------------------------------------------------------------------
 // status / abort
 // ---------------------------------------------------------------------------------------------
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second at 1.9 GHz
+
 struct CtaCtl {
   int* status;              // global status word (0 = ok)
   volatile int* abort_flag; // shared-memory flag, set when any wait of this CTA gave up
+  long long limit = kWaitLimitCycles;   // cycles a wait may spin before it gives up
 };
-
-constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second at 1.9 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -67,7 +68,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
     if (*ctl.abort_flag) return;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > ctl.limit) {
       atomicCAS(ctl.status, 0, code);
       *ctl.abort_flag = 1;
       return;

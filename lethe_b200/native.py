@@ -49,5 +49,3 @@ def _declare(L: ctypes.CDLL) -> None:
                                                           ctypes.c_float, c_void_p]
     L.lethe_gdn_strerror.restype = ctypes.c_char_p
     L.lethe_gdn_strerror.argtypes = [c_int]
-    L.lethe_probe_umma.restype = c_int
-    L.lethe_probe_umma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]

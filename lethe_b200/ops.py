@@ -13,9 +13,11 @@ CUDA library behind ``lethe_b200.native`` (there is no other path: a missing lib
 from __future__ import annotations
 
 import ctypes
+from typing import NamedTuple
 
 import torch
 from torch import Tensor
+from torch.autograd.function import once_differentiable
 
 from . import native
 
@@ -41,7 +43,7 @@ class _Args(ctypes.Structure):
         ("dbeta_write", ctypes.c_void_p),
         ("b_gate", ctypes.c_void_p), ("w_gate", ctypes.c_void_p),
         ("db_gate", ctypes.c_void_p), ("dw_gate", ctypes.c_void_p),
-        ("bh_begin", ctypes.c_uint32), ("bh_count", ctypes.c_uint32),
+        ("bh_begin", ctypes.c_uint32), ("bh_count", ctypes.c_uint32), ("qk_f16", ctypes.c_uint32),
     ]
 
 
@@ -77,6 +79,53 @@ def _prep16(t: Tensor) -> Tensor:
     return t.to(torch.bfloat16).contiguous()
 
 
+def _prep_qk(q: Tensor, k: Tensor) -> tuple[Tensor, Tensor]:
+    """q and k as the kernels read them: fp16 when both came as fp16 (the tensor-core operand type, kept
+    as it is), bf16 otherwise."""
+    if q.dtype == torch.float16 and k.dtype == torch.float16:
+        return q.contiguous(), k.contiguous()
+    return _prep16(q), _prep16(k)
+
+
+class _StatusWatch:
+    """Deferred, sync-free check of the device status words.  After a call the word is copied to a pinned
+    host slot on the call's stream; a later call looks at the slots whose copies have completed and
+    raises if a device-side wait of that earlier call gave up.  Nothing ever waits for the GPU here, so
+    an error surfaces one or two calls late; ``check_status`` is the immediate (synchronising) form."""
+
+    SLOTS = 64
+
+    def __init__(self):
+        self._host = None
+        self._events = [None] * self.SLOTS
+        self._next = 0
+
+    def poll(self) -> None:
+        for i, ev in enumerate(self._events):
+            if ev is not None and ev.query():
+                self._events[i] = None
+                code = int(self._host[i])
+                if code != 0:
+                    raise GdnError(f"lethe_gdn: a device-side wait of an earlier call timed out at site {code}; "
+                                   "the results of that call are invalid")
+
+    def watch(self, status: Tensor) -> None:
+        if self._host is None:
+            self._host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        i = self._next
+        self._next = (i + 1) % self.SLOTS
+        if self._events[i] is not None:      # ring full: this slot's copy is old enough to have landed
+            self._events[i].synchronize()
+            self.poll()
+        self._host[i:i + 1].copy_(status, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(status.device))
+        self._events[i] = ev
+
+
+_watch = _StatusWatch()
+
+
 def _prep32(t: Tensor | None) -> Tensor | None:
     return None if t is None else t.to(torch.float32).contiguous()
 
@@ -87,7 +136,7 @@ class GdnBuffers:
     benchmark) keep one of these and call ``forward_into`` / ``backward_into``."""
 
     def __init__(self, B, L, H, K, V, gate: int, delta: bool, device, backward: bool = True,
-                 saved: Tensor | None = None, status: Tensor | None = None):
+                 saved: Tensor | None = None, status: Tensor | None = None, qk_dtype=torch.bfloat16):
         L_ = native.lib()
         # delta: False / True (one beta per token-head), or 2 for the full op's per-channel gates b, w
         self.dims = _Dims(B, H, L, K, V, gate, int(delta))
@@ -105,8 +154,8 @@ class GdnBuffers:
         self.db = self.dw = None
         if backward:
             self.scratch = _workspace(L_.lethe_gdn_scratch_bytes(ctypes.byref(self.dims)), device)
-            self.dq = torch.empty(B, L, H, K, dtype=bf, device=device)
-            self.dk = torch.empty(B, L, H, K, dtype=bf, device=device)
+            self.dq = torch.empty(B, L, H, K, dtype=qk_dtype, device=device)     # the type of q, k
+            self.dk = torch.empty(B, L, H, K, dtype=qk_dtype, device=device)
             self.dv = torch.empty(B, L, H, V, dtype=bf, device=device)
             gshape = (B, L, H, K) if gate == GATE_CHANNEL else (B, L, H)
             self.dg = torch.empty(gshape, dtype=f32, device=device) if gate != GATE_NONE else None
@@ -125,7 +174,8 @@ def forward_into(buf: GdnBuffers, q, k, v, g, beta, h0, scale: float, kernel_mas
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
               h0=_ptr(h0), o=_ptr(buf.o), hT=_ptr(buf.hT), saved=_ptr(buf.saved),
               saved_bytes=buf.saved.numel(), status=_ptr(buf.status), kernel_mask=kernel_mask,
-              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), bh_begin=bh_range[0], bh_count=bh_range[1])
+              b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), bh_begin=bh_range[0], bh_count=bh_range[1],
+              qk_f16=int(q.dtype == torch.float16))
     _check(native.lib().lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
@@ -139,7 +189,9 @@ def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, 
               saved_bytes=buf.saved.numel(), scratch=_ptr(buf.scratch), scratch_bytes=buf.scratch.numel(),
               status=_ptr(buf.status), kernel_mask=kernel_mask, dbeta_write=_ptr(buf.dbeta_write),
               b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), db_gate=_ptr(buf.db), dw_gate=_ptr(buf.dw),
-              bh_begin=bh_range[0], bh_count=bh_range[1])
+              bh_begin=bh_range[0], bh_count=bh_range[1], qk_f16=int(q.dtype == torch.float16))
+    if buf.dq.dtype != q.dtype:
+        raise GdnError("lethe_gdn: dq / dk buffers must have the type of q / k (make GdnBuffers with qk_dtype=)")
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
@@ -214,8 +266,9 @@ def _gate_code(g: Tensor | None) -> int:
 
 
 def gdn_forward_raw(q, k, v, g, beta, h0, scale: float):
-    """One forward call of the library.  Inputs must be CUDA tensors: q, k, v bf16 contiguous
-    ``[B, L, H, D]``; g, beta, h0 fp32.  Returns ``(o, hT, saved, status)`` in fresh buffers."""
+    """One forward call of the library.  Inputs must be CUDA tensors: q, k (both bf16 or both fp16) and
+    v (bf16) contiguous ``[B, L, H, D]``; g, beta, h0 fp32.  Returns ``(o, hT, saved, status)`` in fresh
+    buffers."""
     B, L, H, K = q.shape
     buf = GdnBuffers(B, L, H, K, v.shape[-1], _gate_code(g), beta is not None, q.device, backward=False)
     forward_into(buf, q, k, v, g, beta, h0, scale)
@@ -226,9 +279,12 @@ def gdn_backward_raw(q, k, v, g, beta, h0, do, dhT, saved, status, scale: float)
     """One backward call of the library.  Returns ``(dq, dk, dv, dg, dbeta, dh0, scratch)``."""
     B, L, H, K = q.shape
     buf = GdnBuffers(B, L, H, K, v.shape[-1], _gate_code(g), beta is not None, q.device,
-                     saved=saved, status=status)
+                     saved=saved, status=status, qk_dtype=q.dtype)
     backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale)
     return buf.dq, buf.dk, buf.dv, buf.dg, buf.dbeta, buf.dh0, buf.scratch
+
+
+L2_IN_F32, L2_NORM_F16 = 1, 2
 
 
 def _l2_working(q: Tensor, k: Tensor) -> tuple[Tensor, Tensor, bool]:
@@ -238,31 +294,41 @@ def _l2_working(q: Tensor, k: Tensor) -> tuple[Tensor, Tensor, bool]:
     return q.to(dt).contiguous(), k.to(dt).contiguous(), f32
 
 
-def l2norm_qk_raw(q: Tensor, k: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+def l2norm_qk_raw(q: Tensor, k: Tensor, eps: float = 1e-6, norm_dtype=torch.float16) -> tuple[Tensor, Tensor]:
     """``x * rsqrt(sum x^2 + eps)`` over the last axis of q and of k in one launch (epsilon placed as in
-    the reference, ``gdn_backward.py:9-10``).  Returns bf16 tensors, the type the GDN kernels read."""
+    the reference, ``gdn_backward.py:9-10``).  The rows are formed in fp32 and rounded once: to fp16 by
+    default (the operand type of the GDN kernels, which then read them unchanged; the reference rounds
+    at the same point, ``gdn2_bwd_dhu_l3.py:477-479``), or to bf16 with ``norm_dtype=torch.bfloat16``."""
     if not q.is_cuda:
         raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
     if q.shape != k.shape:
         raise GdnError("lethe_gdn: q and k must have the same shape")
+    if norm_dtype not in (torch.float16, torch.bfloat16):
+        raise GdnError("lethe_gdn: normalised rows are fp16 or bf16")
     qc, kc, f32 = _l2_working(q, k)
-    qn, kn = torch.empty_like(qc, dtype=torch.bfloat16), torch.empty_like(kc, dtype=torch.bfloat16)
+    qn, kn = torch.empty_like(qc, dtype=norm_dtype), torch.empty_like(kc, dtype=norm_dtype)
     D = q.shape[-1]
+    flags = (L2_IN_F32 if f32 else 0) | (L2_NORM_F16 if norm_dtype == torch.float16 else 0)
     _check(native.lib().lethe_gdn_l2norm_qk(qc.data_ptr(), kc.data_ptr(), qn.data_ptr(), kn.data_ptr(),
-                                            qc.numel() // D, D, int(f32), eps,
+                                            qc.numel() // D, D, flags, eps,
                                             torch.cuda.current_stream(q.device).cuda_stream))
     return qn, kn
 
 
 def l2norm_qk_vjp_raw(q: Tensor, k: Tensor, dqn: Tensor, dkn: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
-    """Gradients with respect to q and k given those with respect to the normalised rows (bf16, as the
-    backward kernels write them).  Returned in the working type of q, k (bf16 or fp32)."""
+    """Gradients with respect to q and k given those with respect to the normalised rows (fp16 or bf16,
+    as the backward kernels wrote them).  Returned in the working type of q, k (bf16 or fp32)."""
     qc, kc, f32 = _l2_working(q, k)
-    dqn, dkn = _prep16(dqn), _prep16(dkn)
+    f16 = dqn.dtype == torch.float16 and dkn.dtype == torch.float16
+    if f16:
+        dqn, dkn = dqn.contiguous(), dkn.contiguous()
+    else:
+        dqn, dkn = _prep16(dqn), _prep16(dkn)
     dq, dk = torch.empty_like(qc), torch.empty_like(kc)
     D = q.shape[-1]
+    flags = (L2_IN_F32 if f32 else 0) | (L2_NORM_F16 if f16 else 0)
     _check(native.lib().lethe_gdn_l2norm_qk_vjp(qc.data_ptr(), kc.data_ptr(), dqn.data_ptr(), dkn.data_ptr(),
-                                                dq.data_ptr(), dk.data_ptr(), qc.numel() // D, D, int(f32), eps,
+                                                dq.data_ptr(), dk.data_ptr(), qc.numel() // D, D, flags, eps,
                                                 torch.cuda.current_stream(q.device).cuda_stream))
     return dq, dk
 
@@ -275,16 +341,18 @@ class _L2NormQK(torch.autograd.Function):
         return l2norm_qk_raw(q, k, eps)
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, dqn, dkn):
         q, k = ctx.saved_tensors
-        dqn = torch.zeros_like(q, dtype=torch.bfloat16) if dqn is None else dqn
-        dkn = torch.zeros_like(k, dtype=torch.bfloat16) if dkn is None else dkn
+        dqn = torch.zeros_like(q, dtype=torch.float16) if dqn is None else dqn
+        dkn = torch.zeros_like(k, dtype=torch.float16) if dkn is None else dkn
         dq, dk = l2norm_qk_vjp_raw(q, k, dqn, dkn, ctx.eps)
         return dq.to(q.dtype), dk.to(k.dtype), None
 
 
 def l2norm_qk(q: Tensor, k: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
-    """Differentiable L2 normalisation of q and k over the channel axis (one kernel each way)."""
+    """Differentiable L2 normalisation of q and k over the channel axis (one kernel each way).  Returns
+    fp16 rows, which ``gdn_chunk`` / ``gdn_chunk_full`` take as they are."""
     return _L2NormQK.apply(q, k, eps)
 
 
@@ -293,10 +361,11 @@ class _GdnChunk(torch.autograd.Function):
     def forward(ctx, q, k, v, g, beta, h0, scale):
         if not q.is_cuda:
             raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+        _watch.poll()
         K = q.shape[-1]
         ctx.in_dtypes = tuple(None if t is None else t.dtype for t in (q, k, v, g, beta, h0))
         ctx.pad_k = 0
-        q16, k16, v16 = _prep16(q), _prep16(k), _prep16(v)
+        (q16, k16), v16 = _prep_qk(q, k), _prep16(v)
         g32, b32, h32 = _prep32(g), _prep32(beta), _prep32(h0)
         if K == 64:
             # the kernels are built for 128 key channels: pad with zero channels (exact)
@@ -317,6 +386,7 @@ class _GdnChunk(torch.autograd.Function):
                 return None if t is None else torch.nn.functional.pad(t, (0, 0) * (t.dim() - 2) + (0, ctx.pad_l))
             q16, k16, v16, g32, b32 = (pad_tokens(t) for t in (q16, k16, v16, g32, b32))
         o, hT, saved, status = gdn_forward_raw(q16, k16, v16, g32, b32, h32, scale)
+        _watch.watch(status)
         ctx.save_for_backward(q16, k16, v16, g32, b32, h32, saved, status)
         ctx.scale = scale
         if ctx.pad_k:
@@ -326,8 +396,10 @@ class _GdnChunk(torch.autograd.Function):
         return o.to(v.dtype), hT
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, do, dhT):
         q16, k16, v16, g32, b32, h32, saved, status = ctx.saved_tensors
+        _watch.poll()
         do16 = _prep16(do)
         dhT32 = _prep32(dhT)
         if ctx.pad_l:
@@ -336,6 +408,7 @@ class _GdnChunk(torch.autograd.Function):
             dhT32 = torch.nn.functional.pad(dhT32, (0, 0, 0, ctx.pad_k))
         dq, dk, dv, dg, dbeta, dh0, _ = gdn_backward_raw(q16, k16, v16, g32, b32, h32, do16, dhT32,
                                                         saved, status, ctx.scale)
+        _watch.watch(status)
         if ctx.pad_k:
             K = q16.shape[-1] - ctx.pad_k
             dq, dk, dh0 = dq[..., :K], dk[..., :K], dh0[:, :, :K]
@@ -361,8 +434,11 @@ def gdn_chunk(q: Tensor, k: Tensor, v: Tensor, g: Tensor | None, beta: Tensor | 
 
     ``g``: per-token log decay, ``[B,L,H]`` (scalar gate), ``[B,L,H,K]`` (channel-wise) or None.
     ``beta``: ``[B,L,H]`` (erase and write gate) or None for the variants without the delta term
-    (linear attention, GLA, SSD).  Gradients flow to q, k, v, g, beta and h0.  ``L`` need not be a
-    multiple of the chunk length and d_k may be 64 or 128: both are met by exact zero padding.
+    (linear attention, GLA, SSD).  Gradients flow to q, k, v, g, beta and h0 (first order only: the
+    backward is not itself differentiable, asking for a second derivative raises).  ``L`` need not be a
+    multiple of the chunk length and d_k may be 64 or 128: both are met by exact zero padding.  q and k
+    are read as bf16, or as fp16 when both are given as fp16; with ``use_qk_l2norm`` they are normalised
+    in fp32 and rounded once to fp16.
     """
     if scale is None:
         scale = q.shape[-1] ** -0.5
@@ -418,26 +494,32 @@ class _GdnFull(torch.autograd.Function):
     def forward(ctx, q, k, v, g, b, w, h0, scale):
         if not q.is_cuda:
             raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+        _watch.poll()
         B, L, H, K = q.shape
         V = v.shape[-1]
         if K != 128 or L % 64:
             raise GdnError("lethe_gdn: the full-gate op needs d_k = 128 and L a multiple of 64")
         ctx.in_dtypes = tuple(None if t is None else t.dtype for t in (q, k, v, g, b, w, h0))
-        q16, k16, v16 = _prep16(q), _prep16(k), _prep16(v)
+        (q16, k16), v16 = _prep_qk(q, k), _prep16(v)
         g32, b32, w32, h32 = _prep32(g), _prep32(b), _prep32(w), _prep32(h0)
         buf = GdnBuffers(B, L, H, K, V, GATE_CHANNEL, 2, q.device, backward=False)
         forward_into(buf, q16, k16, v16, g32, None, h32, scale, b_gate=b32, w_gate=w32)
+        _watch.watch(buf.status)
         ctx.save_for_backward(q16, k16, v16, g32, b32, w32, h32, buf.saved, buf.status)
         ctx.scale = scale
         return buf.o.to(v.dtype), buf.hT
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, do, dhT):
         q16, k16, v16, g32, b32, w32, h32, saved, status = ctx.saved_tensors
+        _watch.poll()
         B, L, H, K = q16.shape
-        buf = GdnBuffers(B, L, H, K, v16.shape[-1], GATE_CHANNEL, 2, q16.device, saved=saved, status=status)
+        buf = GdnBuffers(B, L, H, K, v16.shape[-1], GATE_CHANNEL, 2, q16.device, saved=saved, status=status,
+                         qk_dtype=q16.dtype)
         backward_into(buf, q16, k16, v16, g32, None, h32, _prep16(do), _prep32(dhT), ctx.scale,
                       b_gate=b32, w_gate=w32)
+        _watch.watch(status)
         dts = ctx.in_dtypes
         return (buf.dq.to(dts[0]), buf.dk.to(dts[1]), buf.dv.to(dts[2]), buf.dg.to(dts[3]), buf.db.to(dts[4]),
                 buf.dw.to(dts[5]), None if dts[6] is None else buf.dh0.to(dts[6]), None)
@@ -447,7 +529,7 @@ def gdn_chunk_full(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Ten
                    scale: float | None = None, use_qk_l2norm: bool = False) -> tuple[Tensor, Tensor]:
     """The reference's full six-input recurrence with an initial state in and the final state out:
     ``g, b [B,L,H,K]`` (log decay and erase gate per key channel), ``w [B,L,H,V]`` (write gate per value
-    channel).  Returns ``(o, h_T)``; gradients flow to all seven inputs."""
+    channel).  Returns ``(o, h_T)``; gradients flow to all seven inputs (first order only)."""
     if scale is None:
         scale = q.shape[-1] ** -0.5
     if use_qk_l2norm:
@@ -458,8 +540,22 @@ def gdn_chunk_full(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Ten
 # ------------------------------------------------------------------------------------------------
 # The reference's own six-input surface
 # ------------------------------------------------------------------------------------------------
-def _channel_constant(t: Tensor) -> bool:
-    return bool(torch.equal(t, t[..., :1].expand_as(t)))
+def gate_regime(g: Tensor, b: Tensor, w: Tensor) -> tuple[bool, bool, bool]:
+    """``(scalar_gate, one_beta, no_delta)`` of a six-input call, decided as the reference decides
+    (``src/lethe/kernels/cute/gdn2_backward.py:53-60``): BITWISE equality along the channel axis, never
+    a tolerance - a gate that is merely close to constant is a channel-wise gate.  One device
+    reduction and one host read for all five tests.
+
+    scalar_gate: g is one value per token-head broadcast over the key channels;
+    one_beta:    b and w are the same one value per token-head broadcast over their channels;
+    no_delta:    b = 0 everywhere and w = 1 everywhere (no erase term, unit write gate)."""
+    with torch.no_grad():
+        flags = torch.stack([
+            (g == g[..., :1]).all(),
+            (b == b[..., :1]).all() & (w == w[..., :1]).all() & (b[..., 0] == w[..., 0]).all(),
+            (b == 0).all() & (w == 1).all(),
+        ]).tolist()
+    return bool(flags[0]), bool(flags[1]), bool(flags[2])
 
 
 class _Gdn2Op(torch.autograd.Function):
@@ -479,38 +575,36 @@ class _Gdn2Op(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, q, k, v, g, b, w, scale, use_qk_l2norm):
+    def forward(ctx, q, k, v, g, b, w, scale, use_qk_l2norm, scalar_gate, delta):
         if not q.is_cuda:
             raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+        _watch.poll()
         K, V = q.shape[-1], v.shape[-1]
         with torch.no_grad():
-            if _channel_constant(b) and _channel_constant(w) and bool(torch.equal(b[..., 0], w[..., 0])):
-                beta = b[..., 0].float().contiguous()
-            elif not bool(b.any()) and bool((w == 1).all()):
-                beta = None
-            else:
-                raise GdnError("lethe_gdn: per-channel erase / write gates are not supported: b and w must be "
-                               "one beta per token-head broadcast over the channels, or b = 0 and w = 1")
-            scalar_gate = _channel_constant(g)
+            beta = b[..., 0].float().contiguous() if delta else None
             g_in = (g[..., 0] if scalar_gate else g).float().contiguous()
-        ctx.meta = (q.dtype, k.dtype, v.dtype, g.dtype, b.dtype, w.dtype, K, V, scalar_gate, beta is not None,
-                    use_qk_l2norm)
-        q16, k16 = l2norm_qk_raw(q, k) if use_qk_l2norm else (_prep16(q), _prep16(k))
+        ctx.meta = (q.dtype, k.dtype, v.dtype, g.dtype, b.dtype, w.dtype, K, V, scalar_gate, delta, use_qk_l2norm)
+        q16, k16 = l2norm_qk_raw(q, k) if use_qk_l2norm else _prep_qk(q, k)
         v16 = _prep16(v)
         o, _hT, saved, status = gdn_forward_raw(q16, k16, v16, g_in, beta, None, scale)
+        _watch.watch(status)
         ctx.save_for_backward(q, k, q16, k16, v16, g_in, beta, saved, status)
         ctx.scale = scale
         return o.to(v.dtype)
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, do):
         q, k, q16, k16, v16, g_in, beta, saved, status = ctx.saved_tensors
+        _watch.poll()
         dq_t, dk_t, dv_t, dg_t, db_t, dw_t, K, V, scalar_gate, delta, l2 = ctx.meta
         B, L, H, _ = q16.shape
-        buf = GdnBuffers(B, L, H, K, V, _gate_code(g_in), delta, q16.device, saved=saved, status=status)
+        buf = GdnBuffers(B, L, H, K, V, _gate_code(g_in), delta, q16.device, saved=saved, status=status,
+                         qk_dtype=q16.dtype)
         if delta:
             buf.dbeta_write = torch.empty(B, L, H, dtype=torch.float32, device=q16.device)
         backward_into(buf, q16, k16, v16, g_in, beta, None, _prep16(do), None, ctx.scale)
+        _watch.watch(status)
         dq, dk = buf.dq, buf.dk
         if l2:   # VJP of x / sqrt(|x|^2 + eps) (the reference gets it by autograd, gdn2_assemble.py:300-312)
             dq, dk = l2norm_qk_vjp_raw(q, k, dq, dk)
@@ -522,22 +616,72 @@ class _Gdn2Op(torch.autograd.Function):
             grad_b = torch.zeros(B, L, H, K, device=q16.device)
             grad_w = torch.zeros(B, L, H, V, device=q16.device)
         return (dq.to(dq_t), dk.to(dk_t), buf.dv.to(dv_t), grad_g.to(dg_t).contiguous(),
-                grad_b.to(db_t).contiguous(), grad_w.to(dw_t).contiguous(), None, None)
+                grad_b.to(db_t).contiguous(), grad_w.to(dw_t).contiguous(), None, None, None, None)
 
 
 def gdn2_op(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Tensor, *, scale: float | None = None,
             use_qk_l2norm: bool = True) -> Tensor:
-    """Drop-in for the reference's ``gdn2_op`` (same argument list, same defaults, returns ``o``)."""
+    """Drop-in for the reference's ``gdn2_op`` (same argument list, same defaults, returns ``o``).
+    First-order gradients only: the backward pass is not differentiable (the reference falls back to its
+    eager path for that case, ``cute/gdn2_backward.py:92``; here a second derivative raises)."""
     if scale is None:
         scale = q.shape[-1] ** -0.5
     if q.shape[-1] != 128:
         raise GdnError("lethe_gdn: gdn2_op needs d_k = 128 (use gdn_chunk for d_k = 64)")
-    with torch.no_grad():
-        one_beta = _channel_constant(b) and _channel_constant(w) and bool(torch.equal(b[..., 0], w[..., 0]))
-        no_delta = not bool(b.any()) and bool((w == 1).all())
+    if not q.is_cuda:
+        raise GdnError("lethe_gdn: inputs must live on a CUDA device (there is no CPU path)")
+    scalar_gate, one_beta, no_delta = gate_regime(g, b, w)
     if one_beta or no_delta:
         # the regimes the scalar-beta kernels cover (cheaper: one gate value per token-head)
-        return _Gdn2Op.apply(q, k, v, g, b, w, float(scale), bool(use_qk_l2norm))
+        return _Gdn2Op.apply(q, k, v, g, b, w, float(scale), bool(use_qk_l2norm), scalar_gate, bool(one_beta))
     # independent per-channel erase / write gates: the full recurrence
     o, _ = gdn_chunk_full(q, k, v, g, b, w, None, scale=float(scale), use_qk_l2norm=bool(use_qk_l2norm))
     return o
+
+
+class Gdn2Grads(NamedTuple):
+    """Field for field the reference's result type (``src/lethe/kernels/references/gdn_backward.py:58-67``)."""
+    grad_q: Tensor
+    grad_k: Tensor
+    grad_v: Tensor
+    grad_g: Tensor
+    grad_b: Tensor
+    grad_w: Tensor
+    grad_initial_state: Tensor | None
+
+
+def gdn2_backward(q: Tensor, k: Tensor, v: Tensor, g: Tensor, b: Tensor, w: Tensor, do: Tensor, *,
+                  scale: float | None = None, use_qk_l2norm: bool = True, fwd_stash=None,
+                  rescale_do: bool = True) -> Gdn2Grads:
+    """Drop-in for the reference's backward entry point ``gdn2_backward``
+    (``src/lethe/kernels/ops/gdn_backward.py:16-57``: same positional arguments, same keywords, same
+    result type), which is what its autograd function calls (``ops/gdn_layer.py:69-96``) and what its
+    verifier harness takes as the candidate (``verifier/op_harness.py:714-733``).  The six gradients
+    come back in the dtypes of the inputs they belong to.
+
+    The reference function gets the inputs only, so the forward is recomputed here (the reference does
+    the same, ``cute/gdn2_assemble.py:261-263``); ``fwd_stash`` is accepted and ignored.
+
+    ``rescale_do``: the backward is linear in ``do``, and ``do`` enters the tensor cores as fp16.  With
+    this flag (default) ``do`` is first divided by a power of two near its largest magnitude and the
+    gradients are multiplied back, so that upstream gradients far outside the fp16 range (1e6, 1e-6)
+    neither saturate nor fall into the subnormals.  Exact (a power of two), all on the device, no
+    host synchronisation."""
+    if do.requires_grad:
+        raise GdnError("lethe_gdn: the backward is not differentiable (do.requires_grad): there is no eager "
+                       "fallback to route a second derivative to (the reference declines its native path in "
+                       "this case, cute/gdn2_backward.py:92)")
+    do = do.detach()
+    mult = None
+    if rescale_do:
+        amax = do.abs().amax().float()
+        amax = torch.where(torch.isfinite(amax) & (amax > 0), amax, torch.ones_like(amax))
+        mult = torch.exp2(torch.round(torch.log2(amax)))          # power of two: scaling is exact
+        do = (do.float() / mult).to(do.dtype if do.dtype != torch.float16 else torch.float32)
+    leaves = [t.detach().requires_grad_(True) for t in (q, k, v, g, b, w)]
+    with torch.enable_grad():
+        o = gdn2_op(*leaves, scale=scale, use_qk_l2norm=use_qk_l2norm)
+    grads = torch.autograd.grad(o, leaves, do.to(o.dtype))
+    if mult is not None:
+        grads = tuple((t.float() * mult).to(t.dtype) for t in grads)
+    return Gdn2Grads(*grads, None)

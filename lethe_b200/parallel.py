@@ -42,40 +42,74 @@ def shard_batch_heads(B: int, H: int, rank: int, world: int) -> tuple[slice, sli
     raise ValueError(f"neither B={B} nor H={H} divides by the world size {world}")
 
 
+class HandoffTimeout(ops.GdnError):
+    """A neighbouring rank did not deliver its boundary state in time."""
+
+
+def _peer(group, r: int) -> int:
+    return dist.get_global_rank(group, r) if group is not None else r
+
+
+def _wait_state(work, what: str, src: int, timeout_s: float | None) -> None:
+    """Completes a posted receive.  On the CPU (gloo) the wait is bounded on the host: a neighbour that
+    died, never joined the step or never sent surfaces as ``HandoffTimeout`` after ``timeout_s`` instead of
+    a hang.  On NCCL the wait only orders the current stream behind the receive (the host does not
+    block); there the process group's own timeout ends a receive whose sender is gone."""
+    try:
+        if timeout_s is not None and dist.get_backend() == "gloo":
+            import datetime
+            work.wait(timeout=datetime.timedelta(seconds=timeout_s))
+        else:
+            work.wait()
+    except RuntimeError as e:       # gloo reports an expired wait as RuntimeError / DistBackendError
+        raise HandoffTimeout(f"lethe_gdn: no {what} from rank {src} within {timeout_s} s: {e}") from e
+
+
 def sp_forward(prepare: Callable[[], None], scan: Callable[[Tensor | None], Tensor],
-               output: Callable[[], None], h0: Tensor | None, state_like: Tensor, group=None) -> Tensor:
+               output: Callable[[], None], h0: Tensor | None, state_like: Tensor, group=None,
+               timeout_s: float | None = None) -> Tensor:
     """Sequence-parallel forward.  `scan(h_in)` runs this rank's state scan from `h_in` (None = zero)
     and returns the state leaving the rank.  Returns that state (the global final state on the last
-    rank)."""
+    rank).  The receive of the incoming state is posted before this rank's chunk-parallel work is
+    enqueued, so the transfer does not queue up behind it; the outgoing state is sent as soon as the
+    scan has produced it, before the output kernels."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    prepare()
-    if rank == 0:
-        h_in = h0
-    else:
+    work, h_in = None, h0
+    if rank > 0:
         h_in = torch.empty_like(state_like)
-        dist.recv(h_in, src=dist.get_global_rank(group, rank - 1) if group is not None else rank - 1, group=group)
+        work = dist.irecv(h_in, src=_peer(group, rank - 1), group=group)
+    prepare()
+    if work is not None:
+        _wait_state(work, "chunk-boundary state", rank - 1, timeout_s)
     h_out = scan(h_in)
+    send = None
     if rank + 1 < world:
-        dist.send(h_out, dst=dist.get_global_rank(group, rank + 1) if group is not None else rank + 1, group=group)
+        send = dist.isend(h_out, dst=_peer(group, rank + 1), group=group)
     output()
+    if send is not None:
+        send.wait()
     return h_out
 
 
 def sp_backward(pre: Callable[[], None], scan: Callable[[Tensor | None], Tensor], main: Callable[[], None],
-                dhT: Tensor | None, state_like: Tensor, group=None) -> Tensor:
+                dhT: Tensor | None, state_like: Tensor, group=None, timeout_s: float | None = None) -> Tensor:
     """Sequence-parallel backward: the adjoint state flows from the last rank to the first.
     `scan(dh_in)` returns the adjoint of the state entering this rank (dh0 on rank 0)."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    pre()
-    if rank == world - 1:
-        dh_in = dhT
-    else:
+    work, dh_in = None, dhT
+    if rank < world - 1:
         dh_in = torch.empty_like(state_like)
-        dist.recv(dh_in, src=dist.get_global_rank(group, rank + 1) if group is not None else rank + 1, group=group)
+        work = dist.irecv(dh_in, src=_peer(group, rank + 1), group=group)
+    pre()
+    if work is not None:
+        _wait_state(work, "adjoint state", rank + 1, timeout_s)
     dh_out = scan(dh_in)
+    send = None
     if rank > 0:
-        dist.send(dh_out, dst=dist.get_global_rank(group, rank - 1) if group is not None else rank - 1, group=group)
+        send = dist.isend(dh_out, dst=_peer(group, rank - 1), group=group)
     main()
+    if send is not None:
+        send.wait()
     return dh_out
 
 

@@ -1,7 +1,15 @@
 // Self-test of the tcgen05 / TMA toolkit: one CTA computes D[128 x N] = (+/-) A * B (optionally
 // twice, accumulating) with every combination of operand orientation and fill method the GDN
 // kernels rely on.  The Python test compares D with a plain matrix product.
+//
+// A second kernel, `starved_wait_kernel`, exercises the bounded wait: it arms an mbarrier for bytes
+// that nobody sends and waits on it with a short limit.  The wait has to give up, leave its site code
+// in the status word, let the CTA's later waits fall through, free the tensor memory and return.
+// Nothing faults and nothing hangs: the kernel ends by itself after `limit_cycles`.
+#include <string.h>
+
 #include "host_util.h"
+#include "lethe_probe.h"
 #include "tiles.cuh"
 
 namespace lg {
@@ -99,9 +107,55 @@ probe_kernel(const ProbeParams p, const __grid_constant__ CUtensorMap mapA,
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
+// One CTA: TMEM allocated, a barrier armed for 64 bytes that never arrive, every thread waits.
+__global__ void __launch_bounds__(128, 1)
+starved_wait_kernel(int* status, long long limit_cycles, int* trace) {
+  __shared__ uint64_t bar_a, bar_b;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  CtaCtl ctl{status, &abort_flag, limit_cycles};
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&bar_a, 1);
+    mbar_init(&bar_b, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  if (tid == 0) mbar_expect_tx(&bar_a, 64u);          // armed, and no copy is ever issued
+  const long long t0 = clock64();
+  mbar_wait_warp(&bar_a, 0, ctl, 101);                // runs out after limit_cycles
+  const long long t1 = clock64();
+  mbar_wait_warp(&bar_b, 0, ctl, 102);                // must return at once: the abort flag is up
+  const long long t2 = clock64();
+  if (tid == 0) {
+    trace[0] = abort_flag;
+    trace[1] = static_cast<int>((t1 - t0) >> 10);     // kilo-cycles spent in the first wait
+    trace[2] = static_cast<int>((t2 - t1) >> 10);     // ... in the second
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 64);
+}
+
 }  // namespace lg
 
-// Debug entry point used by the test-suite only; not part of the GDN interface.
+extern "C" int lethe_probe_starved_wait(int* status, long long limit_cycles, int* trace, void* stream) {
+  using namespace lg;
+  if (!status || !trace) return kErrNull;
+  if (limit_cycles < 1000 || limit_cycles > 200000000LL) return kErrDims;    // at most a tenth of a second
+  starved_wait_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_cycles, trace);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// Test entry point; not part of the GDN interface.
 extern "C" int lethe_probe_umma(const void* A, const void* B, float* D, int* status, int a_mn, int b_mn,
                                 int N, int kc, int fill, int a_neg, int twice, void* stream) {
   using namespace lg;
@@ -128,12 +182,8 @@ extern "C" int lethe_probe_umma(const void* A, const void* B, float* D, int* sta
     if (e) return e;
   }
   const int smem = 32768 + 65536 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return kErrLaunch;
-    attr_set = true;
-  }
+  static SmemAttr attr;
+  if (attr.set(probe_kernel, smem)) return kErrLaunch;
   probe_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p, mapA, mapB);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -24,9 +24,25 @@ def test_exports_every_declared_symbol(lib):
     names = set(re.findall(r"\b(lethe_[a-z0-9_]+)\s*\(", hdr))
     assert {"lethe_gdn_forward", "lethe_gdn_backward", "lethe_gdn_saved_bytes", "lethe_gdn_scratch_bytes",
             "lethe_gdn_strerror", "lethe_gdn_forward_static", "lethe_gdn_decode_step", "lethe_gdn_l2norm_qk",
-            "lethe_gdn_l2norm_qk_vjp", "lethe_probe_umma"} <= names
+            "lethe_gdn_l2norm_qk_vjp", "lethe_gdn_forward_static_capacity"} <= names
+    assert not any("probe" in n for n in names)      # test hooks are not part of the public interface
     for n in names:
         assert hasattr(lib, n), n
+    assert not hasattr(lib, "lethe_probe_umma")
+
+
+def test_probe_library_exports_its_header():
+    """The test-only self-test library is separate from the product library and exports what its own
+    header declares."""
+    plib = ctypes.CDLL(_build.build_probe())
+    hdr = open(os.path.join(ROOT, "tests", "native", "lethe_probe.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    names = set(re.findall(r"\b(lethe_[a-z0-9_]+)\s*\(", hdr))
+    assert names == {"lethe_probe_umma", "lethe_probe_starved_wait"}
+    for n in names:
+        assert hasattr(plib, n), n
+    # argument checks come before any launch
+    assert plib.lethe_probe_starved_wait(None, ctypes.c_longlong(100000), None, None) != 0
 
 
 def test_decode_step_argument_errors(lib):
@@ -81,6 +97,21 @@ def test_argument_errors_come_before_any_launch(lib):
     assert rc != 0 and b"workspace" in lib.lethe_gdn_strerror(rc)
     assert lib.lethe_gdn_strerror(0) == b"ok"
     assert b"timed out" in lib.lethe_gdn_strerror(412)
+    # distinct texts for the three host-side failure classes that used to share one
+    texts = {lib.lethe_gdn_strerror(c) for c in (5, 9, 10)}
+    assert len(texts) == 3 and all(b"unknown" not in t for t in texts)
+
+
+def test_static_forward_rejects_host_pointers(lib):
+    """The entry point without a caller workspace finds its GPU from q; a q that is not device memory is
+    refused before anything is looked up or launched."""
+    import numpy as np
+    d = ops._Dims(1, 1, 64, 128, 64, 1, 1)
+    host = np.zeros(64 * 128, dtype=np.uint16)
+    a = ops._Args(dims=d, scale=1.0, q=host.ctypes.data, k=host.ctypes.data, v=host.ctypes.data,
+                  g=host.ctypes.data, beta=host.ctypes.data, o=host.ctypes.data, status=host.ctypes.data)
+    rc = lib.lethe_gdn_forward_static(ctypes.byref(a), None)
+    assert rc != 0 and b"device" in lib.lethe_gdn_strerror(rc)
 
 
 def test_op_refuses_cpu_tensors():

@@ -46,8 +46,7 @@ def test_gdn2_op_six_inputs(gate):
             "dg": scale_rel(grads[3].cpu().sum(-1) if gate == "scalar" else grads[3].cpu(), gr.dg),
             "dbeta": scale_rel(grads[4].cpu().sum(-1) + grads[5].cpu().sum(-1), gr.dbeta)}
     report(f"gdn2_op gate={gate}", errs)
-    # q, k are rounded to bf16 after the normalisation: allow for that extra rounding
-    assert max(errs.values()) <= 8e-3, errs
+    assert max(errs.values()) <= 5e-3, errs
 
 
 def _full_inputs(B, L, H, K, V, seed, with_h0=True):
@@ -128,8 +127,7 @@ def test_gdn2_op_takes_general_gates():
             "dg": scale_rel(grads[3].double().cpu(), gr["g"]), "db": scale_rel(grads[4].double().cpu(), gr["b"]),
             "dw": scale_rel(grads[5].double().cpu(), gr["w"])}
     report("gdn2_op general gates", errs)
-    # q, k are rounded to bf16 after the normalisation: allow for that extra rounding
-    assert max(errs.values()) <= 8e-3, errs
+    assert max(errs.values()) <= 5e-3, errs
 
 
 def test_family_wrappers():
@@ -159,41 +157,32 @@ def test_family_wrappers():
         assert max(errs.values()) <= 5e-3, (name, errs)
 
 
-def test_tiny_train_loop():
-    """Free q, k, v and gate logits are trained through the op to reproduce a teacher's output:
-    300 Adam steps at lr 0.01 on B=4, L=256, H=2, d_k=128, d_v=64 fp32 parameters (the shape of the
-    reference's tiny-train evidence, results/gdn2_tiny_train_native_sbe.json): no NaN and the
-    normalised loss falls by more than 20x."""
-    B, L, H, K, V = 4, 256, 2, 128, 64
-    dev = "cuda"
+@pytest.mark.parametrize("arm", ["gdn", "kda", "gla", "ssd"])
+def test_tiny_train_loop(arm):
+    """The reference's training-loop evidence, arm by arm (``results/gdn2_tiny_train_native_sbe.json`` and
+    ``gdn2_tiny_train_{kda,gla,ssd}.json`` of the reference project): a small language-model block around
+    the six-input op (``lethe_b200.tiny.TinyGdnLM``), fp32 parameters, B=4, L=256, H=2, d_k=128, d_v=64,
+    delayed-copy task, 300 Adam steps at lr 0.01.  Bar, as there: no NaN anywhere, the loss starts near
+    ln(vocab) = 3.69 and ends below 1e-3.  Every step goes through the CUDA forward and backward."""
+    from lethe_b200.tiny import TinyGdnLM, delayed_copy_batch
 
-    def params(seed):
-        gen = torch.Generator().manual_seed(seed)
-        return [torch.randn(B, L, H, K, generator=gen), torch.randn(B, L, H, K, generator=gen),
-                torch.randn(B, L, H, V, generator=gen), torch.randn(B, L, H, generator=gen),
-                torch.randn(B, L, H, generator=gen)]
-
-    def run(ps):
-        q, k, v, gl, bl = ps
-        g = -0.2 * torch.nn.functional.softplus(gl)
-        o, _ = gdn_chunk(q, k, v, g, torch.sigmoid(bl), None, use_qk_l2norm=True)
-        return o.float()
-
-    with torch.no_grad():
-        target = run([t.to(dev) for t in params(100)])
-    student = [t.to(dev).requires_grad_(True) for t in params(200)]
-    opt = torch.optim.Adam(student, lr=0.01)
-    var = float(target.var())
+    torch.manual_seed(0)
+    model = TinyGdnLM(gdn2_op, arm=arm).cuda()
+    opt = torch.optim.Adam(model.parameters(), lr=0.01)
+    x, y = delayed_copy_batch(4, 256, model.vocab, delay=1, seed=0)
+    x, y = x.cuda(), y.cuda()
     losses = []
     for _ in range(300):
         opt.zero_grad()
-        loss = torch.nn.functional.mse_loss(run(student), target) / var
+        loss = torch.nn.functional.cross_entropy(model(x).reshape(-1, model.vocab), y.reshape(-1))
         loss.backward()
         opt.step()
         losses.append(float(loss.detach()))
-    assert all(l == l for l in losses), "NaN in the loss"
-    report("tiny-train", {"first": losses[0], "last": losses[-1]})
-    assert losses[-1] < losses[0] / 20, (losses[0], losses[-1])
+    assert all(l == l and l != float("inf") for l in losses), "NaN / inf in the loss"
+    assert all(torch.isfinite(p).all() for p in model.parameters())
+    report(f"tiny-train {arm}", {"first": losses[0], "step100": losses[100], "last": losses[-1]})
+    assert 3.0 < losses[0] < 4.5, losses[0]
+    assert losses[-1] < 1e-3, (losses[0], losses[-1])
 
 
 def test_kernel_plugins_k1_k2():

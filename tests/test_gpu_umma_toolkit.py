@@ -1,12 +1,28 @@
 """GPU self-test of the tcgen05 / TMA toolkit: D = A @ B on one CTA for every operand orientation
 and tile-fill method the GDN kernels use, against a plain fp32 product."""
 
+import ctypes
+
 import pytest
 import torch
 
-from lethe_b200 import native
+from lethe_b200 import _build
 
 pytestmark = pytest.mark.gpu
+_PROBE = None
+
+
+def probe_lib():
+    """The test-only library built from tests/native/probe.cu (declared in tests/native/lethe_probe.h)."""
+    global _PROBE
+    if _PROBE is None:
+        _PROBE = ctypes.CDLL(_build.build_probe())
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        _PROBE.lethe_probe_umma.restype = ci
+        _PROBE.lethe_probe_umma.argtypes = [vp] * 4 + [ci] * 7 + [vp]
+        _PROBE.lethe_probe_starved_wait.restype = ci
+        _PROBE.lethe_probe_starved_wait.argtypes = [vp, ctypes.c_longlong, vp, vp]
+    return _PROBE
 
 
 def sw128_image(x: torch.Tensor) -> torch.Tensor:
@@ -40,7 +56,7 @@ def run_probe(a_mn, b_mn, N, kc, fill, a_neg=0, twice=0, seed=0):
         A_dev, B_dev = A_store.cuda(), B_store.cuda()
     D = torch.full((128, N), float("nan"), device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    rc = native.lib().lethe_probe_umma(A_dev.data_ptr(), B_dev.data_ptr(), D.data_ptr(),
+    rc = probe_lib().lethe_probe_umma(A_dev.data_ptr(), B_dev.data_ptr(), D.data_ptr(),
                                        status.data_ptr(), a_mn, b_mn, N, kc, fill, a_neg, twice,
                                        torch.cuda.current_stream().cuda_stream)
     assert rc == 0, rc
@@ -73,3 +89,29 @@ CASES = [
 def test_probe(case):
     err, scale = run_probe(*case)
     assert err < 2e-3 * max(scale, 1.0), (case, err, scale)
+
+
+def test_bounded_wait_runs_out_and_the_gpu_stays_usable():
+    """Failure detection without a fault: a CTA waits, with a limit of 1e5 cycles, on a barrier that
+    nothing completes.  The wait must give up and leave its site code (101) in the status word, the
+    CTA's next wait must fall through at once, the kernel must return by itself with its tensor memory
+    freed - and an ordinary probe launched right after on the same stream must still pass."""
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    trace = torch.full((4,), -1, dtype=torch.int32, device="cuda")
+    limit = 100_000
+    rc = probe_lib().lethe_probe_starved_wait(status.data_ptr(), limit, trace.data_ptr(),
+                                              torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 101
+    abort_flag, kcyc_first, kcyc_second = trace[:3].tolist()
+    assert abort_flag == 1
+    assert limit // 1024 <= kcyc_first <= 50 * limit // 1024          # gave up after about the limit
+    assert kcyc_second <= 8                                            # the later wait did not spin
+    from lethe_b200 import ops
+    with pytest.raises(ops.GdnError, match="101"):
+        ops.check_status(status)
+    # the context is intact and the tensor memory was given back: a 256-column product still runs
+    for _ in range(3):
+        err, scale = run_probe(0, 0, 256, 128, 1)
+        assert err < 2e-3 * max(scale, 1.0)

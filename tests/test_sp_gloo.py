@@ -74,6 +74,51 @@ def test_sequence_parallel_protocol_two_ranks(gate):
     mp.spawn(_worker, args=(2, _free_port(), gate), nprocs=2, join=True)
 
 
+def _silent_worker(rank, world, port, q):
+    """Rank 0 joins the group and then never sends its boundary state (it "hangs" before its scan);
+    rank 1 must get a HandoffTimeout from sp_forward, not wait for ever."""
+    import datetime
+    import time
+
+    from lethe_b200.parallel import HandoffTimeout
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        like = torch.zeros(1, 2, 16, 8, dtype=torch.float64)
+        if rank == 0:
+            time.sleep(6.0)                      # alive, but silent for longer than its neighbour waits
+            q.put(("rank0", "stayed silent"))
+        else:
+            t0 = time.time()
+            try:
+                sp_forward(lambda: None, lambda h: h, lambda: None, None, like, timeout_s=1.5)
+                q.put(("rank1", "returned"))
+            except HandoffTimeout as e:
+                q.put(("rank1", f"timeout after {time.time() - t0:.1f}s: {str(e)[:60]}"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:     # noqa: BLE001  (the group may already be broken by the expired wait)
+            pass
+
+
+def test_silent_neighbour_surfaces_as_timeout_not_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_silent_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=60) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert got["rank0"] == "stayed silent"
+    assert got["rank1"].startswith("timeout after"), got
+    waited = float(got["rank1"].split()[2].rstrip("s:"))
+    assert 1.0 <= waited <= 5.5, got            # gave up near its own limit, before the neighbour woke up
+
+
 def test_shard_batch_heads():
     seen = set()
     for r in range(8):

@@ -17,26 +17,27 @@ from lethe_b200.synth import make_inputs
 pytestmark = pytest.mark.gpu
 
 
-def _forward_both(B, L, H, V, seed):
+def _forward_both(B, L, H, V, seed, device="cuda"):
+    dev = torch.device(device)
     inp = make_inputs(B, L, H, 128, V, gate="scalar", delta=True, seed=seed)
-    d = {k: (None if t is None else t.cuda()) for k, t in inp.items()}
+    d = {k: (None if t is None else t.to(dev)) for k, t in inp.items()}
     scale = 128 ** -0.5
     o_ref, hT_ref, _saved, status_ref = ops.gdn_forward_raw(d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"],
                                                             scale)
     # outputs for the static entry point are ordinary caller tensors, allocated before the call
     o = torch.full_like(o_ref, float("nan"))
     hT = torch.full_like(hT_ref, float("nan"))
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize(dev)
+    before = torch.cuda.memory_allocated(dev)
     dims = ops._Dims(B, H, L, 128, V, ops.GATE_SCALAR, 1)
     a = ops._Args(dims=dims, scale=scale, q=d["q"].data_ptr(), k=d["k"].data_ptr(), v=d["v"].data_ptr(),
                   g=d["g"].data_ptr(), beta=d["beta"].data_ptr(), h0=d["h0"].data_ptr(), o=o.data_ptr(),
                   hT=hT.data_ptr(), status=status.data_ptr())
-    rc = native.lib().lethe_gdn_forward_static(ctypes.byref(a), torch.cuda.current_stream().cuda_stream)
+    rc = native.lib().lethe_gdn_forward_static(ctypes.byref(a), torch.cuda.current_stream(dev).cuda_stream)
     assert rc == 0, native.lib().lethe_gdn_strerror(rc)
-    torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before       # nothing came from torch's allocator
+    torch.cuda.synchronize(dev)
+    assert torch.cuda.memory_allocated(dev) == before    # nothing came from torch's allocator
     ops.check_status(status)
     ops.check_status(status_ref)
     return o, hT, o_ref, hT_ref
@@ -62,3 +63,20 @@ def test_static_forward_refuses_oversize():
     rc = native.lib().lethe_gdn_forward_static(ctypes.byref(a), None)
     assert rc != 0
     assert b"16 MiB" in native.lib().lethe_gdn_strerror(rc)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_static_forward_uses_the_gpu_that_owns_q_not_the_current_device():
+    """Every GPU has its own copy of the built-in workspace.  A caller whose thread has GPU 0 selected
+    while its tensors live on GPU 1 (a worker thread of a multi-GPU process) must get GPU 1's copy: the
+    results on GPU 1 equal the ordinary entry point bit for bit, twice in a row, and GPU 0 is left alone."""
+    assert torch.cuda.current_device() == 0
+    for (B, L, H, V, seed) in ((1, 512, 4, 64, 31), (1, 256, 2, 128, 32)):
+        o, hT, o_ref, hT_ref = _forward_both(B, L, H, V, seed, device="cuda:1")
+        assert o.device.index == 1
+        assert torch.equal(o, o_ref)
+        assert torch.equal(hT, hT_ref)
+    assert torch.cuda.current_device() == 0              # the call put the caller's device back
+    # and GPU 0's own copy still serves GPU 0
+    o, hT, o_ref, hT_ref = _forward_both(1, 256, 2, 64, 33, device="cuda:0")
+    assert torch.equal(o, o_ref) and torch.equal(hT, hT_ref)
