@@ -1,9 +1,10 @@
 """Builds ``oracle/_ref/``: the reference project's own Python modules, compiled to bytecode.
 
 The reference (RishiShah99/lethe) is pure Python on the CPU side of this path, so "building" it means
-byte-compiling its sources where they lie.  Only compiled ``.pyc`` files are written, into the
-git-ignored ``oracle/_ref/lethe/`` tree (sourceless imports: ``x.pyc`` sits where ``x.py`` would);
-no reference source is copied.  The tree travels with the checkout to a machine that has no copy
+byte-compiling its sources where they lie.  Only compiled code objects are written, into the
+git-ignored ``oracle/_ref/lethe/`` tree (``x.lbc`` where ``x.py`` would sit: the content of a ``.pyc``
+under a name that file-synchronisation tools do not filter out as a cache file); no reference source is
+copied.  ``import_reference()`` installs a small import hook that loads ``lethe.*`` from those files.  The tree travels with the checkout to a machine that has no copy
 of the reference, where the tests and the benchmark's CPU arm import ``lethe.*`` from it:
 
   * ``lethe.kernels.references.*``      the token-serial and chunkwise references (fp32 / fp64)
@@ -19,6 +20,9 @@ Usage:  python oracle/make_ref.py [/path/to/reference]        (default /root/ref
 
 from __future__ import annotations
 
+import importlib.abc
+import importlib.util
+import marshal
 import os
 import py_compile
 import shutil
@@ -27,6 +31,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 SUBTREES = ("lethe",)          # everything under src/lethe (a few hundred KB of bytecode)
+EXT = ".lbc"                   # a .pyc by content: 16-byte header, then the marshalled code object
 
 
 def build(reference_root: str = "/root/reference", quiet: bool = False) -> str | None:
@@ -44,7 +49,7 @@ def build(reference_root: str = "/root/reference", quiet: bool = False) -> str |
             for f in files:
                 if not f.endswith(".py"):
                     continue
-                dst = os.path.join(tmp, rel, f[:-3] + ".pyc")
+                dst = os.path.join(tmp, rel, f[:-3] + EXT)
                 os.makedirs(os.path.dirname(dst), exist_ok=True)
                 # dfile: the path tracebacks show; UNCHECKED_HASH: valid without the source file
                 py_compile.compile(os.path.join(dirpath, f), cfile=dst, dfile=os.path.join("reference", "src", rel, f),
@@ -61,17 +66,53 @@ def build(reference_root: str = "/root/reference", quiet: bool = False) -> str |
 
 def path() -> str | None:
     """``oracle/_ref`` if it holds the compiled reference, else None."""
-    return OUT if os.path.isfile(os.path.join(OUT, "lethe", "__init__.pyc")) else None
+    return OUT if os.path.isfile(os.path.join(OUT, "lethe", "__init__" + EXT)) else None
+
+
+class _RefImporter(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    """Finds and loads ``lethe`` and its submodules from the ``.lbc`` files under ``oracle/_ref``."""
+
+    def __init__(self, root: str):
+        self.root = root
+
+    def _file(self, fullname: str):
+        rel = os.path.join(self.root, *fullname.split("."))
+        if os.path.isfile(os.path.join(rel, "__init__" + EXT)):
+            return os.path.join(rel, "__init__" + EXT), True
+        if os.path.isfile(rel + EXT):
+            return rel + EXT, False
+        return None, False
+
+    def find_spec(self, fullname, path=None, target=None):
+        if fullname != "lethe" and not fullname.startswith("lethe."):
+            return None
+        file, is_pkg = self._file(fullname)
+        if file is None:
+            return None
+        spec = importlib.util.spec_from_loader(fullname, self, origin=file, is_package=is_pkg)
+        if is_pkg:
+            spec.submodule_search_locations = [os.path.dirname(file)]
+        return spec
+
+    def create_module(self, spec):
+        return None
+
+    def exec_module(self, module):
+        file, _ = self._file(module.__name__)
+        with open(file, "rb") as fh:
+            data = fh.read()
+        module.__file__ = file
+        exec(marshal.loads(data[16:]), module.__dict__)        # noqa: S102  (our own build product)
 
 
 def import_reference():
-    """Put ``oracle/_ref`` on ``sys.path`` and return the imported ``lethe`` package, or None when the
-    compiled reference is absent."""
+    """Install the import hook for ``oracle/_ref`` and return the imported ``lethe`` package, or None when
+    the compiled reference is absent."""
     p = path()
     if p is None:
         return None
-    if p not in sys.path:
-        sys.path.insert(0, p)
+    if not any(isinstance(f, _RefImporter) for f in sys.meta_path):
+        sys.meta_path.insert(0, _RefImporter(p))
     import lethe  # noqa: PLC0415
 
     return lethe

@@ -109,8 +109,15 @@ def test_reference_autograd_function_with_this_backward(regime, monkeypatch):
     o_got, got = run("cuda")                       # its forward (token loop in torch), this library's backward
     assert calls, "the reference's autograd function did not reach the swapped backward"
     assert scale_rel(o_got.double().cpu(), o_ref.double()) <= 1e-5
-    errs = {n: scale_rel(a.double().cpu(), r.double().cpu())
-            for n, a, r in zip(("dq", "dk", "dv", "dg", "db", "dw"), got, want)}
+    # A gate that was given as one value broadcast over the channels gets its gradient spread evenly over
+    # them here (as in the reference's own scalar assembly, gdn2_assemble.py:343-345), while the reference's
+    # eager path differentiates every channel: the two agree in the sum over the channels, which is the
+    # gradient of the underlying scalar.
+    bcast = {"dg": regime == "scalar", "db": regime != "full", "dw": regime != "full"}
+    errs = {}
+    for n, a, r in zip(("dq", "dk", "dv", "dg", "db", "dw"), got, want):
+        a, r = a.double().cpu(), r.double().cpu()
+        errs[n] = scale_rel(a.sum(-1), r.sum(-1)) if bcast.get(n) else scale_rel(a, r)
     report(f"reference _GDN2Function + this backward ({regime})", errs)
     assert max(errs.values()) <= TOL, errs
     assert all(a.dtype == r.dtype and a.shape == r.shape for a, r in zip(got, want))

@@ -162,8 +162,10 @@ def test_tiny_train_loop(arm):
     """The reference's training-loop evidence, arm by arm (``results/gdn2_tiny_train_native_sbe.json`` and
     ``gdn2_tiny_train_{kda,gla,ssd}.json`` of the reference project): a small language-model block around
     the six-input op (``lethe_b200.tiny.TinyGdnLM``), fp32 parameters, B=4, L=256, H=2, d_k=128, d_v=64,
-    delayed-copy task, 300 Adam steps at lr 0.01.  Bar, as there: no NaN anywhere, the loss starts near
-    ln(vocab) = 3.69 and ends below 1e-3.  Every step goes through the CUDA forward and backward."""
+    delayed-copy task, 300 Adam steps at lr 0.01.  Bar: no NaN anywhere, the loss starts near ln(vocab) =
+    3.69 and ends below 1e-3 for the two delta-rule arms (the reference's evidence: 8.9e-5 and 1.9e-4) and
+    below 5e-3 for the two arms without the delta term (the reference's evidence: GLA 1.5e-2, SSD 5.3e-3).
+    Every step goes through the CUDA forward and backward."""
     from lethe_b200.tiny import TinyGdnLM, delayed_copy_batch
 
     torch.manual_seed(0)
@@ -182,7 +184,7 @@ def test_tiny_train_loop(arm):
     assert all(torch.isfinite(p).all() for p in model.parameters())
     report(f"tiny-train {arm}", {"first": losses[0], "step100": losses[100], "last": losses[-1]})
     assert 3.0 < losses[0] < 4.5, losses[0]
-    assert losses[-1] < 1e-3, (losses[0], losses[-1])
+    assert losses[-1] < (1e-3 if arm in ("gdn", "kda") else 5e-3), (losses[0], losses[-1])
 
 
 def test_kernel_plugins_k1_k2():
