@@ -77,8 +77,10 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
     float x[8];
     unpack8_in(tile_ld_chunk(QG, r, ch, 64), x, p.qk16);
     if (CW) {
+      float gg[8];
+      gt8(Gt, r, ch * 8, gg);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[gidx(r, ch * 8 + i)]);
+      for (int i = 0; i < 8; ++i) x[i] *= p.scale * exp2f(gg[i]);
     } else {
       const float sg = p.scale * __expf(Gs[r]);
 #pragma unroll

@@ -16,7 +16,7 @@
 //           the final state, so record index is (b*H + h)*(NT + 1) + c
 //     VN    64 x V  image: v_new = u - w h
 //     AD    128 fp32: exp(G_last) per key channel     (the decay of the chunk)
-//     GT    channel-wise gate only: 64 x 128 fp32, the cumulative log decay of the chunk in the
+//     GT    channel-wise gate only: 64 x 128 fp32, the cumulative decay of the chunk in log2 units in the
 //           swizzled shared-memory arrangement of gidx(), written once by prepare and bulk-loaded
 //           by every later kernel instead of being recomputed
 //   scratch (backward only)
@@ -140,24 +140,26 @@ __device__ __forceinline__ float chunk_rev_cumsum(float x, int tid, float* tmp) 
   return x;
 }
 
-// Channel-wise gate tile: cumulative log decay of the chunk, 64 rows x 128 channels of fp32 in
-// shared memory.  Element (row, col) lives at gidx(row, col): the column is XOR-ed with the low row
-// bits so that both "thread d walks column d" and "thread i walks row i" are free of bank conflicts.
-__device__ __forceinline__ int gidx(int row, int col) { return row * kK + (col ^ (row & 31)); }
-
-// Thread d owns channel d.  `tok0` is the token index of the chunk's first row for this head (tokens
-// of a head are H apart).  All 64 loads are issued before the first add so that they overlap.
-__device__ __forceinline__ void gate_tile_cw(const float* g, size_t tok0, int H, int tid, float* Gt) {
-  float x[kC];
-#pragma unroll
-  for (int i = 0; i < kC; ++i) x[i] = g[(tok0 + static_cast<size_t>(i) * H) * kK + tid];
-  float acc = 0.f;
-#pragma unroll
-  for (int i = 0; i < kC; ++i) {
-    acc += x[i];
-    Gt[gidx(i, tid)] = acc;
-  }
+// Channel-wise gate tile: cumulative decay of the chunk in LOG2 units (G * log2 e, so that every decay
+// factor is one exp2 of a difference), 64 rows x 128 channels of fp32 in shared memory.  Element (row, col)
+// lives at gidx(row, col): the 16-byte pieces of a row (four channels) are XOR-ed with the low three row
+// bits.  "Thread d walks column d" touches 32 consecutive words of one row; "thread i reads row i" is done
+// with 16-byte loads (gt8 / gt4), which the swizzle spreads over all banks for eight neighbouring rows.
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ int gidx(int row, int col) {
+  return row * kK + ((((col >> 2) ^ row) & 7) << 2) + (col & ~31) + (col & 3);
 }
+// four / eight consecutive gate values of one row (col0 a multiple of 4 / 8)
+__device__ __forceinline__ float4 gt4(const float* Gt, int row, int col0) {
+  return *reinterpret_cast<const float4*>(Gt + gidx(row, col0));
+}
+__device__ __forceinline__ void gt8(const float* Gt, int row, int col0, float* g) {
+  const float4 a = gt4(Gt, row, col0), b = gt4(Gt, row, col0 + 4);
+  g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+}
+// fp32 exchange tiles [64][128] (not the gate tile): the column is XOR-ed with the low five row bits, so that
+// both "thread d walks column d" and "thread i walks row i" with scalar accesses are free of bank conflicts
+__device__ __forceinline__ int exi(int row, int col) { return row * kK + (col ^ (row & 31)); }
 
 // Control block at the start of every kernel: barriers, TMEM slot, abort flag.
 struct CtaShared {
@@ -232,8 +234,8 @@ __device__ __forceinline__ uint32_t rrec_off(int row, int col8) {
 }
 
 // T = (I + M)^-1 for a strictly lower-triangular 64 x 64 M (fp32, row stride MS floats, zeros on and
-// above the diagonal), by 16 x 16 blocks on all 256 threads of a CTA (every thread must call; four CTA-wide
-// barriers inside).  With D_b the inverses of the four diagonal blocks of I + M and N_ba = D_b M_ba
+// above the diagonal), by 16 x 16 blocks on threads 0-255 of a CTA (every thread of the CTA must call: four
+// CTA-wide barriers inside; threads beyond 255 only take part in the barriers).  With D_b the inverses of the four diagonal blocks of I + M and N_ba = D_b M_ba
 // (b > a), I + N is unit block-lower with N^4 = 0, so
 //   X = (I + N)^-1:  X_b,b-1 = -N_b,b-1;  X_20 = -N_20 + N_21 N_10;  X_31 = -N_31 + N_32 N_21;
 //                    X_30 = -N_30 + N_31 N_10 - N_32 X_20
@@ -278,8 +280,10 @@ __device__ __forceinline__ void unit_lower_inverse64_blocked(float* Msm, float* 
   float* Xs = Msm;                         // [3] X_20, X_31, X_30 (from stage 3 on)
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
+  const bool on = tid < 256;
   // ---- stage 1: D_b by forward substitution, one column per thread; the rest clear T above the diagonal
-  if (tid < 64) {
+  if (!on) {
+  } else if (tid < 64) {
     const int b = tid >> 4, j = tid & 15;
     const float* Mb = Msm + (16 * b) * MS + 16 * b;
     float col[16];
@@ -310,7 +314,8 @@ __device__ __forceinline__ void unit_lower_inverse64_blocked(float* Msm, float* 
   __syncthreads();
 
   // ---- stage 2: N_ba = D_b M_ba (one warp per block, a lane = one row x 8 columns); T_bb = D_b
-  if (tid < 192) {
+  if (!on) {
+  } else if (tid < 192) {
     const int p = tid >> 5, lane = tid & 31, i = lane >> 1, j0 = 8 * (lane & 1);
     const int b = p < 1 ? 1 : (p < 3 ? 2 : 3), a = p - b * (b - 1) / 2;
     float acc[8];
@@ -375,7 +380,7 @@ __device__ __forceinline__ void unit_lower_inverse64_blocked(float* Msm, float* 
 
   // ---- stage 5: T_30 = X_30 D_0, one element per thread (a lone warp with eight columns per lane
   // takes more than twice as long)
-  {
+  if (on) {
     const int i = tid >> 4, j = tid & 15;
     const float* left = Xs + 2 * kInvBlk + i * kInvBs;
     const float* right = Ds + j;

@@ -21,10 +21,6 @@
 
 namespace lg {
 
-// fp32 exchange tile [64][128] with a column swizzle so that "thread d writes column d" and
-// "thread i reads row i" are both free of bank conflicts
-__device__ __forceinline__ int exi(int row, int col) { return gidx(row, col); }
-
 // fp32 [64][128] records passed between the backward kernels (dq / dk / dG parts): element (i, d) of
 // a record lives at ridx(i, d) - the 16-byte pieces of a row are XOR-ed with the low row bits, so that
 // a shared-memory image of the record takes row-wise 16-byte stores and column-wise reads without
@@ -106,8 +102,11 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     float x[8], y[8];
     unpack8_in(tile_ld_chunk(X1, r, ch, 128), x, p.qk16);
     tile_st_chunk(X1, r, ch, 128, pack8_f16(x));
+    float gl8[8], gr8[8];
+    gt8(Gt, 63, ch * 8, gl8);
+    gt8(Gt, r, ch * 8, gr8);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = x[e] * __expf(Gt[gidx(63, ch * 8 + e)] - Gt[gidx(r, ch * 8 + e)]);
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * exp2f(gl8[e] - gr8[e]);
     tile_st_chunk(X1, 64 + r, ch, 128, pack8_f16(y));
     unpack8_in(tile_ld_chunk(QT, r, ch, 64), x, p.qk16);
     tile_st_chunk(QT, r, ch, 64, pack8_f16(x));
@@ -142,7 +141,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc += x[e] * y[e];
     }
-    hh[tid] = acc * __expf(Gt[gidx(63, tid)]);
+    hh[tid] = acc * exp2f(Gt[gidx(63, tid)]);
   }
   wait_products(bar_mma, ph, ctl, 602);
   if (tid >= 64 && tid < 128) {
@@ -210,13 +209,15 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
         float qv[8], kv[8];
         unpack8_f16(tile_ld_chunk(QT, r, jb * 4 + i, 64), qv);
         unpack8_f16(tile_ld_chunk(X1, r, jb * 4 + i, 128), kv);
-        float o1[8], o2[8], o3[8];
+        float o1[8], o2[8], o3[8], g8[8], gl8[8];
+        gt8(Gt, r, jb * 32 + i * 8, g8);
+        gt8(Gt, 63, jb * 32 + i * 8, gl8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int d = jb * 32 + i * 8 + e;
-          const float g = Gt[gidx(r, d)];
-          const float sg = p.scale * __expf(g);
-          const float de = __expf(Gt[gidx(63, d)] - g);
+          const float g = g8[e];
+          const float sg = p.scale * exp2f(g);
+          const float de = exp2f(gl8[e] - g);
           o1[e] = sg * dqg[8 * i + e];                       // part of dq
           o2[e] = dkd[8 * i + e] * de;                       // part of dk
           const float dde = o2[e] * kv[e];
@@ -343,8 +344,10 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
 #pragma unroll
       for (int e = 0; e < 8; ++e) bb[e] = be;
     }
+    float gg[8];
+    gt8(Gt, r, ch * 8, gg);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = x[e] * bb[e] * __expf(Gt[gidx(r, ch * 8 + e)]);
+    for (int e = 0; e < 8; ++e) y[e] = x[e] * bb[e] * exp2f(gg[e]);
     tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
@@ -471,10 +474,11 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float kv[8];
+        float kv[8], gg[8];
         unpack8_f16(tile_ld_chunk(KB, r, jb * 4 + i, 128), kv);
+        gt8(Gt, r, jb * 32 + i * 8, gg);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) pq += d[8 * i + e] * kv[e] * __expf(Gt[gidx(r, jb * 32 + i * 8 + e)]);
+        for (int e = 0; e < 8; ++e) pq += d[8 * i + e] * kv[e] * exp2f(gg[e]);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -500,8 +504,12 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
 // cumulative sum per channel); otherwise it leaves its contribution in the DGB record.
 // Accumulators: out1 rows 0-63 of [0,128); out2 rows 64-127 of [128,256).
 // ---------------------------------------------------------------------------------------------
+// 512 threads for the same reason as the forward's prepare kernel: one CTA per SM (197 KB of tiles) whose
+// CUDA-core phases are bound by instruction latency.
+constexpr int kPairThreads = 512;
+
 template <int MODE, bool FINAL_G>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPairThreads)
 bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024(smem_raw);
@@ -515,8 +523,8 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   float* fs = Gt + 64 * kK;
   float* Cd = fs;                // [64][16] diagonal blocks of C
   float* betas = fs + 1024;      // [64]
-  float* red = fs + 1088;        // [2][64] partial row sums for dbeta
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 1216);
+  float* red = fs + 1088;        // [4][64] partial row sums for dbeta
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 1344);
   float* EX1 = reinterpret_cast<float*>(KR);    // exchange tiles, once the products are done
   float* EX2 = reinterpret_cast<float*>(XE);
 
@@ -563,7 +571,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   mbar_wait_warp(bar_load, 0, ctl, 621);
   // ---- decayed operand rows
-  for (int idx = tid; idx < 64 * 16; idx += 256) {
+  for (int idx = tid; idx < 64 * 16; idx += kPairThreads) {
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8, blk = r >> 4;
     float kx[8], xx[8], y[8], gr[8];
     unpack8_in(tile_ld_chunk(KX, r, ch, 128), kx, p.qk16);
@@ -575,29 +583,31 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
 #pragma unroll
       for (int e = 0; e < 8; ++e) xx[e] *= bb[e];
     }
+    gt8(Gt, r, d0, gr);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      xx[e] *= be;
-      gr[e] = Gt[gidx(r, d0 + e)];
-    }
+    for (int e = 0; e < 8; ++e) xx[e] *= be;
     tile_st_chunk(KX, r, ch, 128, pack8_f16(kx));
     tile_st_chunk(KX, 64 + r, ch, 128, pack8_f16(xx));
     for (int I = blk + 1; I < 4; ++I) {
       const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
+      float ga[8];
+      gt8(Gt, I * 16, d0, ga);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[gidx((I * 16), d0 + e)] - gr[e]);
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * exp2f(ga[e] - gr[e]);
       tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
     }
     for (int J = 0; J < blk; ++J) {
       const int off = (J == 0) ? 0 : (J == 1 ? 48 : 80);
+      float ga[8];
+      gt8(Gt, J * 16 + 15, d0, ga);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = xx[e] * __expf(gr[e] - Gt[gidx((J * 16 + 15), d0 + e)]);
+      for (int e = 0; e < 8; ++e) y[e] = xx[e] * exp2f(gr[e] - ga[e]);
       tile_st_chunk(XE, off + (r - 16 * (J + 1)), ch, 128, pack8_f16(y));
     }
   }
   mbar_wait_warp(bar_c, 0, ctl, 623);
   // ---- masked copies of C and its diagonal blocks
-  for (int idx = tid; idx < 64 * 8; idx += 256) {
+  for (int idx = tid; idx < 64 * 8; idx += kPairThreads) {
     const int r = idx >> 3, s8 = idx & 7, blk = r >> 4, cb = s8 >> 1;
     const uint4 cv = tile_ld_chunk(CS, r, s8, 64);
     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -632,11 +642,11 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   wait_products(bar_mma, ph, ctl, 622);
   __syncthreads();          // products done for every thread: KR / XE become the exchange tiles
-  // ---- diagonal blocks, exact; thread d owns channel d
+  // ---- diagonal blocks, exact; thread (block, channel d) owns channel d of one 16-row block
   {
     const int d = tid & 127;
-#pragma unroll 1
-    for (int blk = 2 * (tid >> 7); blk < 2 * (tid >> 7) + 2; ++blk) {
+    {
+      const int blk = tid >> 7;
       float g[16], kk[16], xv[16], a1[16], a2[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -652,7 +662,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
 #pragma unroll
         for (int ss = 0; ss <= ii; ++ss) {
           const float cv = Cd[(blk * 16 + ii) * 16 + ss];
-          const float e = cv * __expf(g[ii] - g[ss]);
+          const float e = cv * exp2f(g[ii] - g[ss]);
           a1[ii] += e * kk[ss];
           a2[ss] += e * xv[ii];
         }
@@ -666,27 +676,29 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   __syncthreads();
   // ---- phase A: row owners fold the tensor-core part (with its decay) into the exchange tiles.
-  // Threads 0-127 own accumulator lanes 0-127 and take columns 0-63; threads 128-255 (warps 4-7 reach
-  // the same lanes) take columns 64-127.
+  // Thread t & 127 owns accumulator lane t & 127; the four warps that reach a lane quadrant (w, w + 4, w + 8,
+  // w + 12) take one 32-column block each.
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   {
-    const int t = tid & 127, jb0 = 2 * (tid >> 7);
+    const int t = tid & 127, jb0 = tid >> 7;      // the four warps of a lane quadrant take one 32-column block each
     if (t < 64) {
       const int i = t, a = (i >> 4) * 16;      // out1 row i: decay from the block's reference row
       float rsum = 0.f;
 #pragma unroll 1
-      for (int jb = jb0; jb < jb0 + 2; ++jb) {
+      for (int jb = jb0; jb < jb0 + 1; ++jb) {
         float acc[32];
         tmem_ld32(tmem + lane_base + jb * 32, acc);
         tmem_ld_wait();
 #pragma unroll
         for (int q8 = 0; q8 < 4; ++q8) {
-          float kv[8];
+          float kv[8], gi8[8], ga8[8];
           if (MODE == 1) unpack8_f16(tile_ld_chunk(KX, i, jb * 4 + q8, 128), kv);
+          gt8(Gt, i, jb * 32 + q8 * 8, gi8);
+          gt8(Gt, a, jb * 32 + q8 * 8, ga8);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int d = jb * 32 + q8 * 8 + e;
-            const float o1 = acc[8 * q8 + e] * __expf(Gt[gidx(i, d)] - Gt[gidx(a, d)]) + EX1[exi(i, d)];
+            const float o1 = acc[8 * q8 + e] * exp2f(gi8[e] - ga8[e]) + EX1[exi(i, d)];
             EX1[exi(i, d)] = o1;
             if (MODE == 1) rsum += o1 * kv[e];
           }
@@ -696,25 +708,32 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     } else {
       const int s = t - 64, el = (s >> 4) * 16 + 15;   // out2 row s: decay to the last row of its block
 #pragma unroll 1
-      for (int jb = jb0; jb < jb0 + 2; ++jb) {
+      for (int jb = jb0; jb < jb0 + 1; ++jb) {
         float acc[32];
         tmem_ld32(tmem + 128 + lane_base + jb * 32, acc);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int d = jb * 32 + e;
-          EX2[exi(s, d)] = acc[e] * __expf(Gt[gidx(el, d)] - Gt[gidx(s, d)]) + EX2[exi(s, d)];
+        for (int q8 = 0; q8 < 4; ++q8) {
+          float ge8[8], gs8[8];
+          gt8(Gt, el, jb * 32 + q8 * 8, ge8);
+          gt8(Gt, s, jb * 32 + q8 * 8, gs8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int d = jb * 32 + q8 * 8 + e;
+            EX2[exi(s, d)] = acc[8 * q8 + e] * exp2f(ge8[e] - gs8[e]) + EX2[exi(s, d)];
+          }
         }
       }
     }
   }
   __syncthreads();
-  if (MODE == 1 && !full && tid < 64) p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += red[tid] + red[64 + tid];   // sum_d d(bk)_m k
+  if (MODE == 1 && !full && tid < 64)      // sum_d d(bk)_m k
+    p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += (red[tid] + red[64 + tid]) + (red[128 + tid] + red[192 + tid]);
   // ---- phase B: column owners (thread d; the two halves of the CTA split the rows) combine with the
   // fp32 records; every global access is coalesced and the records of eight rows are requested before
   // any of them is used or overwritten.
   {
-    const int d = tid & 127, ibase = 32 * (tid >> 7);
+    const int d = tid & 127, ibase = 16 * (tid >> 7);
     const float* __restrict__ dqp_g = reinterpret_cast<const float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
     float* __restrict__ dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
     float* __restrict__ dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
@@ -728,7 +747,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
       ndkb[j] = dkb_g[ridx(ibase + j, d)];
     }
 #pragma unroll 1
-    for (int i0 = ibase; i0 < ibase + 32; i0 += 8) {
+    for (int i0 = ibase; i0 < ibase + 16; i0 += 8) {
       float part8[8], dgb8[8], dkb8[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -736,7 +755,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
         dgb8[j] = ndgb[j];
         dkb8[j] = ndkb[j];
       }
-      if (i0 + 8 < ibase + 32) {
+      if (i0 + 8 < ibase + 16) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           npart[j] = dqp_g[ridx(i0 + 8 + j, d)];
@@ -758,7 +777,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
           dk = dkb + o2;
           dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
         } else {
-          const float eg = __expf(Gt[gidx(i, d)]);
+          const float eg = exp2f(Gt[gidx(i, d)]);
           const float dbk = part * eg + o1;              // d(beta k), or d(b k) of the full op
           if (full) {
             dk = dkb + dbk * p.bch[tok] + o2;
@@ -815,10 +834,10 @@ static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
 }
 template <int MODE, bool FINAL_G>
 static int launch_pair_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, cudaStream_t st) {
-  const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1216 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1344 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_cw_pair_kernel<MODE, FINAL_G>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk) !=
+  if (launch_dependent(bwd_cw_pair_kernel<MODE, FINAL_G>, dim3(p.nbh * p.NT), dim3(kPairThreads), smem, st, p, mq, mk) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -19,9 +19,12 @@
 namespace lg {
 
 constexpr int kMsC = 68;
+constexpr int kPrepCwThreads = 256;
+constexpr int kGateSegs = kPrepCwThreads / 128;       // row segments of the cumulative sum (thread = segment x channel)
+constexpr int kGateRows = kC / kGateSegs;
 
 template <int V, bool DELTA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPrepCwThreads)
 prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
                   const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
   extern __shared__ unsigned char smem_raw[];
@@ -74,9 +77,24 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     }
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
-  if (tid < 128) {
-    gate_tile_cw(p.g, tok0, p.H, tid, Gt);
-    reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + tid] = __expf(Gt[gidx(63, tid)]);
+  {
+    // cumulative decay: thread (segment of rows, channel) sums its rows, the segment totals are exchanged
+    // through shared memory (Adg is free until the diagonal blocks), every thread adds the totals of the
+    // segments before its own and writes its entries once, in log2 units
+    const int seg = tid >> 7, d = tid & 127;
+    float x[kGateRows];
+#pragma unroll
+    for (int i = 0; i < kGateRows; ++i) x[i] = p.g[(tok0 + static_cast<size_t>(seg * kGateRows + i) * p.H) * kK + d];
+#pragma unroll
+    for (int i = 1; i < kGateRows; ++i) x[i] += x[i - 1];
+    Adg[seg * kK + d] = x[kGateRows - 1];
+    __syncthreads();
+    float base = 0.f;
+    for (int s2 = 0; s2 < seg; ++s2) base += Adg[s2 * kK + d];
+#pragma unroll
+    for (int i = 0; i < kGateRows; ++i) Gt[gidx(seg * kGateRows + i, d)] = (base + x[i]) * kLog2e;
+    if (seg == kGateSegs - 1)
+      reinterpret_cast<float*>(p.saved + p.lay.ad)[static_cast<size_t>(z) * kK + d] = __expf(base + x[kGateRows - 1]);
     fence_proxy_async();
   }
   __syncthreads();
@@ -87,7 +105,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   }
   // ---- operand tiles
   mbar_wait_warp(bar_load, 0, ctl, 501);
-  for (int idx = tid; idx < 64 * 16; idx += 256) {
+  for (int idx = tid; idx < 64 * 16; idx += kPrepCwThreads) {
     const int r = idx >> 4, ch = idx & 15, d0 = ch * 8;
     const int blk = r >> 4;
     float kx[8], qx[8], y[8], gr[8], ga[8], gl[8];
@@ -95,15 +113,12 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     unpack8_in(tile_ld_chunk(KQ, 64 + r, ch, 128), qx, p.qk16);
     tile_st_chunk(KQ, r, ch, 128, pack8_f16(kx));
     tile_st_chunk(KQ, 64 + r, ch, 128, pack8_f16(qx));
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      gr[e] = Gt[gidx(r, d0 + e)];
-      ga[e] = Gt[gidx((blk * 16), d0 + e)];
-      gl[e] = Gt[gidx(63, d0 + e)];
-    }
+    gt8(Gt, r, d0, gr);
+    gt8(Gt, blk * 16, d0, ga);
+    gt8(Gt, 63, d0, gl);
     float ea[8], bb[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ea[e] = __expf(gr[e] - ga[e]);
+    for (int e = 0; e < 8; ++e) ea[e] = exp2f(gr[e] - ga[e]);
     if (DELTA && full) {
       ld8(p.bch + (tok0 + static_cast<size_t>(r) * p.H) * kK + d0, bb);
 #pragma unroll
@@ -117,7 +132,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     for (int e = 0; e < 8; ++e) y[e] = qx[e] * ea[e];
     tile_st_chunk(LA, 64 + r, ch, 128, pack8_f16(y));
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(gl[e] - gr[e]);
+    for (int e = 0; e < 8; ++e) y[e] = kx[e] * exp2f(gl[e] - gr[e]);
     tile_st_chunk(KD, r, ch, 64, pack8_f16(y));
     if (DELTA) {
       if (!full) {
@@ -126,17 +141,18 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
         for (int e = 0; e < 8; ++e) bb[e] = be;
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = kx[e] * bb[e] * __expf(gr[e]);
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * bb[e] * exp2f(gr[e]);
       tile_st_chunk(BGK, r, ch, 64, pack8_f16(y));
     }
     for (int I = blk + 1; I < 4; ++I) {     // row r is a source row for every later row block I
       const int off = (I == 1) ? 0 : (I == 2 ? 16 : 48);
+      gt8(Gt, I * 16, d0, ga);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = kx[e] * __expf(Gt[gidx((I * 16), d0 + e)] - gr[e]);
+      for (int e = 0; e < 8; ++e) y[e] = kx[e] * exp2f(ga[e] - gr[e]);
       tile_st_chunk(KR, off + r, ch, 128, pack8_f16(y));
     }
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 256) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += kPrepCwThreads) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(BV, r, ch, 64), x);
@@ -165,37 +181,68 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     umma_commit_led(leader, bar_mma);
   }
   __syncwarp();
-  // ---- diagonal blocks, exact: pair (i, s) of one block, s <= i
-  for (int pp = tid; pp < 4 * 136; pp += 256) {
-    const int blk = pp / 136, t = pp % 136;
-    int ii = static_cast<int>((sqrtf(8.f * t + 1.f) - 1.f) * 0.5f);
-    while ((ii + 1) * (ii + 2) / 2 <= t) ++ii;
-    while (ii * (ii + 1) / 2 > t) --ii;
-    const int ss = t - ii * (ii + 1) / 2;
-    const int i = blk * 16 + ii, s = blk * 16 + ss;
-    float acc_a = 0.f, acc_m = 0.f;
-#pragma unroll 4
-    for (int ch = 0; ch < 16; ++ch) {
-      float qi[8], ki[8], ks[8];
-      unpack8_f16(tile_ld_chunk(KQ, 64 + i, ch, 128), qi);
-      unpack8_f16(tile_ld_chunk(KQ, i, ch, 128), ki);
-      unpack8_f16(tile_ld_chunk(KQ, s, ch, 128), ks);
+  // ---- diagonal blocks, exact: pairs (i, s) of one 16-row block, s <= i, one exp2 per pair and channel.
+  // Thread (block, row pair j, piece c): rows 16 blk + j and 16 blk + 15 - j - together 17 pairs, the same
+  // count for every thread - over channels [16 c, 16 c + 16).  The row operands stay in registers while
+  // the source rows stream by; the eight pieces of a pair sit in neighbouring lanes and are added by a
+  // butterfly (fixed order: deterministic).
+  {
+    static_assert(kPrepCwThreads == 256, "4 blocks x 8 row pairs x 8 pieces");
+    const int c = tid & 7, j = (tid >> 3) & 7, blk = tid >> 6;
+    float qi[16], ki[16], gi[16];
+    auto load_row = [&](int i) {
+      unpack8_f16(tile_ld_chunk(KQ, 64 + i, 2 * c, 128), qi);
+      unpack8_f16(tile_ld_chunk(KQ, 64 + i, 2 * c + 1, 128), qi + 8);
+      unpack8_f16(tile_ld_chunk(KQ, i, 2 * c, 128), ki);
+      unpack8_f16(tile_ld_chunk(KQ, i, 2 * c + 1, 128), ki + 8);
+      gt8(Gt, i, 16 * c, gi);
+      gt8(Gt, i, 16 * c + 8, gi + 8);
       if (DELTA && full) {
-        float bi[8];
-        ld8(p.bch + (tok0 + static_cast<size_t>(i) * p.H) * kK + ch * 8, bi);
+        float bi[16];
+        const float* bp = p.bch + (tok0 + static_cast<size_t>(i) * p.H) * kK + 16 * c;
+        ld8(bp, bi);
+        ld8(bp + 8, bi + 8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ki[e] *= bi[e];
+        for (int e = 0; e < 16; ++e) ki[e] *= bi[e];
       }
+    };
+    int i = blk * 16 + j;
+    load_row(i);
+#pragma unroll 1
+    for (int t = 0; t < 17; ++t) {
+      if (t == j + 1) {               // the first row's pairs are done: on to the mirrored row
+        i = blk * 16 + 15 - j;
+        load_row(i);
+      }
+      const int ss = (t > j) ? t - j - 1 : t;
+      const int s = blk * 16 + ss;
+      float ks[16], gs[16];
+      unpack8_f16(tile_ld_chunk(KQ, s, 2 * c, 128), ks);
+      unpack8_f16(tile_ld_chunk(KQ, s, 2 * c + 1, 128), ks + 8);
+      gt8(Gt, s, 16 * c, gs);
+      gt8(Gt, s, 16 * c + 8, gs + 8);
+      float aa0 = 0.f, aa1 = 0.f, mm0 = 0.f, mm1 = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float ex = __expf(Gt[gidx(i, ch * 8 + e)] - Gt[gidx(s, ch * 8 + e)]);
-        const float kse = ks[e] * ex;
-        acc_a += qi[e] * kse;
-        acc_m += ki[e] * kse;
+      for (int e = 0; e < 16; e += 2) {
+        const float k0 = ks[e] * exp2f(gi[e] - gs[e]);
+        const float k1 = ks[e + 1] * exp2f(gi[e + 1] - gs[e + 1]);
+        aa0 = fmaf(qi[e], k0, aa0);
+        aa1 = fmaf(qi[e + 1], k1, aa1);
+        mm0 = fmaf(ki[e], k0, mm0);
+        mm1 = fmaf(ki[e + 1], k1, mm1);
+      }
+      float acc_a = aa0 + aa1, acc_m = mm0 + mm1;
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) {
+        acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
+        acc_m += __shfl_xor_sync(0xffffffffu, acc_m, o);
+      }
+      if (c == 0) {
+        const int ii = i - blk * 16;
+        Adg[i * 16 + ss] = p.scale * acc_a;
+        Mdg[i * 16 + ss] = (DELTA && ss < ii) ? betas[i] * acc_m : 0.f;
       }
     }
-    Adg[i * 16 + ss] = p.scale * acc_a;
-    Mdg[i * 16 + ss] = (DELTA && ss < ii) ? betas[i] * acc_m : 0.f;
   }
   __syncthreads();
   wait_products(bar_mma, ph, ctl, 502);
@@ -270,14 +317,14 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       if (tid == 0) bulk_commit();
     }
     wait_products(bar_mma, ph, ctl, 503);
-    if (tid < 64) {
+    if ((tid & 127) < 64) {     // rows 0-63: lane quadrants 0 and 1; the four warps of a quadrant split the columns
 #pragma unroll 1
-      for (int jb = 0; jb < (128 + V) / 32; ++jb) {
+      for (int jb = tid >> 7; jb < (128 + V) / 32; jb += kPrepCwThreads / 128) {
         float d[32];
         tmem_ld32(tmem + lane_base + jb * 32, d);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tile_st_chunk(WU, tid, jb * 4 + i, 64, pack8_f16(d + 8 * i));
+        for (int i = 0; i < 4; ++i) tile_st_chunk(WU, tid & 127, jb * 4 + i, 64, pack8_f16(d + 8 * i));
       }
     }
     sync_for_issue();
@@ -306,10 +353,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     // leave by bulk stores; the two thread halves split the columns.
     unsigned char* SP = LA;
     unsigned char* SR = KR;
-    const int tq = tid & 127, half = tid >> 7;
-    constexpr int kHalfBlocks = N3 / 64;
+    const int tq = tid & 127;
+    // warp w reads the lanes of quadrant w & 3; the four warps of a quadrant split the 32-column blocks
 #pragma unroll 1
-    for (int jb = half * kHalfBlocks; jb < (half + 1) * kHalfBlocks; ++jb) {
+    for (int jb = tid >> 7; jb < N3 / 32; jb += kPrepCwThreads / 128) {
       float d[32];
       tmem_ld32(tmem + lane_base + jb * 32, d);
       tmem_ld_wait();
@@ -346,7 +393,7 @@ static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CU
   auto kern = prepare_cw_kernel<V, DELTA>;
   static SmemAttr attr;
   if (attr.set(kern, smem)) return kErrLaunch;
-  kern<<<p.nbh * p.NT, 256, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.nbh * p.NT, kPrepCwThreads, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

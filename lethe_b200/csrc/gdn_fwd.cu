@@ -373,8 +373,10 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
     float x[8];
     unpack8_in(tile_ld_chunk(WQ, 64 + r, ch, 128), x, p.qk16);
     if (CW) {
+      float gg[8];
+      gt8(Gt, r, ch * 8, gg);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] *= p.scale * __expf(Gt[gidx(r, ch * 8 + i)]);
+      for (int i = 0; i < 8; ++i) x[i] *= p.scale * exp2f(gg[i]);
     } else {
       const float sg = p.scale * __expf(Gs[r]);
 #pragma unroll

@@ -166,12 +166,13 @@ def k2_fn(k: Tensor, v: Tensor, beta: Tensor, g2: Tensor, t_mat: Tensor, dw: Ten
 
 
 def _gate_tile_image(G: Tensor) -> Tensor:
-    """[Z, 64, 128] fp32 cumulative log decay -> the record image the kernels read: element (row, col) at
-    row * 128 + (col ^ (row & 31))."""
+    """[Z, 64, 128] fp32 cumulative decay in log2 units -> the record image the kernels read: element
+    (row, col) at row * 128 + (col & ~31) + 4 * (((col >> 2) ^ row) & 7) + (col & 3) (the 16-byte pieces of
+    every 128-byte line XOR-ed with the low three row bits)."""
     Z = G.shape[0]
     row = torch.arange(64, device=G.device)[:, None]
     col = torch.arange(128, device=G.device)[None, :]
-    dst = (row * 128 + (col ^ (row & 31))).reshape(-1)
+    dst = (row * 128 + (col & ~31) + ((((col >> 2) ^ row) & 7) << 2) + (col & 3)).reshape(-1)
     img = torch.empty(Z, 64 * 128, dtype=torch.float32, device=G.device)
     img[:, dst] = G.reshape(Z, -1)
     return img
@@ -194,7 +195,7 @@ def k2_fn_cw(k: Tensor, v: Tensor, b: Tensor, w: Tensor, g2: Tensor, t_mat: Tens
     ta = torch.zeros(B, H, NT, 128, 64, dtype=torch.float16, device=dev)
     ta[..., :64, :] = t_mat.half()
     _record_view(buf.saved, off["ta"], sz["ta"], Z, torch.float16).copy_(to_image(ta).reshape(Z, -1))
-    _record_view(buf.saved, off["gt"], sz["gt"], Z, f32).copy_(_gate_tile_image((g2.to(f32) * LN2).reshape(Z, C, K)))
+    _record_view(buf.saved, off["gt"], sz["gt"], Z, f32).copy_(_gate_tile_image(g2.to(f32).reshape(Z, C, K)))
     _record_view(buf.scratch, off2["dv2"], sz2["dv2"], Z, torch.float16).copy_(to_image(du.half()).reshape(Z, -1))
     _record_view(buf.scratch, off2["dw"], sz2["dw"], Z, torch.float16).copy_(to_image(dwy.half()).reshape(Z, -1))
     _record_view(buf.scratch, off2["dkb"], sz2["dkb"], Z, f32).zero_()
