@@ -534,11 +534,15 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
   uint64_t* bar_c = &cs->bar[2];        // C (dA or dM), written by the kernel just before this one
+  uint64_t* bar_rec = &cs->bar[3];      // the fp32 records of phase B, fetched into dead operand tiles
+  float* RQ = reinterpret_cast<float*>(CS);               // 32 KB: the dq part (Stage B) / d(beta gamma k) part (WY VJP)
+  float* RK = reinterpret_cast<float*>(CS + 32768);       // 32 KB: the dk part
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     mbar_init(bar_c, 1);
+    mbar_init(bar_rec, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -642,6 +646,14 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   }
   wait_products(bar_mma, ph, ctl, 622);
   __syncthreads();          // products done for every thread: KR / XE become the exchange tiles
+  // The masked copies of C (CS, MB, MA: 64 KB in a row) are dead too: two of the three fp32 records phase B
+  // combines are fetched into them now, by bulk copies that run under the diagonal blocks and phase A,
+  // instead of being read element by element from global memory when phase B needs them.
+  if (tid == 0) {
+    mbar_expect_tx(bar_rec, 65536u);
+    bulk_g2s(RQ, p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4), 32768u, bar_rec);
+    bulk_g2s(RK, p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb, 32768u, bar_rec);
+  }
   // ---- diagonal blocks, exact; thread (block, channel d) owns channel d of one 16-row block
   {
     const int d = tid & 127;
@@ -729,81 +741,65 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   __syncthreads();
   if (MODE == 1 && !full && tid < 64)      // sum_d d(bk)_m k
     p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += (red[tid] + red[64 + tid]) + (red[128 + tid] + red[192 + tid]);
-  // ---- phase B: column owners (thread d; the two halves of the CTA split the rows) combine with the
-  // fp32 records; every global access is coalesced and the records of eight rows are requested before
-  // any of them is used or overwritten.
+  // ---- phase B: column owners (thread (row group, channel d): 16 rows each) combine with the fp32 records:
+  // the dq / dk parts from their shared-memory copies, the gate-gradient part from global memory (all 16
+  // rows requested at once; coalesced along d).
+  mbar_wait_warp(bar_rec, 0, ctl, 624);
   {
     const int d = tid & 127, ibase = 16 * (tid >> 7);
-    const float* __restrict__ dqp_g = reinterpret_cast<const float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
     float* __restrict__ dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
     float* __restrict__ dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
     constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
-    // the records of the next eight rows are requested before the current eight are worked on
-    float npart[8], ndgb[8], ndkb[8];
+    float dgb16[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      npart[j] = dqp_g[ridx(ibase + j, d)];
-      ndgb[j] = dgb_g[ridx(ibase + j, d)];
-      ndkb[j] = dkb_g[ridx(ibase + j, d)];
-    }
-#pragma unroll 1
-    for (int i0 = ibase; i0 < ibase + 16; i0 += 8) {
-      float part8[8], dgb8[8], dkb8[8];
+    for (int j = 0; j < 16; ++j) dgb16[j] = dgb_g[ridx(ibase + j, d)];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        part8[j] = npart[j];
-        dgb8[j] = ndgb[j];
-        dkb8[j] = ndkb[j];
-      }
-      if (i0 + 8 < ibase + 16) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          npart[j] = dqp_g[ridx(i0 + 8 + j, d)];
-          ndgb[j] = dgb_g[ridx(i0 + 8 + j, d)];
-          ndkb[j] = dkb_g[ridx(i0 + 8 + j, d)];
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int i = i0 + j;
-        const float part = part8[j], dgb = dgb8[j], dkb = dkb8[j];
-        const float o1 = EX1[exi(i, d)], o2 = EX2[exi(i, d)];
-        const float kv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(i, d, 128)));
-        const float xv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(64 + i, d, 128)));
-        const size_t tok = (tok0 + static_cast<size_t>(i) * p.H) * kK + d;
-        float dk, dG;
-        if (MODE == 0) {
-          store_out16(p.dq + tok, part + o1, p.qk16);
-          dk = dkb + o2;
-          dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
+    for (int j = 0; j < 16; ++j) {
+      const int i = ibase + j;
+      const float part = RQ[ridx(i, d)], dgb = dgb16[j], dkb = RK[ridx(i, d)];
+      const float o1 = EX1[exi(i, d)], o2 = EX2[exi(i, d)];
+      const float kv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(i, d, 128)));
+      const float xv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(64 + i, d, 128)));
+      const size_t tok = (tok0 + static_cast<size_t>(i) * p.H) * kK + d;
+      float dk, dG;
+      if (MODE == 0) {
+        store_out16(p.dq + tok, part + o1, p.qk16);
+        dk = dkb + o2;
+        dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
+      } else {
+        const float eg = exp2f(Gt[gidx(i, d)]);
+        const float dbk = part * eg + o1;              // d(beta k), or d(b k) of the full op
+        if (full) {
+          dk = dkb + dbk * p.bch[tok] + o2;
+          p.dbch[tok] = dbk * kv;
         } else {
-          const float eg = exp2f(Gt[gidx(i, d)]);
-          const float dbk = part * eg + o1;              // d(beta k), or d(b k) of the full op
-          if (full) {
-            dk = dkb + dbk * p.bch[tok] + o2;
-            p.dbch[tok] = dbk * kv;
-          } else {
-            dk = dkb + dbk * betas[i] + o2;
-          }
-          dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
+          dk = dkb + dbk * betas[i] + o2;
         }
-        if (kFinalK) store_out16(p.dk + tok, dk, p.qk16);
-        else dkb_g[ridx(i, d)] = dk;
-        if (FINAL_G) EX1[exi(i, d)] = dG;                // closed below by the reverse cumulative sum
-        else dgb_g[ridx(i, d)] = dG;
+        dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
       }
+      if (kFinalK) store_out16(p.dk + tok, dk, p.qk16);
+      else dkb_g[ridx(i, d)] = dk;
+      if (FINAL_G) EX1[exi(i, d)] = dG;                // closed below by the reverse cumulative sum
+      else dgb_g[ridx(i, d)] = dG;
     }
   }
-  if (FINAL_G) {   // dg[i, d] = sum_{j >= i} dG[j, d]; thread d walks its channel from the last row up
+  if (FINAL_G) {
+    // dg[i, d] = sum_{j >= i} dG[j, d]: thread (row group, channel) forms the suffix sums of its 16 rows, the
+    // group totals are exchanged through shared memory (Cd is dead since the diagonal blocks) and the totals
+    // of the groups below are added
     __syncthreads();
-    if (tid < 128) {
-      float run = 0.f;
-#pragma unroll 8
-      for (int i = 63; i >= 0; --i) {
-        run += EX1[exi(i, tid)];
-        p.dg[(tok0 + static_cast<size_t>(i) * p.H) * kK + tid] = run;
-      }
-    }
+    const int d = tid & 127, grp = tid >> 7;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = EX1[exi(grp * 16 + j, d)];
+#pragma unroll
+    for (int j = 14; j >= 0; --j) v[j] += v[j + 1];
+    Cd[grp * kK + d] = v[0];
+    __syncthreads();
+    float below = 0.f;
+    for (int g2 = 3; g2 > grp; --g2) below += Cd[g2 * kK + d];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) p.dg[(tok0 + static_cast<size_t>(grp * 16 + j) * p.H) * kK + d] = v[j] + below;
   }
   tc_fence_before();
   __syncthreads();

@@ -50,26 +50,15 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
+  // Everything that has to come from global memory is requested first - the tensor-map loads of k, q, v by
+  // the thread that has just initialised their barrier, the gate values and beta by every thread - so that
+  // the one memory latency of the chunk overlaps the tensor-memory allocation and the first barrier.
   if (tid == 0) {
     cs->abort_flag = 0;
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     fence_mbar_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(&cs->tmem_slot, 256);
-    tmem_relinquish();
-  }
-  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
-  // full op (per-channel erase gate b, write gate w): the gates enter the operand tiles element by
-  // element and the per-row beta is one
-  const bool full = p.bch != nullptr;
-  if (DELTA && tid < 64) betas[tid] = full ? 1.f : p.beta[tok0 + static_cast<size_t>(tid) * p.H];
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = cs->tmem_slot;
-  if (tid == 0) {
+    fence_proxy_async();
     mbar_expect_tx(bar_load, 32768u + V * 128u);
     for (int a = 0; a < 2; ++a) {
       tma_load_4d(KQ + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
@@ -77,14 +66,31 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     }
     for (int a = 0; a < V / 64; ++a) tma_load_4d(BV + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
   }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  const int seg = tid >> 7;
+  float x[kGateRows];
+#pragma unroll
+  for (int i = 0; i < kGateRows; ++i)
+    x[i] = p.g[(tok0 + static_cast<size_t>(seg * kGateRows + i) * p.H) * kK + (tid & 127)];
+  // full op (per-channel erase gate b, write gate w): the gates enter the operand tiles element by
+  // element and the per-row beta is one
+  const bool full = p.bch != nullptr;
+  float beta_r = 1.f;
+  if (DELTA && tid < 64 && !full) beta_r = p.beta[tok0 + static_cast<size_t>(tid) * p.H];
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 256);
+    tmem_relinquish();
+  }
+  if (DELTA && tid < 64) betas[tid] = beta_r;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
   {
     // cumulative decay: thread (segment of rows, channel) sums its rows, the segment totals are exchanged
     // through shared memory (Adg is free until the diagonal blocks), every thread adds the totals of the
     // segments before its own and writes its entries once, in log2 units
-    const int seg = tid >> 7, d = tid & 127;
-    float x[kGateRows];
-#pragma unroll
-    for (int i = 0; i < kGateRows; ++i) x[i] = p.g[(tok0 + static_cast<size_t>(seg * kGateRows + i) * p.H) * kK + d];
+    const int d = tid & 127;
 #pragma unroll
     for (int i = 1; i < kGateRows; ++i) x[i] += x[i - 1];
     Adg[seg * kK + d] = x[kGateRows - 1];
@@ -208,7 +214,9 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     };
     int i = blk * 16 + j;
     load_row(i);
-#pragma unroll 1
+    // (unrolled: the loads of a pair and the butterfly of the pair before it overlap this pair's arithmetic;
+    // rolled up, every iteration is one chain of dependent latencies and runs at a quarter of the issue rate)
+#pragma unroll
     for (int t = 0; t < 17; ++t) {
       if (t == j + 1) {               // the first row's pairs are done: on to the mirrored row
         i = blk * 16 + 15 - j;
@@ -247,44 +255,54 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   __syncthreads();
   wait_products(bar_mma, ph, ctl, 502);
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  if (tid < 128) {
+  {
+    // thread t & 127 owns accumulator lane t & 127 (row r of M for lanes 0-63, of A for lanes 64-127); the two
+    // warps that reach a lane quadrant split the row's 64 columns in halves
+    const int t = tid & 127, half = tid >> 7;
     float d[96];
     tmem_ld32(tmem + lane_base, d);
     tmem_ld32(tmem + lane_base + 32, d + 32);
     tmem_ld32(tmem + lane_base + 64, d + 64);
     tmem_ld_wait();
-    const int r = tid & 63, I = r >> 4;
-    float row[64];
+    const int r = t & 63, I = r >> 4;
+    float row[32];                       // this half's off-diagonal values: columns [32 half, 32 half + 32)
 #pragma unroll
-    for (int s = 0; s < 64; ++s) row[s] = 0.f;
-    if (I == 1) {
+    for (int s = 0; s < 32; ++s) row[s] = 0.f;
+    if (half == 0) {
+      if (I == 1) {
 #pragma unroll
-      for (int s = 0; s < 16; ++s) row[s] = d[s];
-    } else if (I == 2) {
+        for (int s = 0; s < 16; ++s) row[s] = d[s];
+      } else if (I == 2) {
 #pragma unroll
-      for (int s = 0; s < 32; ++s) row[s] = d[16 + s];
+        for (int s = 0; s < 32; ++s) row[s] = d[16 + s];
+      } else if (I == 3) {
+#pragma unroll
+        for (int s = 0; s < 32; ++s) row[s] = d[48 + s];
+      }
     } else if (I == 3) {
 #pragma unroll
-      for (int s = 0; s < 48; ++s) row[s] = d[48 + s];
+      for (int s = 0; s < 16; ++s) row[s] = d[80 + s];
     }
-    if (tid < 64) {
+    if (t < 64) {
       if (DELTA) {
         const float be = betas[r];
 #pragma unroll
-        for (int s = 0; s < 64; ++s) {
-          float m = row[s] * be;                               // off-diagonal blocks (zero beyond 16 I)
+        for (int j = 0; j < 32; ++j) {
+          const int s = half * 32 + j;
+          float m = row[j] * be;                               // off-diagonal blocks (zero beyond 16 I)
           if ((s >> 4) == I) m = (s < r) ? Mdg[r * 16 + (s & 15)] : 0.f;
           Msm[r * kMsC + s] = m;
         }
       }
     } else {
 #pragma unroll
-      for (int s8 = 0; s8 < 8; ++s8) {
+      for (int q = 0; q < 4; ++q) {
+        const int s8 = half * 4 + q;
         float a[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int s = s8 * 8 + e;
-          float x = row[s] * p.scale;
+          float x = row[q * 8 + e] * p.scale;
           if ((s >> 4) == I) x = (s <= r) ? Adg[r * 16 + (s & 15)] : 0.f;
           a[e] = x;
         }
