@@ -142,12 +142,18 @@ __device__ __forceinline__ float chunk_rev_cumsum(float x, int tid, float* tmp) 
 
 // Channel-wise gate tile: cumulative decay of the chunk in LOG2 units (G * log2 e, so that every decay
 // factor is one exp2 of a difference), 64 rows x 128 channels of fp32 in shared memory.  Element (row, col)
-// lives at gidx(row, col): the 16-byte pieces of a row (four channels) are XOR-ed with the low three row
-// bits.  "Thread d walks column d" touches 32 consecutive words of one row; "thread i reads row i" is done
-// with 16-byte loads (gt8 / gt4), which the swizzle spreads over all banks for eight neighbouring rows.
+// lives at gidx(row, col).  A row is 32 pieces of 16 bytes (four channels).  The even pieces - the first
+// halves of the 8-channel groups that match one 16-byte chunk of an fp16 operand tile - come first, then
+// the odd pieces, and within every 128-byte line the pieces are XOR-ed with the low three row bits (the odd
+// half with 4 more).  All three ways the kernels read the tile then run without bank replays:
+//   "lane = chunk of one row" (operand builds): 16 lanes read 16 neighbouring pieces, twice (gt8);
+//   "thread i reads row i" (epilogues): eight neighbouring rows land in eight different pieces of a line;
+//   "thread d walks column d": 32 channels are 4 + 4 pieces in two lines, on disjoint banks.
 constexpr float kLog2e = 1.4426950408889634f;
 __device__ __forceinline__ int gidx(int row, int col) {
-  return row * kK + ((((col >> 2) ^ row) & 7) << 2) + (col & ~31) + (col & 3);
+  const int p = col >> 2;
+  const int piece = ((p >> 1) + ((p & 1) << 4)) ^ ((row & 7) ^ ((p & 1) << 2));
+  return row * kK + (piece << 2) + (col & 3);
 }
 // four / eight consecutive gate values of one row (col0 a multiple of 4 / 8)
 __device__ __forceinline__ float4 gt4(const float* Gt, int row, int col0) {

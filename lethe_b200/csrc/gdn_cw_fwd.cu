@@ -189,7 +189,9 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   __syncwarp();
   // ---- diagonal blocks, exact: pairs (i, s) of one 16-row block, s <= i, one exp2 per pair and channel.
   // Thread (block, row pair j, piece c): rows 16 blk + j and 16 blk + 15 - j - together 17 pairs, the same
-  // count for every thread - over channels [16 c, 16 c + 16).  The row operands stay in registers while
+  // count for every thread - over channels [8 c, 8 c + 8) and [64 + 8 c, 64 + 8 c + 8): the eight pieces of a
+  // row read eight neighbouring 16-byte chunks of a tile row (and two whole lines of the gate tile), which
+  // keeps the shared-memory pipe - the limit of this phase - free of replays.  The row operands stay in registers while
   // the source rows stream by; the eight pieces of a pair sit in neighbouring lanes and are added by a
   // butterfly (fixed order: deterministic).
   {
@@ -197,17 +199,17 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     const int c = tid & 7, j = (tid >> 3) & 7, blk = tid >> 6;
     float qi[16], ki[16], gi[16];
     auto load_row = [&](int i) {
-      unpack8_f16(tile_ld_chunk(KQ, 64 + i, 2 * c, 128), qi);
-      unpack8_f16(tile_ld_chunk(KQ, 64 + i, 2 * c + 1, 128), qi + 8);
-      unpack8_f16(tile_ld_chunk(KQ, i, 2 * c, 128), ki);
-      unpack8_f16(tile_ld_chunk(KQ, i, 2 * c + 1, 128), ki + 8);
-      gt8(Gt, i, 16 * c, gi);
-      gt8(Gt, i, 16 * c + 8, gi + 8);
+      unpack8_f16(tile_ld_chunk(KQ, 64 + i, c, 128), qi);
+      unpack8_f16(tile_ld_chunk(KQ, 64 + i, c + 8, 128), qi + 8);
+      unpack8_f16(tile_ld_chunk(KQ, i, c, 128), ki);
+      unpack8_f16(tile_ld_chunk(KQ, i, c + 8, 128), ki + 8);
+      gt8(Gt, i, 8 * c, gi);
+      gt8(Gt, i, 64 + 8 * c, gi + 8);
       if (DELTA && full) {
         float bi[16];
-        const float* bp = p.bch + (tok0 + static_cast<size_t>(i) * p.H) * kK + 16 * c;
+        const float* bp = p.bch + (tok0 + static_cast<size_t>(i) * p.H) * kK + 8 * c;
         ld8(bp, bi);
-        ld8(bp + 8, bi + 8);
+        ld8(bp + 64, bi + 8);
 #pragma unroll
         for (int e = 0; e < 16; ++e) ki[e] *= bi[e];
       }
@@ -225,10 +227,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       const int ss = (t > j) ? t - j - 1 : t;
       const int s = blk * 16 + ss;
       float ks[16], gs[16];
-      unpack8_f16(tile_ld_chunk(KQ, s, 2 * c, 128), ks);
-      unpack8_f16(tile_ld_chunk(KQ, s, 2 * c + 1, 128), ks + 8);
-      gt8(Gt, s, 16 * c, gs);
-      gt8(Gt, s, 16 * c + 8, gs + 8);
+      unpack8_f16(tile_ld_chunk(KQ, s, c, 128), ks);
+      unpack8_f16(tile_ld_chunk(KQ, s, c + 8, 128), ks + 8);
+      gt8(Gt, s, 8 * c, gs);
+      gt8(Gt, s, 64 + 8 * c, gs + 8);
       float aa0 = 0.f, aa1 = 0.f, mm0 = 0.f, mm1 = 0.f;
 #pragma unroll
       for (int e = 0; e < 16; e += 2) {

@@ -166,13 +166,15 @@ def k2_fn(k: Tensor, v: Tensor, beta: Tensor, g2: Tensor, t_mat: Tensor, dw: Ten
 
 
 def _gate_tile_image(G: Tensor) -> Tensor:
-    """[Z, 64, 128] fp32 cumulative decay in log2 units -> the record image the kernels read: element
-    (row, col) at row * 128 + (col & ~31) + 4 * (((col >> 2) ^ row) & 7) + (col & 3) (the 16-byte pieces of
-    every 128-byte line XOR-ed with the low three row bits)."""
+    """[Z, 64, 128] fp32 cumulative decay in log2 units -> the record image the kernels read (``gidx`` of
+    ``csrc/gdn_common.cuh``): a row is 32 pieces of four channels, even pieces first, then the odd ones, and
+    within each 128-byte line the pieces are XOR-ed with the low three row bits (the odd half with 4 more)."""
     Z = G.shape[0]
     row = torch.arange(64, device=G.device)[:, None]
     col = torch.arange(128, device=G.device)[None, :]
-    dst = (row * 128 + (col & ~31) + ((((col >> 2) ^ row) & 7) << 2) + (col & 3)).reshape(-1)
+    p = col >> 2
+    piece = ((p >> 1) + ((p & 1) << 4)) ^ ((row & 7) ^ ((p & 1) << 2))
+    dst = (row * 128 + (piece << 2) + (col & 3)).reshape(-1)
     img = torch.empty(Z, 64 * 128, dtype=torch.float32, device=G.device)
     img[:, dst] = G.reshape(Z, -1)
     return img
