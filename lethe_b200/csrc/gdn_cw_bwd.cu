@@ -669,12 +669,35 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
         a1[j] = 0.f;
         a2[j] = 0.f;
       }
+      // ratio(i, s) = exp2(g_i - g_s) for the 136 pairs s <= i of the block with 54 exponentials instead of
+      // 136 (the special-function unit is what bounds this phase).  The 16 rows are cut into four groups of
+      // four; with a_G the first and l_G the last row of group G:
+      //   s == i                              1
+      //   s < i in the same group             exp2(g_i - g_s)                                       (24)
+      //   i in group A, s in an earlier B     exp2(g_i - g_aA) * exp2(g_aA - g_lB) * exp2(g_lB - g_s)   (12 + 6 + 12)
+      // Every factor is a decay between two rows that lie between s and i, so each is <= 1 and >= the
+      // ratio itself: nothing can overflow, and nothing underflows before the ratio does.
+      float eu[16], fd[16], br[6];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        eu[j] = (j & 3) ? exp2f(g[j] - g[j & ~3]) : 1.f;
+        fd[j] = ((j & 3) != 3) ? exp2f(g[j | 3] - g[j]) : 1.f;
+      }
+#pragma unroll
+      for (int A = 1; A < 4; ++A)
+#pragma unroll
+        for (int B = 0; B < A; ++B) br[A * (A - 1) / 2 + B] = exp2f(g[4 * A] - g[4 * B + 3]);
 #pragma unroll
       for (int ii = 0; ii < 16; ++ii) {
 #pragma unroll
         for (int ss = 0; ss <= ii; ++ss) {
+          const int A = ii >> 2, B = ss >> 2;
+          float r;
+          if (ss == ii) r = 1.f;
+          else if (A == B) r = exp2f(g[ii] - g[ss]);
+          else r = (eu[ii] * br[A * (A - 1) / 2 + B]) * fd[ss];
           const float cv = Cd[(blk * 16 + ii) * 16 + ss];
-          const float e = cv * exp2f(g[ii] - g[ss]);
+          const float e = cv * r;
           a1[ii] += e * kk[ss];
           a2[ss] += e * xv[ii];
         }
