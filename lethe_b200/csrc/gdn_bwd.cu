@@ -36,7 +36,6 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   float* Gs = fs;
   float* tmp = fs + 64;
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
-  float* Gt = fs + 128;     // channel-wise gate only
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
@@ -49,9 +48,10 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
     mbar_init(bar_mma, 1);
     fence_mbar_init();
     fence_proxy_async();
-    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u) + (CW ? 32768u : 0u));
-    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
-    for (int a = 0; a < 2; ++a) tma_load_4d(QG + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
+    mbar_expect_tx(bar_load, 16384u + V * 128u + (DELTA ? 32768u : 0u));
+    // scale * gamma * q: built below from q, or - channel-wise gate - read as the record the forward's prepare kernel left
+    if (CW) bulk_g2s(QG, p.saved + p.lay.qg + static_cast<size_t>(z) * 16384, 16384, bar_load);
+    else for (int a = 0; a < 2; ++a) tma_load_4d(QG + a * 8192, &mq, bar_load, a * 64, h, c * kC, b);
     for (int a = 0; a < V / 64; ++a) tma_load_4d(DO + a * 8192, &mdo, bar_load, a * 64, h, c * kC, b);
     if (DELTA) {
       bulk_g2s(Wt, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w, 16384, bar_load);
@@ -72,21 +72,16 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   if (tid < 64) Gs[tid] = G;
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 401);
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
-    const int r = idx >> 4, ch = idx & 15;
-    float x[8];
-    unpack8_in(tile_ld_chunk(QG, r, ch, 64), x, p.qk16);
-    if (CW) {
-      float gg[8];
-      gt8(Gt, r, ch * 8, gg);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] *= p.scale * exp2f(gg[i]);
-    } else {
+  if (!CW) {
+    for (int idx = tid; idx < 64 * 16; idx += 128) {
+      const int r = idx >> 4, ch = idx & 15;
+      float x[8];
+      unpack8_in(tile_ld_chunk(QG, r, ch, 64), x, p.qk16);
       const float sg = p.scale * __expf(Gs[r]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[i] *= sg;
+      tile_st_chunk(QG, r, ch, 64, pack8_f16(x));
     }
-    tile_st_chunk(QG, r, ch, 64, pack8_f16(x));
   }
   for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
@@ -496,7 +491,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
 // ---------------------------------------------------------------------------------------------
 template <int V, bool DELTA, bool CW>
 static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mdo, cudaStream_t st) {
-  const int smem = 16384 * 3 + V * 256 + 128 * 4 + (CW ? 32768 : 0) + 1024;
+  const int smem = 16384 * 3 + V * 256 + 128 * 4 + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_pre_kernel<V, DELTA, CW>, smem)) return kErrLaunch;
   bwd_pre_kernel<V, DELTA, CW><<<p.nbh * p.NT, 128, smem, st>>>(p, mq, mdo);

@@ -19,6 +19,9 @@
 //     GT    channel-wise gate only: 64 x 128 fp32, the cumulative decay of the chunk in log2 units in the
 //           swizzled shared-memory arrangement of gidx(), written once by prepare and bulk-loaded
 //           by every later kernel instead of being recomputed
+//     QG    channel-wise gate only: 16 KB image, 64 x 128: scale * gamma * q, the query operand of the output
+//           kernel and of the adjoint scan's input kernel (written by prepare, which has q and the gate in
+//           registers anyway, so that those two kernels need neither the 32 KB gate tile nor a conversion)
 //   scratch (backward only)
 //     RB    128 x V fp16 row-major: (q gamma)^T do - w^T (A^T do)
 //     DH    128 x V image: adjoint of the state leaving the chunk
@@ -44,7 +47,7 @@ constexpr int kK = 128;   // key dimension
 
 struct Layout {
   // byte offsets of the record arrays inside `saved` / `scratch`, and record sizes
-  size_t ta, w, u, p, r, hc, vn, ad, gt, saved_total;
+  size_t ta, w, u, p, r, hc, vn, ad, gt, qg, saved_total;
   size_t rb, dh, dv2, dw, dkb, dgb, da, dm, dqp, scratch_total;
   size_t sz_ta, sz_w, sz_u, sz_p, sz_r, sz_hc, sz_vn, sz_ad;
   size_t sz_rb, sz_dh, sz_dv2, sz_dw, sz_dkb, sz_dgb;
@@ -69,6 +72,7 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
   l.ad = o; o = align_up(o + Z * l.sz_ad, 1024);
   if (d.gate == LETHE_GATE_CHANNEL) {
     l.gt = o; o = align_up(o + Z * static_cast<size_t>(kC * kK * 4), 1024);
+    l.qg = o; o = align_up(o + Z * static_cast<size_t>(16384), 1024);
   }
   l.saved_total = o;
   l.sz_rb = kK * V * 2; l.sz_dh = kK * V * 2; l.sz_dv2 = kC * V * 2; l.sz_dw = 16384;

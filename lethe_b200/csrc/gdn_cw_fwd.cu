@@ -137,6 +137,11 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = qx[e] * ea[e];
     tile_st_chunk(LA, 64 + r, ch, 128, pack8_f16(y));
+    // scale * gamma * q for the output kernel and the adjoint scan's input kernel, staged in the [T; A] tile
+    // (not written before the first epilogue) and stored as a record
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = qx[e] * (p.scale * exp2f(gr[e]));
+    tile_st_chunk(TA, r, ch, 64, pack8_f16(y));
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = kx[e] * exp2f(gl[e] - gr[e]);
     tile_st_chunk(KD, r, ch, 64, pack8_f16(y));
@@ -185,6 +190,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     issue_product_led(leader, tmem + 16, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 16 * 128, 128, false}, 32, 128, 0u);
     issue_product_led(leader, tmem + 48, Tile{smem_u32(LA), 128, false}, Tile{smem_u32(KR) + 48 * 128, 128, false}, 48, 128, 0u);
     umma_commit_led(leader, bar_mma);
+    if (tid == 0) {
+      bulk_s2g(p.saved + p.lay.qg + static_cast<size_t>(z) * 16384, TA, 16384);
+      bulk_commit();
+    }
   }
   __syncwarp();
   // ---- diagonal blocks, exact: pairs (i, s) of one 16-row block, s <= i, one exp2 per pair and channel.
@@ -254,6 +263,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
       }
     }
   }
+  if (tid == 0) bulk_wait_read();      // the query record has left the [T; A] tile, which the epilogue now fills
   __syncthreads();
   wait_products(bar_mma, ph, ctl, 502);
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;

@@ -309,7 +309,6 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   float* Gs = fs;
   float* tmp = fs + 64;
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
-  float* Gt = fs + 128;     // channel-wise gate only: cumulative log decay [64][128]
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
@@ -326,10 +325,12 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
     mbar_init(bar_ht, 1);
     fence_mbar_init();
     fence_proxy_async();
-    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + 16384u + (CW ? 32768u : 0u));
-    if (CW) bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
+    mbar_expect_tx(bar_load, 16384u + (DELTA ? 16384u : V * 128u) + 16384u);
     for (int a = 0; a < 2; ++a) {
-      tma_load_4d(WQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
+      // the query operand: q from the user tensor (scaled below), or - channel-wise gate - the record of
+      // scale * gamma * q that the prepare kernel left (two 64-row atoms of 8 KB)
+      if (CW) bulk_g2s(WQ + a * 16384 + 8192, p.saved + p.lay.qg + static_cast<size_t>(z) * 16384 + a * 8192, 8192, bar_load);
+      else tma_load_4d(WQ + a * 16384 + 8192, &mq, bar_load, a * 64, h, c * kC, b);
       if (DELTA)
         bulk_g2s(WQ + a * 16384, p.saved + p.lay.w + static_cast<size_t>(z) * p.lay.sz_w + a * 8192, 8192, bar_load);
     }
@@ -370,19 +371,14 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   mbar_wait_warp(bar_load, 0, ctl, 211);
   for (int idx = tid; idx < 64 * 16; idx += 128) {
     const int r = idx >> 4, ch = idx & 15;
-    float x[8];
-    unpack8_in(tile_ld_chunk(WQ, 64 + r, ch, 128), x, p.qk16);
-    if (CW) {
-      float gg[8];
-      gt8(Gt, r, ch * 8, gg);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] *= p.scale * exp2f(gg[i]);
-    } else {
+    if (!CW) {
+      float x[8];
+      unpack8_in(tile_ld_chunk(WQ, 64 + r, ch, 128), x, p.qk16);
       const float sg = p.scale * __expf(Gs[r]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[i] *= sg;
+      tile_st_chunk(WQ, 64 + r, ch, 128, pack8_f16(x));
     }
-    tile_st_chunk(WQ, 64 + r, ch, 128, pack8_f16(x));
     if (!DELTA) tile_st_chunk(WQ, r, ch, 128, make_uint4(0, 0, 0, 0));
   }
   fence_proxy_async();
@@ -468,7 +464,7 @@ static int launch_prepare_t(const Problem& p, const CUtensorMap& mq, const CUten
 }
 template <int V, bool DELTA, bool CW>
 static int launch_output_t(const Problem& p, const CUtensorMap& mq, cudaStream_t st) {
-  const int smem = 32768 + V * 256 + 16384 + V * 128 + 128 * 4 + (CW ? 32768 : 0) + 1024;
+  const int smem = 32768 + V * 256 + 16384 + V * 128 + 128 * 4 + 1024;
   auto kern = output_kernel<V, DELTA, CW>;
   static SmemAttr attr;
   if (attr.set(kern, smem)) return kErrLaunch;
