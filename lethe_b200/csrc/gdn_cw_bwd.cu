@@ -63,18 +63,8 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     mbar_init(bar_mma, 1);
     mbar_init(bar_dh, 1);
     fence_mbar_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(&cs->tmem_slot, 512);
-    tmem_relinquish();
-  }
-  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = cs->tmem_slot;
-  const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
-  if (tid == 0) {
+    fence_proxy_async();
+    // every load that does not depend on the kernel just before this one is requested at once
     mbar_expect_tx(bar_load, 16384u + 16384u + V * 128u + 16384u + V * 128u + V * 256u + 32768u);
     bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
     for (int a = 0; a < 2; ++a) {
@@ -87,6 +77,16 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
     bulk_g2s(Ht, p.saved + p.lay.hc + static_cast<size_t>(z + bh) * p.lay.sz_hc, V * 256, bar_load);
     // (dh, written by the adjoint scan just before this kernel, is loaded after griddep_wait)
   }
+  if (warp == 0) {
+    tmem_alloc(&cs->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = cs->tmem_slot;
+  const uint32_t cA = tmem, cB = tmem + 128, cC = tmem + 256, cD = tmem + 320;
   __syncthreads();
   // the loads above fetch inputs and records older than the adjoint scan; once it is complete (at once,
   // except for the CTAs that started early) its dh image is fetched too
@@ -302,6 +302,15 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     mbar_init(bar_load, 1);
     mbar_init(bar_mma, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    // every load that does not depend on the kernel just before this one is requested at once
+    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u + 32768u);
+    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
+    for (int a = 0; a < 2; ++a) tma_load_4d(KB + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
+    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
+    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
+    bulk_g2s(DWt, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, 16384, bar_load);
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, 512);
@@ -320,15 +329,6 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
   const uint32_t c1 = tmem + 64, c2 = tmem + 128, c3 = tmem + 192, c4 = tmem + 256;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 16384u + V * 128u + 16384u + V * 128u + 16384u + 32768u);
-    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
-    for (int a = 0; a < 2; ++a) tma_load_4d(KB + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-    for (int a = 0; a < V / 64; ++a) tma_load_4d(VT + a * 8192, &mv, bar_load, a * 64, h, c * kC, b);
-    bulk_g2s(TAt, p.saved + p.lay.ta + static_cast<size_t>(z) * p.lay.sz_ta, 16384, bar_load);
-    bulk_g2s(DV2t, p.scratch + p.lay.dv2 + static_cast<size_t>(z) * p.lay.sz_dv2, V * 128, bar_load);
-    bulk_g2s(DWt, p.scratch + p.lay.dw + static_cast<size_t>(z) * p.lay.sz_dw, 16384, bar_load);
-  }
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 611);
   for (int idx = tid; idx < 64 * 16; idx += 128) {
@@ -544,6 +544,14 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
     mbar_init(bar_c, 1);
     mbar_init(bar_rec, 1);
     fence_mbar_init();
+    fence_proxy_async();
+    // every load that does not depend on the kernel just before this one is requested at once
+    mbar_expect_tx(bar_load, 32768u + 32768u);
+    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
+    for (int a = 0; a < 2; ++a) {
+      tma_load_4d(KX + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
+      tma_load_4d(KX + a * 16384 + 8192, MODE == 0 ? &mq : &mk, bar_load, a * 64, h, c * kC, b);
+    }
   }
   if (warp == 0) {
     tmem_alloc(&cs->tmem_slot, 256);
@@ -556,14 +564,6 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 32768u + 32768u);
-    bulk_g2s(Gt, p.saved + p.lay.gt + static_cast<size_t>(z) * (kC * kK * 4), 32768, bar_load);
-    for (int a = 0; a < 2; ++a) {
-      tma_load_4d(KX + a * 16384, &mk, bar_load, a * 64, h, c * kC, b);
-      tma_load_4d(KX + a * 16384 + 8192, MODE == 0 ? &mq : &mk, bar_load, a * 64, h, c * kC, b);
-    }
-  }
   __syncthreads();
   // the loads above fetch inputs and the gate record; C and the fp32 records come from the kernels just
   // before this one
