@@ -325,6 +325,101 @@ def io_bytes(kernel: str, Z: int, V: int, delta, gate: str) -> int:
     return per * Z
 
 
+def pcie_probe(dev, world, mbytes: int = 128, reps: int = 4):
+    """Host link of this rank while every rank uses its own at the same time: GB/s of pinned-host -> device
+    copies, of device -> pinned-host copies, and of both at once (what the end-to-end pipeline does).  Returns
+    the slowest rank's figures and the sum over the ranks - the host's aggregate, which is what bounds the
+    end-to-end number when several GPUs of one host copy together."""
+    import torch.distributed as dist
+    n = mbytes << 20
+    hbuf = torch.empty(n, dtype=torch.uint8).pin_memory()
+    hbuf2 = torch.empty(n, dtype=torch.uint8).pin_memory()
+    dbuf = torch.empty(n, dtype=torch.uint8, device=dev)
+    dbuf2 = torch.empty(n, dtype=torch.uint8, device=dev)
+    s1, s2 = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def run(which):
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        s1.wait_event(a)
+        s2.wait_event(a)
+        for _ in range(reps):
+            if which in ("h2d", "both"):
+                with torch.cuda.stream(s1):
+                    dbuf.copy_(hbuf, non_blocking=True)
+            if which in ("d2h", "both"):
+                with torch.cuda.stream(s2):
+                    hbuf2.copy_(dbuf2, non_blocking=True)
+        torch.cuda.current_stream(dev).wait_stream(s1)
+        torch.cuda.current_stream(dev).wait_stream(s2)
+        b.record()
+        torch.cuda.synchronize(dev)
+        return reps * n / (a.elapsed_time(b) * 1e-3) / 1e9        # GB/s per direction
+
+    run("both")                                                     # warm
+    out = {}
+    for which in ("h2d", "d2h", "both"):
+        g = torch.tensor([run(which)], device=dev, dtype=torch.float64)
+        lo, tot = g.clone(), g.clone()
+        if world > 1:
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        out[which] = {"slowest_rank_gbs": float(lo), "all_ranks_gbs": float(tot)}
+    out["note"] = (f"{mbytes} MiB pinned copies, all {world} ranks at once; 'both' is GB/s per direction with the two "
+                   "directions running together")
+    return out
+
+
+def aux_main(args):
+    """Timing of the two kernels on either side of the path that the step does not contain: the L2
+    normalisation of q, k with its VJP (one launch each way) and the one-token decode step.  Both are
+    HBM-bound element-wise kernels; the line reports achieved GB/s against the measured copy bandwidth."""
+    from lethe_b200 import ops
+    dev = torch.device("cuda", 0)
+    hbm = peaks()[0]
+    B, L, H, K, V = 2, 8192, 32, 128, 128            # the q, k of one GPU's share of configuration 4a
+    gen = torch.Generator().manual_seed(0)
+    q = torch.randn(B, L, H, K, generator=gen).bfloat16().to(dev)
+    k = torch.randn(B, L, H, K, generator=gen).bfloat16().to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in evs:
+            flush.zero_()
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / n
+
+    qn, kn = ops.l2norm_qk_raw(q, k)
+    rows = q.numel() // K
+    t_f = timed(lambda: ops.l2norm_qk_raw(q, k))
+    t_b = timed(lambda: ops.l2norm_qk_vjp_raw(q, k, qn, kn))
+    by_f, by_b = 2 * rows * K * (2 + 2), 2 * rows * K * (2 + 2 + 2)          # q and k: read x (+ dy), write y / dx
+    Bd, Hd = 64, 32
+    state = torch.randn(Bd, Hd, K, V, generator=gen).to(dev)
+    q1 = torch.randn(Bd, Hd, K, generator=gen).bfloat16().to(dev)
+    v1 = torch.randn(Bd, Hd, V, generator=gen).bfloat16().to(dev)
+    g1 = -torch.rand(Bd, Hd, generator=gen).to(dev)
+    b1 = torch.rand(Bd, Hd, generator=gen).to(dev)
+    t_d = timed(lambda: ops.gdn_decode_step(q1, q1, v1, g1, b1, state))
+    by_d = 2 * state.numel() * 4                                                # the state is read and written once
+    out = {"impl": "aux", "l2norm_qk": {"ms": t_f, "GB/s": by_f / t_f / 1e6, "frac_of_hbm": by_f / t_f / 1e6 / hbm,
+                                        "rows_per_tensor": rows},
+           "l2norm_qk_vjp": {"ms": t_b, "GB/s": by_b / t_b / 1e6, "frac_of_hbm": by_b / t_b / 1e6 / hbm},
+           "decode_step": {"ms": t_d, "GB/s": by_d / t_d / 1e6, "frac_of_hbm": by_d / t_d / 1e6 / hbm,
+                           "B": Bd, "H": Hd, "state_MB": by_d / 2e6},
+           "peak_gbs": hbm, "l2": "flushed between launches (256 MiB write)"}
+    print(json.dumps(out))
+
+
 def fla_main(args, B, L, H, K, V, gate, delta, config):
     """Extra comparator row, not the reference arm and not part of this package: the flash-linear-attention
     Triton kernels (a third-party library the reference itself times against) on the same workload, same
@@ -415,7 +510,12 @@ def sp_main(args, rank, world, dev, B, L, H, K, V, gate, delta, config):
     ops.check_status(sp.buf.status)
     if rank == 0:
         config = dict(config, mode="sequence parallel", L_per_gpu=Ll, l2="inputs and records exceed L2")
+        hbm, _tfb, tfs, _which = peaks()
+        m = path_model(args.workload)
+        byt, flop = m["fwd"][1] + m["bwd"][1], m["fwd"][0] + m["bwd"][0]
         print(json.dumps({"metric": METRIC, "value": B * L / (float(ms) * 1e-3), "unit": "tokens/s",
+                          "hbm_frac": byt / (float(ms) * 1e-3) / 1e9 / (hbm * world),
+                          "tensor_frac": flop / (float(ms) * 1e-3) / 1e12 / (tfs * world),
                           "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                           "ms_per_step": float(ms), "higher_is_better": True, "scaling": "strong",
                           "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate (bf16 in/out)",
@@ -429,8 +529,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fla"],
-                    help="reference: the CPU port of the reference path; fla: third-party comparator (see fla_main)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fla", "aux"],
+                    help="reference: the reference's own CPU path (oracle/_ref) or its CPU port; fla: third-party "
+                         "comparator (see fla_main); aux: the L2-normalisation and decode-step kernels")
     ap.add_argument("--groups", type=int, default=1,
                     help="cut the (batch, head) pairs into this many ranges that run as concurrent kernel chains "
                          "inside the step graph (helps when the scans leave SMs idle: a few % on the larger workloads)")
@@ -453,6 +554,10 @@ def main():
     if args.impl == "fla":
         if rank == 0:
             fla_main(args, B, L, H, K, V, gate, delta, config)
+        return
+    if args.impl == "aux":
+        if rank == 0:
+            aux_main(args)
         return
     if args.impl == "reference":
         if rank != 0:
@@ -600,6 +705,7 @@ def main():
             single_host[n].copy_(t, non_blocking=True)
 
     e2e_single_ms = timed(e2e_single, 3, 3)
+    pcie = pcie_probe(dev, world)
 
     # the call a training loop makes: the autograd op on tensors that already live on the device
     dev_leaves = {n: (d[n].clone().requires_grad_(True) if n in d else None) for n in ("q", "k", "v", "g", "beta", "h0")}
@@ -647,7 +753,11 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "lethe_b200.host.HostPipeline (copy-in, kernels and copy-out of consecutive steps "
                            "overlap)", "steps": e2e_steps,
-                    "single_step_ms": e2e_single_ms, "single_step_api": "lethe_b200.ops.gdn_chunk + autograd"},
+                    "single_step_ms": e2e_single_ms, "single_step_api": "lethe_b200.ops.gdn_chunk + autograd",
+                    # the pipelined step moves h2d + d2h bytes per step over the host link in both directions at
+                    # once: its floor is bytes / the measured link rate with every rank copying
+                    "host_link": pcie,
+                    "host_link_floor_ms": max(h2d, d2h) / (pcie["both"]["slowest_rank_gbs"] * 1e9) * 1e3},
             "autograd_op_ms": op_ms,
             "gpu_launches": args.steps * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
             "clocks": clocks,
