@@ -103,6 +103,15 @@ typedef struct LetheGdnArgs {
   /* once, as the reference does when it stages operands (gdn2_bwd_dhu_l3.py:477-479), instead of twice.     */
   /* v, o, d_o, dv stay bf16.                                                                               */
   uint32_t qk_f16;
+  /* The chunks (64-token blocks) of every sequence this call works on: [c_begin, c_begin + c_count); c_count = 0  */
+  /* means all L / 64 of them.  The chunk-parallel kernels simply cover that range.  The state scans carry    */
+  /* their fp32 state from one range to the next through the workspaces, so the forward ranges must be run    */
+  /* in ascending order and the backward ranges in descending order (kernel_mask selects the kernels): a      */
+  /* call cut into ranges gives bit-identical results and lets a caller overlap the chunk-parallel kernels    */
+  /* of one range with the serial scan of the next on another stream (lethe_b200.ops.GdnStepGraph does).      */
+  /* No counterpart in the reference.                                                                          */
+  uint32_t c_begin;
+  uint32_t c_count;
 } LetheGdnArgs;
 
 /* Bytes of the forward->backward workspace / of the backward scratch for these sizes (0 = bad dims). */

@@ -73,6 +73,15 @@ static int fill_problem(const LetheGdnArgs* a, Problem* p, bool backward) {
     p->bh0 = static_cast<int>(a->bh_begin);
     p->nbh = static_cast<int>(a->bh_count);
   }
+  if (a->c_count == 0) {
+    if (a->c_begin != 0) return kErrDims;
+    p->c0 = 0;
+    p->cn = p->NT;
+  } else {
+    if (static_cast<uint64_t>(a->c_begin) + a->c_count > static_cast<uint64_t>(p->NT)) return kErrDims;
+    p->c0 = static_cast<int>(a->c_begin);
+    p->cn = static_cast<int>(a->c_count);
+  }
   p->scale = a->scale;
   p->qk16 = a->qk_f16 ? 1 : 0;
   p->q = static_cast<const __nv_bfloat16*>(a->q);

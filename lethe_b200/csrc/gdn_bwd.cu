@@ -38,7 +38,7 @@ bwd_pre_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const __
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -191,7 +191,7 @@ bwd_stageb_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves
   // take the same rows and split the columns of every epilogue.
   const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -494,7 +494,7 @@ static int launch_pre_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
   const int smem = 16384 * 3 + V * 256 + 128 * 4 + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_pre_kernel<V, DELTA, CW>, smem)) return kErrLaunch;
-  bwd_pre_kernel<V, DELTA, CW><<<p.nbh * p.NT, 128, smem, st>>>(p, mq, mdo);
+  bwd_pre_kernel<V, DELTA, CW><<<p.nbh * p.cn, 128, smem, st>>>(p, mq, mdo);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V, bool DELTA>
@@ -504,7 +504,7 @@ static int launch_stageb_t(const Problem& p, const CUtensorMap& mq, const CUtens
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_stageb_kernel<V, DELTA>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_stageb_kernel<V, DELTA>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk, mdo,
+  if (launch_dependent(bwd_stageb_kernel<V, DELTA>, dim3(p.nbh * p.cn), dim3(256), smem, st, p, mq, mk, mdo,
                        mo.dq, mo.dk) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -42,7 +42,7 @@ bwd_wy2_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __
   // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves take
   // the same rows and split the columns of every epilogue; per-row sums are combined through `prt`.
   const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -353,7 +353,7 @@ static int launch_wy2_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
   const int smem = 32768 + 16384 + 16384 + 8192 + 8192 + V * 256 + 8192 + 904 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_wy2_kernel<V>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_wy2_kernel<V>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mk, mv, mo.dk, mo.dv) !=
+  if (launch_dependent(bwd_wy2_kernel<V>, dim3(p.nbh * p.cn), dim3(256), smem, st, p, mk, mv, mo.dk, mo.dv) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -47,8 +47,8 @@ constexpr int kK = 128;   // key dimension
 
 struct Layout {
   // byte offsets of the record arrays inside `saved` / `scratch`, and record sizes
-  size_t ta, w, u, p, r, hc, vn, ad, gt, qg, saved_total;
-  size_t rb, dh, dv2, dw, dkb, dgb, da, dm, dqp, scratch_total;
+  size_t ta, w, u, p, r, hc, vn, ad, gt, qg, carry_f, saved_total;
+  size_t rb, dh, dv2, dw, dkb, dgb, da, dm, dqp, carry_b, scratch_total;
   size_t sz_ta, sz_w, sz_u, sz_p, sz_r, sz_hc, sz_vn, sz_ad;
   size_t sz_rb, sz_dh, sz_dv2, sz_dw, sz_dkb, sz_dgb;
 };
@@ -74,6 +74,8 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
     l.gt = o; o = align_up(o + Z * static_cast<size_t>(kC * kK * 4), 1024);
     l.qg = o; o = align_up(o + Z * static_cast<size_t>(16384), 1024);
   }
+  // fp32 master state handed from one chunk-range call of the forward scan to the next ([B, H, K, V])
+  l.carry_f = o; o = align_up(o + static_cast<size_t>(d.B) * d.H * kK * V * 4, 1024);
   l.saved_total = o;
   l.sz_rb = kK * V * 2; l.sz_dh = kK * V * 2; l.sz_dv2 = kC * V * 2; l.sz_dw = 16384;
   l.sz_dkb = kC * kK * 4; l.sz_dgb = (d.gate == LETHE_GATE_CHANNEL ? kC * kK : kC) * 4;
@@ -89,6 +91,7 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
     l.dm = o;  o = align_up(o + Z * 8192, 1024);
     l.dqp = o; o = align_up(o + Z * static_cast<size_t>(kC * kK * 4), 1024);
   }
+  l.carry_b = o; o = align_up(o + static_cast<size_t>(d.B) * d.H * kK * V * 4, 1024);   // the same for the adjoint scan
   l.scratch_total = o;
   return l;
 }
@@ -97,6 +100,7 @@ __host__ inline Layout make_layout(const LetheGdnDims& d) {
 struct Problem {
   int B, H, L, NT, V, gate, delta;
   int bh0, nbh;      // the (batch, head) pairs this call works on: [bh0, bh0 + nbh) of the B * H pairs
+  int c0, cn;        // the chunks of every pair this call works on: [c0, c0 + cn) of the NT chunks
   int qk16;          // non-zero: q, k, dq, dk hold fp16 instead of bf16
   float scale;
   const __nv_bfloat16 *q, *k, *v, *d_o;

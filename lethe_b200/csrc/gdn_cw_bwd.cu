@@ -52,7 +52,7 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
   float* DDE = reinterpret_cast<float*>(Ht);   // [64][128] fp32 exchange tile, after the products are done
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -293,7 +293,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 64);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -529,7 +529,7 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   float* EX2 = reinterpret_cast<float*>(XE);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -837,7 +837,7 @@ static int launch_sb1_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_cw_sb1_kernel<V, DELTA>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_cw_sb1_kernel<V, DELTA>, dim3(p.nbh * p.NT), dim3(256), smem, st, p, mq, mk, mdo) !=
+  if (launch_dependent(bwd_cw_sb1_kernel<V, DELTA>, dim3(p.nbh * p.cn), dim3(256), smem, st, p, mq, mk, mdo) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
@@ -847,7 +847,7 @@ static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorM
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_cw_wy1_kernel<V>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_cw_wy1_kernel<V>, dim3(p.nbh * p.NT), dim3(128), smem, st, p, mk, mv) != cudaSuccess)
+  if (launch_dependent(bwd_cw_wy1_kernel<V>, dim3(p.nbh * p.cn), dim3(128), smem, st, p, mk, mv) != cudaSuccess)
     return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
@@ -856,7 +856,7 @@ static int launch_pair_t(const Problem& p, const CUtensorMap& mq, const CUtensor
   const int smem = 32768 * 3 + 8192 * 8 + 32768 + 1344 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_cw_pair_kernel<MODE, FINAL_G>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_cw_pair_kernel<MODE, FINAL_G>, dim3(p.nbh * p.NT), dim3(kPairThreads), smem, st, p, mq, mk) !=
+  if (launch_dependent(bwd_cw_pair_kernel<MODE, FINAL_G>, dim3(p.nbh * p.cn), dim3(kPairThreads), smem, st, p, mq, mk) !=
       cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -46,7 +46,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   unsigned char* WU = KQ;
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -423,7 +423,7 @@ static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CU
   auto kern = prepare_cw_kernel<V, DELTA>;
   static SmemAttr attr;
   if (attr.set(kern, smem)) return kErrLaunch;
-  kern<<<p.nbh * p.NT, kPrepCwThreads, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.nbh * p.cn, kPrepCwThreads, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -48,7 +48,7 @@ prepare_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   // Threads 0-127 and 128-255 reach the same TMEM lanes (lane quadrant = warp & 3): the two halves take
   // the same rows and split the columns of every epilogue.
   const int tid = threadIdx.x, warp = tid >> 5, tq = tid & 127, half = tid >> 7;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_load = &cs->bar[0];
   uint64_t* bar_mma = &cs->bar[1];
@@ -311,7 +311,7 @@ output_kernel(const Problem p, const __grid_constant__ CUtensorMap mq) {
   CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 72);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.x + p.bh0 * p.NT, bh = z / p.NT, c = z % p.NT, b = bh / p.H, h = bh % p.H;
+  const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
   CtaCtl ctl{p.status, &cs->abort_flag};
   const unsigned char* Ug = p.saved + p.lay.u + static_cast<size_t>(z) * p.lay.sz_u;
   uint64_t* bar_load = &cs->bar[0];
@@ -459,7 +459,7 @@ static int launch_prepare_t(const Problem& p, const CUtensorMap& mq, const CUten
   auto kern = prepare_kernel<V, DELTA>;
   static SmemAttr attr;
   if (attr.set(kern, smem)) return kErrLaunch;
-  kern<<<p.nbh * p.NT, 256, smem, st>>>(p, mq, mk, mv);
+  kern<<<p.nbh * p.cn, 256, smem, st>>>(p, mq, mk, mv);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 template <int V, bool DELTA, bool CW>
@@ -468,7 +468,7 @@ static int launch_output_t(const Problem& p, const CUtensorMap& mq, cudaStream_t
   auto kern = output_kernel<V, DELTA, CW>;
   static SmemAttr attr;
   if (attr.set(kern, smem)) return kErrLaunch;
-  if (launch_dependent(kern, dim3(p.nbh * p.NT), dim3(128), smem, st, p, mq) != cudaSuccess) return kErrLaunch;
+  if (launch_dependent(kern, dim3(p.nbh * p.cn), dim3(128), smem, st, p, mq) != cudaSuccess) return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -42,7 +42,13 @@ scan_kernel(const Problem p) {
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int v0 = blockIdx.x * kVs, bh = blockIdx.y + p.bh0;
-  const int V = p.V, NT = p.NT;
+  // This launch walks the chunks [c0, c0 + cn) of every pair (all NT of them in an ordinary call), forward in
+  // chunk order, the adjoint in reverse.  A launch that does not start at the sequence's first (adjoint: last)
+  // chunk takes its fp32 state from the carry buffer the launch before it left, and one that does not end at
+  // the other end leaves its state there: a scan cut into chunk ranges is bit-identical to one launch.
+  const int V = p.V, NT = p.NT, n = p.cn;
+  const bool seg_first = ADJOINT ? (p.c0 + p.cn == NT) : (p.c0 == 0);
+  const bool seg_last = ADJOINT ? (p.c0 == 0) : (p.c0 + p.cn == NT);
   CtaCtl ctl{p.status, &cs->abort_flag};
   uint64_t* bar_full = &cs->bar[0];                 // [kStages] P stage loaded
   uint64_t* bar_free = &cs->bar[kStages];           // [kStages] the products reading the stage are done
@@ -65,7 +71,7 @@ scan_kernel(const Problem p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = cs->tmem_slot;
-  auto chunk_of = [&](int it) { return ADJOINT ? NT - 1 - it : it; };
+  auto chunk_of = [&](int it) { return ADJOINT ? p.c0 + n - 1 - it : p.c0 + it; };
   // The kernel before this one wrote R (forward) or Rb (adjoint); P comes from the same kernel in the
   // forward and from the forward call in the adjoint, whose producer may start at once.
   if (!(ADJOINT && warp == 4)) {
@@ -77,7 +83,7 @@ scan_kernel(const Problem p) {
     // ---- producer: keeps the ring of P stages full
     if (tid == 128) {
       const unsigned char* Pg = p.saved + p.lay.p;
-      for (int it = 0; it < NT; ++it) {
+      for (int it = 0; it < n; ++it) {
         const int st = it % kStages;
         if (it >= kStages) mbar_wait(&bar_free[st], static_cast<uint32_t>(((it / kStages) - 1) & 1), ctl, 303);
         mbar_expect_tx(&bar_full[st], 32768u);
@@ -95,7 +101,7 @@ scan_kernel(const Problem p) {
     const uint64_t b_desc0 = make_desc_sw32(smem_u32(XB), 16u, 256u);
     const uint32_t idesc = make_idesc(128, kVs, ADJOINT, true);
     const uint32_t acc = tmem + static_cast<uint32_t>(m * kVs);
-    for (int it = 0; it < NT; ++it) {
+    for (int it = 0; it < n; ++it) {
       const int st = it % kStages;
       mbar_wait_warp(&bar_full[st], static_cast<uint32_t>((it / kStages) & 1), ctl, 301);
       step_sync();
@@ -124,9 +130,10 @@ scan_kernel(const Problem p) {
     // R / Rb records are [V / 16 column blocks][128 rows][16 columns]: this CTA's block, this thread's row
     const size_t rofs = (static_cast<size_t>(blockIdx.x) * kK + tid) * kVs;
 
+    float* carry = reinterpret_cast<float*>(ADJOINT ? p.scratch + p.lay.carry_b : p.saved + p.lay.carry_f);
     float x[kVs];
     {
-      const float* x0 = ADJOINT ? p.dhT : p.h0;
+      const float* x0 = seg_first ? (ADJOINT ? p.dhT : p.h0) : carry;
 #pragma unroll
       for (int j = 0; j < kVs; ++j) x[j] = x0 ? x0[(static_cast<size_t>(bh) * kK + tid) * V + v0 + j] : 0.f;
     }
@@ -138,7 +145,7 @@ scan_kernel(const Problem p) {
     }
     float a_next = ADg[(static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid];
 
-    for (int it = 0; it < NT; ++it) {
+    for (int it = 0; it < n; ++it) {
       const size_t z = static_cast<size_t>(bh) * NT + chunk_of(it);
       // critical path: the state as a tensor-core operand
       {
@@ -156,7 +163,7 @@ scan_kernel(const Problem p) {
       unpack8_f16(rnext[1], rr + 8);
 #pragma unroll
       for (int j = 0; j < kVs; ++j) rr[j] = fmaf(a, x[j], rr[j]);
-      if (it + 1 < NT) {
+      if (it + 1 < n) {
         const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
         const __half* r = Rg + zn * kK * V + rofs;
         rnext[0] = *reinterpret_cast<const uint4*>(r);
@@ -183,12 +190,12 @@ scan_kernel(const Problem p) {
         x[j] = rr[j] - s;
       }
     }
-    if (!ADJOINT) {   // the final state as one more record
+    if (!ADJOINT && seg_last) {   // the final state as one more record
       unsigned char* rec = Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx;
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
       *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
     }
-    float* xT = ADJOINT ? p.dh0 : p.hT;
+    float* xT = seg_last ? (ADJOINT ? p.dh0 : p.hT) : carry;
     if (xT) {
 #pragma unroll
       for (int j = 0; j < kVs; j += 4)
@@ -213,7 +220,10 @@ __global__ void __launch_bounds__(256)
 scan_nodelta_kernel(const Problem p) {
   const int tid = threadIdx.x;
   const int atom = blockIdx.x >> 2, d = (blockIdx.x & 3) * 32 + (tid >> 3), c8 = tid & 7;
-  const int bh = blockIdx.y + p.bh0, V = p.V, NT = p.NT;
+  const int bh = blockIdx.y + p.bh0, V = p.V, NT = p.NT, n = p.cn;
+  const bool seg_first = ADJOINT ? (p.c0 + p.cn == NT) : (p.c0 == 0);        // chunk ranges as in scan_kernel
+  const bool seg_last = ADJOINT ? (p.c0 == 0) : (p.c0 + p.cn == NT);
+  float* carry = reinterpret_cast<float*>(ADJOINT ? p.scratch + p.lay.carry_b : p.saved + p.lay.carry_f);
   const int col0 = atom * 64 + c8 * 8;
   griddep_wait();
   griddep_launch();
@@ -222,21 +232,21 @@ scan_nodelta_kernel(const Problem p) {
   unsigned char* Xg = ADJOINT ? p.scratch + p.lay.dh : p.saved + p.lay.hc;
   const size_t szx = p.lay.sz_hc;
   const uint32_t off = sw128_chunk(d, atom * 8 + c8, 128);     // this thread's piece inside any 128-row image
-  auto chunk_of = [&](int it) { return ADJOINT ? NT - 1 - it : it; };
+  auto chunk_of = [&](int it) { return ADJOINT ? p.c0 + n - 1 - it : p.c0 + it; };
 
   float x[8];
   {
-    const float* x0 = ADJOINT ? p.dhT : p.h0;
+    const float* x0 = seg_first ? (ADJOINT ? p.dhT : p.h0) : carry;
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] = x0 ? x0[(static_cast<size_t>(bh) * kK + d) * V + col0 + j] : 0.f;
   }
   constexpr int kBatch = 8;
-  for (int it0 = 0; it0 < NT; it0 += kBatch) {
+  for (int it0 = 0; it0 < n; it0 += kBatch) {
     uint4 rb[kBatch];
     float ab[kBatch];
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
-      if (it0 + j < NT) {
+      if (it0 + j < n) {
         const size_t zj = static_cast<size_t>(bh) * NT + chunk_of(it0 + j);
         rb[j] = *reinterpret_cast<const uint4*>(Rg + zj * p.lay.sz_r + off);
         ab[j] = ADg[zj * kK + d];
@@ -244,7 +254,7 @@ scan_nodelta_kernel(const Problem p) {
     }
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
-      if (it0 + j < NT) {
+      if (it0 + j < n) {
         const size_t zj = static_cast<size_t>(bh) * NT + chunk_of(it0 + j);
         *reinterpret_cast<uint4*>(Xg + (ADJOINT ? zj : zj + bh) * szx + off) = pack8_f16(x);
         float rr[8];
@@ -254,9 +264,9 @@ scan_nodelta_kernel(const Problem p) {
       }
     }
   }
-  if (!ADJOINT)   // the final state as one more record
+  if (!ADJOINT && seg_last)   // the final state as one more record
     *reinterpret_cast<uint4*>(Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx + off) = pack8_f16(x);
-  float* xT = ADJOINT ? p.dh0 : p.hT;
+  float* xT = seg_last ? (ADJOINT ? p.dh0 : p.hT) : carry;
   if (xT) {
     float* dst = xT + (static_cast<size_t>(bh) * kK + d) * V + col0;
     *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);

@@ -44,6 +44,7 @@ class _Args(ctypes.Structure):
         ("b_gate", ctypes.c_void_p), ("w_gate", ctypes.c_void_p),
         ("db_gate", ctypes.c_void_p), ("dw_gate", ctypes.c_void_p),
         ("bh_begin", ctypes.c_uint32), ("bh_count", ctypes.c_uint32), ("qk_f16", ctypes.c_uint32),
+        ("c_begin", ctypes.c_uint32), ("c_count", ctypes.c_uint32),
     ]
 
 
@@ -167,20 +168,24 @@ class GdnBuffers:
 
 
 def forward_into(buf: GdnBuffers, q, k, v, g, beta, h0, scale: float, kernel_mask: int = 0, *,
-                 b_gate=None, w_gate=None, bh_range: tuple[int, int] = (0, 0)) -> None:
+                 b_gate=None, w_gate=None, bh_range: tuple[int, int] = (0, 0),
+                 c_range: tuple[int, int] = (0, 0)) -> None:
     """Enqueue the forward kernels on the current stream; results land in ``buf.o`` / ``buf.hT``.
     ``b_gate [B,L,H,K]`` / ``w_gate [B,L,H,V]`` (fp32) replace ``beta`` for buffers made with ``delta=2``.
-    ``bh_range = (begin, count)`` restricts the call to those (batch, head) pairs (count 0: all)."""
+    ``bh_range = (begin, count)`` restricts the call to those (batch, head) pairs (count 0: all),
+    ``c_range = (begin, count)`` to those 64-token chunks of every sequence (the scans carry their state from
+    one range to the next: forward ranges in ascending order)."""
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
               h0=_ptr(h0), o=_ptr(buf.o), hT=_ptr(buf.hT), saved=_ptr(buf.saved),
               saved_bytes=buf.saved.numel(), status=_ptr(buf.status), kernel_mask=kernel_mask,
               b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), bh_begin=bh_range[0], bh_count=bh_range[1],
-              qk_f16=int(q.dtype == torch.float16))
+              qk_f16=int(q.dtype == torch.float16), c_begin=c_range[0], c_count=c_range[1])
     _check(native.lib().lethe_gdn_forward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
 def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, kernel_mask: int = 0, *,
-                  b_gate=None, w_gate=None, bh_range: tuple[int, int] = (0, 0)) -> None:
+                  b_gate=None, w_gate=None, bh_range: tuple[int, int] = (0, 0),
+                  c_range: tuple[int, int] = (0, 0)) -> None:
     """Enqueue the backward kernels; gradients land in ``buf.dq`` ... ``buf.dh0`` (``buf.db`` / ``buf.dw``
     for the per-channel gates of buffers made with ``delta=2``)."""
     a = _Args(dims=buf.dims, scale=scale, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), beta=_ptr(beta),
@@ -189,7 +194,8 @@ def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, 
               saved_bytes=buf.saved.numel(), scratch=_ptr(buf.scratch), scratch_bytes=buf.scratch.numel(),
               status=_ptr(buf.status), kernel_mask=kernel_mask, dbeta_write=_ptr(buf.dbeta_write),
               b_gate=_ptr(b_gate), w_gate=_ptr(w_gate), db_gate=_ptr(buf.db), dw_gate=_ptr(buf.dw),
-              bh_begin=bh_range[0], bh_count=bh_range[1], qk_f16=int(q.dtype == torch.float16))
+              bh_begin=bh_range[0], bh_count=bh_range[1], qk_f16=int(q.dtype == torch.float16),
+              c_begin=c_range[0], c_count=c_range[1])
     if buf.dq.dtype != q.dtype:
         raise GdnError("lethe_gdn: dq / dk buffers must have the type of q / k (make GdnBuffers with qk_dtype=)")
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
@@ -199,34 +205,108 @@ class GdnStepGraph:
     """Forward + backward of one fixed problem, captured once into a CUDA graph and replayed.
 
     A training step at fixed shapes calls the library with the same pointers every time; replaying the
-    captured kernels removes the launch gaps between them.  With ``groups > 1`` the (batch, head) pairs
-    are cut into that many ranges and every range runs its own kernel chain on its own stream inside the
-    graph: the pairs are independent recurrences, so while the serial state scan of one range occupies a
-    few SMs, the chunk-parallel kernels of the other ranges use the rest.  Results are bitwise the same
-    for every ``groups``.  Inputs are read from, and results written to, the tensors given here: copy
-    new data into them between replays.  Results land in ``buf`` as with ``forward_into`` /
-    ``backward_into``.
+    captured kernels removes the launch gaps between them.  Two ways to fill the SMs the serial state scans
+    leave idle (a scan occupies V / 16 CTAs per (batch, head) pair), both bitwise equal to the plain chain:
+
+    ``pipeline`` (default for the delta-rule variants with at least 8 chunks): every sequence is cut into
+    an early and a late half of its chunks (``c_range`` of the C ABI) and the kernels of the two halves run
+    on two streams inside the graph, so that the chunk-parallel kernels of one half overlap the scan of the
+    other: prepare(late) runs under the forward scan of the early half, output(early) under the scan of the
+    late half, and in the backward Stage B and the WY kernel of the late half run under the adjoint scan of
+    the early half.  The scans hand their fp32 state from half to half through the workspace.  (Finer cuts,
+    and a stream per segment, measured slower: every extra segment adds a scan prologue to the serial chain
+    and the kernels lose their scan as stream predecessor.)
+
+    ``groups > 1``: the (batch, head) pairs are cut into that many ranges and every range runs its own
+    kernel chain on its own stream inside the graph (the pairs are independent recurrences).
+
+    Inputs are read from, and results written to, the tensors given here: copy new data into them between
+    replays.  Results land in ``buf`` as with ``forward_into`` / ``backward_into``.
     """
 
     def __init__(self, buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, *, b_gate=None, w_gate=None,
-                 groups: int = 1):
+                 groups: int = 1, pipeline: bool | None = None):
         self.buf = buf
         self._keep = (q, k, v, g, beta, h0, do, dhT, b_gate, w_gate)
         dev = q.device
         BH = buf.dims.B * buf.dims.H
+        NT = buf.dims.L // 64
         groups = max(1, min(int(groups), BH))
         bounds = [BH * i // groups for i in range(groups + 1)]
         ranges = [(bounds[i], bounds[i + 1] - bounds[i]) for i in range(groups)]
         self.groups = groups
+        if pipeline is None:
+            pipeline = groups == 1 and buf.dims.delta != 0 and NT >= 8
+        self.pipeline = bool(pipeline) and groups == 1 and NT >= 2
+        self.segments = 2 if self.pipeline else 1
+        gates = dict(b_gate=b_gate, w_gate=w_gate)
 
         def chain(rng):
-            forward_into(buf, q, k, v, g, beta, h0, scale, b_gate=b_gate, w_gate=w_gate, bh_range=rng)
-            backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, b_gate=b_gate, w_gate=w_gate, bh_range=rng)
+            forward_into(buf, q, k, v, g, beta, h0, scale, bh_range=rng, **gates)
+            backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, bh_range=rng, **gates)
 
         side = torch.cuda.Stream(device=dev)
-        self._streams = [torch.cuda.Stream(device=dev) for _ in range(groups - 1)]
+        self._streams = [torch.cuda.Stream(device=dev) for _ in range(max(groups - 1, 1))]
+
+        def fwd(mask, cr):
+            forward_into(buf, q, k, v, g, beta, h0, scale, mask, c_range=cr, **gates)
+
+        def bwd(mask, cr):
+            backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, mask, c_range=cr, **gates)
+
+        def mark(st):
+            e = torch.cuda.Event()
+            e.record(st)
+            return e
+
+        def pipelined():
+            # `side` carries the scans and, behind each scan, the kernels of the segment it has just passed (so
+            # that their programmatic-dependency launches keep their scan as the stream predecessor); `other`
+            # carries the kernels that run under a scan.
+            other = self._streams[0]
+            lo, hi = (0, NT // 2), (NT // 2, NT - NT // 2)
+            has_wy = buf.dims.delta != 0
+            with torch.cuda.stream(side):
+                fwd(1, lo)                                   # prepare, early half
+                e_plo = mark(side)
+                fwd(2, lo)                                   # forward scan over the early half
+                e_s1 = mark(side)
+            other.wait_event(e_plo)
+            with torch.cuda.stream(other):
+                fwd(1, hi)                                   # prepare, late half: under the scan above
+                e_phi = mark(other)
+            side.wait_event(e_phi)
+            with torch.cuda.stream(side):
+                fwd(2, hi)                                   # forward scan over the late half
+            other.wait_event(e_s1)
+            with torch.cuda.stream(other):
+                fwd(4, lo)                                   # output, early half: under the scan above
+                bwd(1, lo)                                   # input of the adjoint scan, early half
+                e_prelo = mark(other)
+            with torch.cuda.stream(side):
+                fwd(4, hi)
+                bwd(1, hi)
+                bwd(2, hi)                                   # the adjoint scan starts at the sequence's end
+                e_b1 = mark(side)
+            side.wait_event(e_prelo)
+            with torch.cuda.stream(side):
+                bwd(2, lo)                                   # adjoint scan over the early half
+            other.wait_event(e_b1)
+            with torch.cuda.stream(other):
+                bwd(4, hi)                                   # Stage B and the WY kernel of the late half: under it
+                if has_wy:
+                    bwd(8, hi)
+                e_end = mark(other)
+            with torch.cuda.stream(side):
+                bwd(4, lo)
+                if has_wy:
+                    bwd(8, lo)
+            side.wait_event(e_end)
 
         def step():
+            if self.pipeline:
+                pipelined()
+                return
             if groups == 1:
                 chain((0, 0))
                 return

@@ -70,7 +70,8 @@ def test_workspace_sizes(lib):
     scratch = lib.lethe_gdn_scratch_bytes(ctypes.byref(d))
     Z = 2 * 8 * 32
     per_saved = 16384 + 16384 + 8192 + 32768 + 16384 + 16384 + 8192 + 512
-    assert Z * per_saved <= saved <= Z * per_saved + 16 * 16384 + 8 * 1024
+    carry = 2 * 8 * 128 * 64 * 4            # fp32 state handed between chunk-range calls of the scan
+    assert Z * per_saved + carry <= saved <= Z * per_saved + carry + 16 * 16384 + 9 * 1024
     assert scratch >= Z * (16384 + 16384 + 8192 + 16384 + 32768 + 256)
     for bad in (ops._Dims(2, 8, 2000, 128, 64, 1, 1), ops._Dims(2, 8, 2048, 96, 64, 1, 1),
                 ops._Dims(2, 8, 2048, 128, 32, 1, 1), ops._Dims(0, 8, 2048, 128, 64, 1, 1),
