@@ -256,13 +256,43 @@ def path_fractions(workload: str, fwd_ms: float, bwd_ms: float, step_ms: float, 
 # every kernel's traffic grows in proportion to its chunks).  Keyed by (kernel, gate, d_v, delta); the
 # channel-wise "stageb" and "wy" are two launches each, summed.  Absent combinations report null.
 NCU_DRAM_BYTES_PER_CHUNK = {
-    ("stageb", "scalar", 64, True): (185.1e6 + 105.6e6) / 2048,
-    ("prepare", "scalar", 64, True): (85.0e6 + 127.9e6) / 2048,
-    ("wy", "scalar", 64, True): (203.0e6 + 34.2e6) / 2048,
-    ("scan_bwd", "scalar", 64, True): (101.7e6 + 14.6e6) / 2048,
-    ("prepare", "channel", 128, True): (168.4e6 + 247.3e6) / 2048,
-    ("scan_fwd", "scalar", 128, False): (140.5e6 + 91.5e6) / 4096,
-    ("scan_bwd", "scalar", 128, False): (136.4e6 + 89.0e6) / 4096,
+    # scalar-gate GDN, B4 H8 L4096 d_v 64 (2048 chunks)
+    ("prepare", "scalar", 64, True): (85.0e6 + 127.4e6) / 2048,
+    ("scan_fwd", "scalar", 64, True): (102.8e6 + 14.2e6) / 2048,
+    ("output", "scalar", 64, True): (151.5e6 + 18.3e6) / 2048,
+    ("bwd_pre", "scalar", 64, True): (118.0e6 + 15.4e6) / 2048,
+    ("scan_bwd", "scalar", 64, True): (101.7e6 + 13.4e6) / 2048,
+    ("stageb", "scalar", 64, True): (185.1e6 + 104.6e6) / 2048,
+    ("wy", "scalar", 64, True): (203.0e6 + 33.3e6) / 2048,
+    # KDA, B4 H8 L4096 d_v 128 (2048 chunks)
+    ("prepare", "channel", 128, True): (168.5e6 + 279.0e6) / 2048,
+    ("scan_fwd", "channel", 128, True): (137.4e6 + 38.5e6) / 2048,
+    ("output", "channel", 128, True): (201.4e6 + 43.3e6) / 2048,
+    ("bwd_pre", "channel", 128, True): (134.2e6 + 36.1e6) / 2048,
+    ("scan_bwd", "channel", 128, True): (135.3e6 + 38.4e6) / 2048,
+    ("stageb", "channel", 128, True): (369.2e6 + 242.3e6 + 352.4e6 + 131.0e6) / 2048,
+    ("wy", "channel", 128, True): (235.5e6 + 87.2e6 + 320.0e6 + 81.6e6) / 2048,
+    # GLA, B4 H16 L4096 d_v 128 (4096 chunks)
+    ("prepare", "channel", 128, False): (335.6e6 + 418.7e6) / 4096,
+    ("scan_fwd", "channel", 128, False): (141.0e6 + 93.5e6) / 4096,
+    ("output", "channel", 128, False): (335.6e6 + 105.7e6) / 4096,
+    ("bwd_pre", "channel", 128, False): (134.2e6 + 89.7e6) / 4096,
+    ("scan_bwd", "channel", 128, False): (136.4e6 + 90.6e6) / 4096,
+    ("stageb", "channel", 128, False): (738.3e6 + 460.8e6 + 704.7e6 + 244.6e6) / 4096,
+    # SSD, B4 H16 L4096 d_v 128 (4096 chunks)
+    ("prepare", "scalar", 128, False): (202.5e6 + 217.3e6) / 4096,
+    ("scan_fwd", "scalar", 128, False): (141.0e6 + 92.5e6) / 4096,
+    ("output", "scalar", 128, False): (336.6e6 + 106.5e6) / 4096,
+    ("bwd_pre", "scalar", 128, False): (135.3e6 + 90.4e6) / 4096,
+    ("scan_bwd", "scalar", 128, False): (136.4e6 + 91.0e6) / 4096,
+    ("stageb", "scalar", 128, False): (571.6e6 + 179.6e6) / 4096,
+    # LA, B4 H16 L4096 d_v 128 (4096 chunks)
+    ("prepare", "none", 128, False): (201.4e6 + 216.9e6) / 4096,
+    ("scan_fwd", "none", 128, False): (141.0e6 + 93.0e6) / 4096,
+    ("output", "none", 128, False): (335.6e6 + 105.9e6) / 4096,
+    ("bwd_pre", "none", 128, False): (134.2e6 + 90.8e6) / 4096,
+    ("scan_bwd", "none", 128, False): (136.4e6 + 89.7e6) / 4096,
+    ("stageb", "none", 128, False): (570.5e6 + 178.0e6) / 4096,
 }
 
 
@@ -274,18 +304,20 @@ def measured_traffic(kernel: str, gate: str, V: int, delta: bool, Z: int):
 # ------------------------------------------------------------------------------------------------
 def algorithmic_bytes(kernel: str, Z: int, BH: int, V: int, delta: bool, cw: bool = False) -> int:
     """Bytes one launch of `kernel` must move: each input tile and each record read once, each
-    result written once (Z chunks, 64 tokens each; K = 128).  With the channel-wise gate every kernel
-    also reads the chunk's 32 KB of gate values, "stageb" and "wy" are two launches each and pass
-    three fp32 64 x 128 records (dq / dk / dg parts) between them."""
+    result written once (Z chunks, 64 tokens each; K = 128).  With the channel-wise gate "prepare" also
+    writes the chunk's 32 KB tile of cumulative gate values and the 16 KB record of the scaled, decayed
+    query (which "output" and "bwd_pre" read in place of q), the Stage B and WY kernels read the gate
+    tile, and "stageb" and "wy" are two launches each that pass three fp32 64 x 128 records (dq / dk / dg
+    parts) between them."""
     qk, vv, img = 64 * 128 * 2, 64 * V * 2, 128 * V * 2
     ta, w, p_, r, f32k = 16384, 16384, 32768, 128 * V * 2, 64 * 128 * 4
     if cw:
         g = f32k
         per = {
-            "prepare": g + 2 * qk + vv + ta + vv + r + ((w + p_) if delta else 0) + 512,
+            "prepare": g + 2 * qk + vv + g + qk + ta + vv + r + ((w + p_) if delta else 0) + 512,
             "scan_fwd": (p_ if delta else 0) + r + img + 512,
-            "output": g + qk + ta + img + vv + vv + vv + (w if delta else 0),
-            "bwd_pre": g + qk + vv + r + ((w + ta) if delta else 0),
+            "output": qk + ta + img + vv + vv + vv + (w if delta else 0),
+            "bwd_pre": qk + vv + r + ((w + ta) if delta else 0),
             "scan_bwd": (p_ if delta else 0) + r + img + 512,
             "stageb": (g + 2 * qk + vv + ta + vv + 2 * img + 8192 + 3 * f32k + (vv + w if delta else vv))
                       + (g + 2 * qk + 8192 + 3 * f32k + qk + (2 * f32k if delta else qk + f32k)),
@@ -780,6 +812,7 @@ def main():
                          # is timed inside a long loop)
                          "path": fr,
                          "kernels": {n: {"ms": kern[n], "io_bytes": io_bytes(n, Z, V, delta, gate),
+                                         "traffic": measured_traffic(n, gate, V, delta, Z),
                                          "record_bytes": algorithmic_bytes(n, Z, BH, V, delta, gate == "channel")
                                          - io_bytes(n, Z, V, delta, gate)} for n in kern}},
             "hbm_frac": fr["step"]["hbm_frac"], "tensor_frac": fr["step"]["tensor_frac"],

@@ -103,37 +103,53 @@ struct L2Problem {
   int norm_f16;         // the normalised rows and their gradients are fp16
 };
 
-// grid.y selects the tensor; LANES = D / 8 lanes per row
+// grid.y selects the tensor; LANES = D / 8 lanes per row.  A thread works on kPieces 16-byte pieces, 256
+// pieces apart, and requests all of them before it uses the first: with one piece per thread an SM has
+// 32 KB of loads in flight, too little to cover the latency of HBM (the forward reached 0.44 of the copy
+// bandwidth that way).
+constexpr int kPieces = 4;
+
 template <int LANES, bool F32, bool BACKWARD>
 __global__ void __launch_bounds__(256)
 l2norm_qk_kernel(const L2Problem p) {
   const int t = blockIdx.y;
-  const long long piece = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long row = piece / LANES;
-  // a warp never straddles the end: rows * LANES is padded to whole warps by the row test only,
-  // so every lane of a live row takes part in the butterfly
-  const bool live = row < p.rows;
-  const size_t idx = static_cast<size_t>(live ? piece : 0) * 8;
-  float x[8];
-  load8<F32>(p.x[t], idx, x);
-  float ss = 0.f;
+  const long long first = static_cast<long long>(blockIdx.x) * (256 * kPieces) + threadIdx.x;
+  // a warp never straddles the end of the tensor inside a row: rows * LANES pieces are padded to whole
+  // CTAs by the row test only, so every lane of a live row takes part in the butterfly
+  bool live[kPieces];
+  size_t idx[kPieces];
+  float x[kPieces][8], dy[BACKWARD ? kPieces : 1][8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
-  const float r = rsqrtf(row_sum<LANES>(ss) + p.eps);
-  if (!BACKWARD) {
+  for (int u = 0; u < kPieces; ++u) {
+    const long long piece = first + u * 256;
+    live[u] = piece / LANES < p.rows;
+    idx[u] = static_cast<size_t>(live[u] ? piece : 0) * 8;
+  }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] *= r;
-    if (live) store8_16(p.out[t], idx, x, p.norm_f16);
-  } else {
-    float dy[8];
-    load8_16(p.dy[t], idx, dy, p.norm_f16);
-    float dot = 0.f;
+  for (int u = 0; u < kPieces; ++u) load8<F32>(p.x[t], idx[u], x[u]);
+  if (BACKWARD) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dot = fmaf(x[j], dy[j], dot);
-    const float c = row_sum<LANES>(dot) * r * r;       // dx = r dy - x r^3 (x . dy)
+    for (int u = 0; u < kPieces; ++u) load8_16(p.dy[t], idx[u], dy[u], p.norm_f16);
+  }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] = r * (dy[j] - x[j] * c);
-    if (live) store8<F32>(p.out[t], idx, x);
+  for (int u = 0; u < kPieces; ++u) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(x[u][j], x[u][j], ss);
+    const float r = rsqrtf(row_sum<LANES>(ss) + p.eps);
+    if (!BACKWARD) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[u][j] *= r;
+      if (live[u]) store8_16(p.out[t], idx[u], x[u], p.norm_f16);
+    } else {
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot = fmaf(x[u][j], dy[u][j], dot);
+      const float c = row_sum<LANES>(dot) * r * r;       // dx = r dy - x r^3 (x . dy)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[u][j] = r * (dy[u][j] - x[u][j] * c);
+      if (live[u]) store8<F32>(p.out[t], idx[u], x[u]);
+    }
   }
 }
 
@@ -141,7 +157,8 @@ template <bool BACKWARD>
 int launch_l2norm(const L2Problem& p, int D, bool f32, cudaStream_t st) {
   const int lanes = D / 8;
   const long long pieces = p.rows * lanes;
-  const dim3 grid(static_cast<unsigned>((pieces + 255) / 256), 2);
+  const int per_cta = 256 * kPieces;
+  const dim3 grid(static_cast<unsigned>((pieces + per_cta - 1) / per_cta), 2);
   if (lanes == 16) {
     if (f32) l2norm_qk_kernel<16, true, BACKWARD><<<grid, 256, 0, st>>>(p);
     else l2norm_qk_kernel<16, false, BACKWARD><<<grid, 256, 0, st>>>(p);
