@@ -567,10 +567,11 @@ def main():
     ap.add_argument("--groups", type=int, default=1,
                     help="cut the (batch, head) pairs into this many ranges that run as concurrent kernel chains "
                          "inside the step graph (helps when the scans leave SMs idle: a few % on the larger workloads)")
-    ap.add_argument("--segments", type=int, default=-1,
-                    choices=(-1, 1, 2),
-                    help="2: cut every sequence into two chunk segments whose kernels overlap the other segment's "
-                         "scan inside the step graph; 1: one plain chain; -1: the library's default")
+    ap.add_argument("--cut", type=int, default=-1,
+                    help="chunk index at which the step graph cuts every sequence into an early and a late segment "
+                         "(0: no cut; -1: the library's default, about half of the chunks on a whole number of CTA waves)")
+    ap.add_argument("--plain-chain", action="store_true",
+                    help="capture the step as one chain of kernels on one stream (no overlap inside the graph)")
     ap.add_argument("--mild-gate", action="store_true",
                     help="draw the gate as -0.1 U(0,1), the draw of the reference's own benchmark, instead of "
                          "-softplus(N(0,1) + 3)")
@@ -669,7 +670,7 @@ def main():
     # the timed step is the CUDA-graph replay of forward + backward (ops.GdnStepGraph: the public call for a
     # training step at fixed shapes); the per-kernel and fwd / bwd timings below are plain launches
     graph = ops.GdnStepGraph(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale, groups=args.groups,
-                             pipeline=None if args.segments < 0 else args.segments == 2, **gates)
+                             pipeline=not args.plain_chain, cut=None if args.cut < 0 else args.cut, **gates)
     ms = timed(graph.replay, args.steps, max(args.warmup, 3))
     ops.check_status(buf.status)
     eager_ms = timed(step, args.steps, 3)
@@ -783,7 +784,7 @@ def main():
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate (bf16 in/out)",
             "data": "synthetic", "config": config,
-            "launch": f"CUDA graph replay (lethe_b200.ops.GdnStepGraph, groups={args.groups}, segments={graph.segments})",
+            "launch": f"CUDA graph replay (lethe_b200.ops.GdnStepGraph, groups={args.groups}, overlap={graph.pipeline}, cut={graph.cut})",
             "eager_ms_per_step": eager_ms,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "kernel_ms": kern,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,

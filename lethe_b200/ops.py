@@ -208,14 +208,15 @@ class GdnStepGraph:
     captured kernels removes the launch gaps between them.  Two ways to fill the SMs the serial state scans
     leave idle (a scan occupies V / 16 CTAs per (batch, head) pair), both bitwise equal to the plain chain:
 
-    ``pipeline`` (default for the delta-rule variants with at least 8 chunks): every sequence is cut into
-    an early and a late half of its chunks (``c_range`` of the C ABI) and the kernels of the two halves run
-    on two streams inside the graph, so that the chunk-parallel kernels of one half overlap the scan of the
-    other: prepare(late) runs under the forward scan of the early half, output(early) under the scan of the
-    late half, and in the backward Stage B and the WY kernel of the late half run under the adjoint scan of
-    the early half.  The scans hand their fp32 state from half to half through the workspace.  (Finer cuts,
-    and a stream per segment, measured slower: every extra segment adds a scan prologue to the serial chain
-    and the kernels lose their scan as stream predecessor.)
+    ``pipeline`` (default): only the serial chain of the step - prepare, forward scan, adjoint scan, Stage B
+    and WY - stays on one stream; the output kernel and the kernel that builds the adjoint scan's input run
+    on other streams of the graph beside the scans (the adjoint scan needs neither the outputs nor the
+    forward scan).  ``cut`` (default: about half of the chunks, on a whole number of CTA waves, for sequences of at
+    least 8 chunks; 0 = no cut) splits every sequence into an early and a late segment of chunks (``c_range`` of the C
+    ABI): the late segment is prepared under the forward scan of the early one, and its Stage B and WY
+    kernels run under the adjoint scan of the early one.  The scans hand their fp32 state from segment to
+    segment through the workspace.  (More than two segments, and a stream per segment, measured slower:
+    every extra segment adds a scan prologue to the serial chain.)
 
     ``groups > 1``: the (batch, head) pairs are cut into that many ranges and every range runs its own
     kernel chain on its own stream inside the graph (the pairs are independent recurrences).
@@ -225,7 +226,8 @@ class GdnStepGraph:
     """
 
     def __init__(self, buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, *, b_gate=None, w_gate=None,
-                 groups: int = 1, pipeline: bool | None = None):
+                 groups: int = 1, pipeline: bool | None = None,
+                 cut: int | None = None):
         self.buf = buf
         self._keep = (q, k, v, g, beta, h0, do, dhT, b_gate, w_gate)
         dev = q.device
@@ -236,9 +238,12 @@ class GdnStepGraph:
         ranges = [(bounds[i], bounds[i + 1] - bounds[i]) for i in range(groups)]
         self.groups = groups
         if pipeline is None:
-            pipeline = groups == 1 and buf.dims.delta != 0 and NT >= 8
-        self.pipeline = bool(pipeline) and groups == 1 and NT >= 2
-        self.segments = 2 if self.pipeline else 1
+            pipeline = groups == 1
+        self.pipeline = bool(pipeline) and groups == 1
+        if cut is None:
+            cut = self._default_cut(buf, NT, BH, dev)
+        self.cut = int(cut) if self.pipeline and 0 < int(cut) < NT else 0
+        self.segments = 2 if self.cut else 1
         gates = dict(b_gate=b_gate, w_gate=w_gate)
 
         def chain(rng):
@@ -246,7 +251,7 @@ class GdnStepGraph:
             backward_into(buf, q, k, v, g, beta, h0, do, dhT, scale, bh_range=rng, **gates)
 
         side = torch.cuda.Stream(device=dev)
-        self._streams = [torch.cuda.Stream(device=dev) for _ in range(max(groups - 1, 1))]
+        self._streams = [torch.cuda.Stream(device=dev) for _ in range(max(groups - 1, 2))]
 
         def fwd(mask, cr):
             forward_into(buf, q, k, v, g, beta, h0, scale, mask, c_range=cr, **gates)
@@ -260,48 +265,61 @@ class GdnStepGraph:
             return e
 
         def pipelined():
-            # `side` carries the scans and, behind each scan, the kernels of the segment it has just passed (so
-            # that their programmatic-dependency launches keep their scan as the stream predecessor); `other`
-            # carries the kernels that run under a scan.
-            other = self._streams[0]
-            lo, hi = (0, NT // 2), (NT // 2, NT - NT // 2)
+            # The serial chain of a step is prepare(first segment) -> forward scan -> adjoint scan -> Stage B and
+            # WY of the first segment; `side` carries exactly that.  Everything else hangs off it by events:
+            # `other` prepares the later segment and builds the adjoint scan's input while the forward scan
+            # runs, computes the outputs behind the scan, and runs Stage B / WY of the later segment under the
+            # adjoint scan of the first; `third` computes the output of the last segment while the adjoint scan
+            # has already started.  Stream order is chosen so that no kernel launched with the
+            # programmatic-dependency attribute follows, on its own stream, the kernel whose result it loads
+            # before its wait (Stage B loads v_new early: it never follows an output kernel of its own segment).
+            other, third = self._streams[0], self._streams[1]
+            segs = [(0, self.cut), (self.cut, NT - self.cut)] if self.segments == 2 else [(0, NT)]
+            S = len(segs)
             has_wy = buf.dims.delta != 0
+            e_p, e_f, e_r, e_o, e_a = ([None] * S for _ in range(5))
             with torch.cuda.stream(side):
-                fwd(1, lo)                                   # prepare, early half
-                e_plo = mark(side)
-                fwd(2, lo)                                   # forward scan over the early half
-                e_s1 = mark(side)
-            other.wait_event(e_plo)
+                fwd(1, segs[0])
+                e_p[0] = mark(side)
+            other.wait_event(e_p[0])
             with torch.cuda.stream(other):
-                fwd(1, hi)                                   # prepare, late half: under the scan above
-                e_phi = mark(other)
-            side.wait_event(e_phi)
+                for i in range(1, S):
+                    fwd(1, segs[i])                          # prepare of the later segment: under the first scan
+                    e_p[i] = mark(other)
+                for i in reversed(range(S)):
+                    bwd(1, segs[i])                          # input of the adjoint scan: needs prepare and do only
+                    e_r[i] = mark(other)
+            for i in range(S):                               # forward scan, segment after segment
+                if i:
+                    side.wait_event(e_p[i])
+                with torch.cuda.stream(side):
+                    fwd(2, segs[i])
+                    e_f[i] = mark(side)
+            for i in range(S):                               # outputs behind the scan, off the serial chain
+                st = third if i == S - 1 else other
+                st.wait_event(e_f[i])
+                with torch.cuda.stream(st):
+                    fwd(4, segs[i])
+                    e_o[i] = mark(st)
+            for i in reversed(range(S)):                     # adjoint scan straight behind the forward scan
+                side.wait_event(e_r[i])
+                with torch.cuda.stream(side):
+                    bwd(2, segs[i])
+                    e_a[i] = mark(side)
+            for i in reversed(range(1, S)):                  # Stage B / WY of the later segment: under the adjoint scan
+                other.wait_event(e_a[i])
+                other.wait_event(e_o[i])
+                with torch.cuda.stream(other):
+                    bwd(4, segs[i])
+                    if has_wy:
+                        bwd(8, segs[i])
+            side.wait_event(e_o[0])
             with torch.cuda.stream(side):
-                fwd(2, hi)                                   # forward scan over the late half
-            other.wait_event(e_s1)
-            with torch.cuda.stream(other):
-                fwd(4, lo)                                   # output, early half: under the scan above
-                bwd(1, lo)                                   # input of the adjoint scan, early half
-                e_prelo = mark(other)
-            with torch.cuda.stream(side):
-                fwd(4, hi)
-                bwd(1, hi)
-                bwd(2, hi)                                   # the adjoint scan starts at the sequence's end
-                e_b1 = mark(side)
-            side.wait_event(e_prelo)
-            with torch.cuda.stream(side):
-                bwd(2, lo)                                   # adjoint scan over the early half
-            other.wait_event(e_b1)
-            with torch.cuda.stream(other):
-                bwd(4, hi)                                   # Stage B and the WY kernel of the late half: under it
+                bwd(4, segs[0])
                 if has_wy:
-                    bwd(8, hi)
-                e_end = mark(other)
-            with torch.cuda.stream(side):
-                bwd(4, lo)
-                if has_wy:
-                    bwd(8, lo)
-            side.wait_event(e_end)
+                    bwd(8, segs[0])
+            side.wait_event(mark(other))
+            side.wait_event(mark(third))
 
         def step():
             if self.pipeline:
@@ -335,6 +353,24 @@ class GdnStepGraph:
             with torch.cuda.graph(self.graph, stream=side):
                 step()
         torch.cuda.current_stream(dev).wait_stream(side)
+
+    @staticmethod
+    def _default_cut(buf, NT: int, BH: int, dev) -> int:
+        """Chunk index of the cut: the whole number of CTA waves of the chunk kernels nearest to half of the
+        sequence.  A chunk kernel runs one CTA per chunk, two per SM for the scalar gate at d_v = 64 and one
+        otherwise; when the early segment fills whole waves, the kernels on the serial chain (its prepare, its
+        Stage B and WY) do not end on a nearly empty wave, which is worth 7 % of the step at B=2, H=8, L=2048."""
+        if NT < 8:
+            return 0
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        per_sm = 2 if (buf.dims.gate != GATE_CHANNEL and buf.dims.V == 64) else 1
+        wave = (sms * per_sm) // BH                  # chunks of every (batch, head) pair in one wave
+        if wave == 0 or wave >= NT:
+            return NT // 2
+        cut = max(1, int(NT / 2 / wave + 0.5)) * wave
+        if cut >= NT:
+            cut -= wave
+        return cut if cut > 0 else NT // 2
 
     def replay(self) -> None:
         """Enqueue the captured step on the current stream."""

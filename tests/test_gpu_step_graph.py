@@ -96,10 +96,10 @@ def test_chunk_ranges_and_the_pipelined_graph_give_the_same_bits(gate, delta, V)
         for cr in reversed(ranges):
             ops.backward_into(part, *args, d["do"], dhT, sc, m, c_range=cr)
     pipes = []
-    for _ in range(1):
+    for cut in (0, NT // 2, 1, NT - 1):
         pipe = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
-        graph = ops.GdnStepGraph(pipe, *args, d["do"], dhT, sc, pipeline=True)
-        assert graph.pipeline and graph.segments == 2
+        graph = ops.GdnStepGraph(pipe, *args, d["do"], dhT, sc, pipeline=True, cut=cut)
+        assert graph.pipeline and graph.cut == cut and graph.segments == (2 if cut else 1)
         for t in (pipe.o, pipe.dq, pipe.dk, pipe.dv, pipe.hT, pipe.dh0):
             t.fill_(float("nan"))
         graph.replay()
