@@ -9,10 +9,14 @@ L=2048, d_k=128, d_v=64, chunk 64, bf16 inputs, initial state.  With N > 1 every
 workload on its own (batch x head) shard -- the path shards without communication -- so scaling is
 "weak" and `value` is the whole job's tokens (B*L per rank) per second.
 
-Prints ONE JSON line (rank 0).  `value`: inputs resident in HBM, CUDA events around every step, L2
-flushed between steps, max over ranks.  `e2e`: the same step through the public op
-(`lethe_b200.ops.gdn_chunk` + autograd) with pinned host buffers, host->device copies of all inputs
-and device->host copies of all results inside the timed region.  `roofline`: the dominant kernel,
+Prints ONE JSON line (rank 0).  `value`: inputs resident in HBM, the step as the CUDA-graph replay of
+`lethe_b200.ops.GdnStepGraph` (`eager_ms_per_step`: the same kernels launched one by one from the host,
+`autograd_op_ms`: through `ops.gdn_chunk` + autograd), CUDA events around every step, L2 flushed between
+steps, max over ranks.  `e2e`: the same step through `lethe_b200.host.HostPipeline`, the public call for
+tensors in host memory: pinned host buffers, host->device copies of all inputs and device->host copies of
+all results inside the timed region, consecutive steps overlapped; `e2e.host_link` is the host link measured
+in the same process with every rank copying at once, and `host_link_floor_ms` the time those bytes need on
+it.  `roofline`: the dominant kernel,
 timed alone with CUDA events, plus the whole step against the algorithmic bytes and FLOPs of the path
 (HBM and tensor-core fractions for forward, backward and both).  `cpu_baseline`: the reference project's
 own PyTorch CPU chunkwise path (its backward assembly, imported from `oracle/_ref`, the reference compiled
@@ -689,6 +693,7 @@ def main():
     fwd_ms = timed(lambda: ops.forward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, scale, **gates), args.steps, 3)
     bwd_ms = timed(lambda: ops.backward_into(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale,
                                              **gates), args.steps, 3)
+
     ops.check_status(buf.status)
 
     # ---- end to end through the public host API: pinned host buffers in, pinned host buffers out, every

@@ -63,52 +63,3 @@ def test_head_ranges_and_groups_give_the_same_bits():
     with pytest.raises(ops.GdnError):
         ops.forward_into(part, *args, K ** -0.5, bh_range=(5, 2))     # beyond B * H = 6
 
-
-@pytest.mark.parametrize("gate,delta,V", [("scalar", True, 64), ("channel", True, 128), ("scalar", False, 128),
-                                          ("channel", False, 64)])
-def test_chunk_ranges_and_the_pipelined_graph_give_the_same_bits(gate, delta, V):
-    """Calls restricted to chunk ranges (forward ranges ascending, backward ranges descending: the scans hand
-    their fp32 state on through the workspace) and the graph that overlaps the two halves of every sequence
-    on two streams must reproduce the one-call result bit for bit, final state and initial-state gradient
-    included."""
-    B, L, H, K = 2, 1024, 3, 128
-    NT = L // 64
-    dev = torch.device("cuda")
-    code = {"scalar": ops.GATE_SCALAR, "channel": ops.GATE_CHANNEL}[gate]
-    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=9)
-    d = {n: (None if t is None else t.to(dev)) for n, t in inp.items()}
-    dhT = 0.1 * torch.randn(B, H, K, V, generator=torch.Generator().manual_seed(10)).to(dev)
-    args = (d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"])
-    sc = K ** -0.5
-    ref = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
-    ops.forward_into(ref, *args, sc)
-    ops.backward_into(ref, *args, d["do"], dhT, sc)
-    names = ["o", "hT", "dq", "dk", "dv", "dg", "dh0"] + (["dbeta"] if delta else [])
-    # three uneven ranges, kernel by kernel
-    part = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
-    for t in (part.o, part.dq, part.dk, part.dv, part.hT, part.dh0):
-        t.fill_(float("nan"))
-    ranges = [(0, 5), (5, 1), (6, NT - 6)]
-    for m in (1, 2, 4):
-        for cr in ranges:
-            ops.forward_into(part, *args, sc, m, c_range=cr)
-    for m in (1, 2, 4, 8) if delta else (1, 2, 4):
-        for cr in reversed(ranges):
-            ops.backward_into(part, *args, d["do"], dhT, sc, m, c_range=cr)
-    pipes = []
-    for cut in (0, NT // 2, 1, NT - 1):
-        pipe = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
-        graph = ops.GdnStepGraph(pipe, *args, d["do"], dhT, sc, pipeline=True, cut=cut)
-        assert graph.pipeline and graph.cut == cut and graph.segments == (2 if cut else 1)
-        for t in (pipe.o, pipe.dq, pipe.dk, pipe.dv, pipe.hT, pipe.dh0):
-            t.fill_(float("nan"))
-        graph.replay()
-        graph.replay()
-        pipes.append(pipe)
-    torch.cuda.synchronize()
-    for b in [part] + pipes:
-        ops.check_status(b.status)
-        for n in names:
-            assert torch.equal(getattr(b, n), getattr(ref, n)), n
-    with pytest.raises(ops.GdnError):
-        ops.forward_into(part, *args, sc, c_range=(NT - 1, 2))          # beyond the last chunk
