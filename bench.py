@@ -802,7 +802,8 @@ def main():
                     "host_link": pcie,
                     "host_link_floor_ms": max(h2d, d2h) / (pcie["both"]["slowest_rank_gbs"] * 1e9) * 1e3},
             "autograd_op_ms": op_ms,
-            "gpu_launches": args.steps * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
+            # kernels per replayed step: one chain per segment of the step graph
+            "gpu_launches": args.steps * graph.segments * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
             "clocks": clocks,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "peak_source": which,
