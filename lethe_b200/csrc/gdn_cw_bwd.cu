@@ -274,8 +274,10 @@ bwd_cw_sb1_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, const
 // WY VJP, part 1.  Accumulators: c1 [64,128) dT; c2 [128,192) X; c3 [192,256) dM;
 // c4 [256, 256+V+128) [dbv | d(beta gamma k)].
 // ---------------------------------------------------------------------------------------------
+constexpr int kWy1Threads = 256;
+
 template <int V>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kWy1Threads)
 bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024(smem_raw);
@@ -290,7 +292,8 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   float* Gt = reinterpret_cast<float*>(XT + 16384);
   float* fs = Gt + 64 * kK;
   float* betas = fs;
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 64);
+  float* part = fs + 64;                        // [2][64]: the second column half's share of the two row sums
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 64 + 128);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int bh = p.bh0 + blockIdx.x / p.cn, c = p.c0 + blockIdx.x % p.cn, z = bh * p.NT + c, b = bh / p.H, h = bh % p.H;
@@ -319,11 +322,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   const size_t tok0 = (static_cast<size_t>(b) * p.L + c * kC) * p.H + h;
   // full op (per-channel erase gate b, write gate w): the gates enter element by element, beta is one
   const bool full = p.bch != nullptr;
-  float bval = 0.f;
-  if (tid < 64) {
-    bval = full ? 1.f : p.beta[tok0 + static_cast<size_t>(tid) * p.H];
-    betas[tid] = bval;
-  }
+  if (tid < 64) betas[tid] = full ? 1.f : p.beta[tok0 + static_cast<size_t>(tid) * p.H];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -331,7 +330,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   const uint32_t c1 = tmem + 64, c2 = tmem + 128, c3 = tmem + 192, c4 = tmem + 256;
   __syncthreads();
   mbar_wait_warp(bar_load, 0, ctl, 611);
-  for (int idx = tid; idx < 64 * 16; idx += 128) {
+  for (int idx = tid; idx < 64 * 16; idx += kWy1Threads) {
     const int r = idx >> 4, ch = idx & 15;
     float x[8], y[8];
     unpack8_in(tile_ld_chunk(KB, r, ch, 128), x, p.qk16);
@@ -350,7 +349,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     for (int e = 0; e < 8; ++e) y[e] = x[e] * bb[e] * exp2f(gg[e]);
     tile_st_chunk(KB, 64 + r, ch, 128, pack8_f16(y));
   }
-  for (int idx = tid; idx < 64 * (V / 8); idx += 128) {
+  for (int idx = tid; idx < 64 * (V / 8); idx += kWy1Threads) {
     const int r = idx / (V / 8), ch = idx % (V / 8);
     float x[8];
     unpack8_bf16(tile_ld_chunk(VT, r, ch, 64), x);
@@ -379,13 +378,16 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 612);
-  if (tid < 64) {
-    float d[64];
-    tmem_ld32(c1 + lane_base, d);
-    tmem_ld32(c1 + lane_base + 32, d + 32);
+  // The accumulators have 64 rows (lanes 0-63): warps 0, 1, 4, 5 reach them, warp w and w + 4 the same
+  // lanes, and split the columns of every epilogue between them.
+  const bool owner = (warp & 3) < 2;
+  const int r = (warp & 3) * 32 + (tid & 31), half = warp >> 2;
+  if (owner) {
+    float d[32];
+    tmem_ld32(c1 + lane_base + half * 32, d);
     tmem_ld_wait();
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(DTt, tid, s8, 64, pack8_f16(d + 8 * s8));
+    for (int s8 = 0; s8 < 4; ++s8) tile_st_chunk(DTt, r, half * 4 + s8, 64, pack8_f16(d + 8 * s8));
   }
   sync_for_issue();
   if (warp == 0) {
@@ -395,13 +397,12 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     umma_commit_led(leader, bar_mma);
   }
   wait_products(bar_mma, ph, ctl, 613);
-  if (tid < 64) {
-    float d[64];
-    tmem_ld32(c2 + lane_base, d);
-    tmem_ld32(c2 + lane_base + 32, d + 32);
+  if (owner) {
+    float d[32];
+    tmem_ld32(c2 + lane_base + half * 32, d);
     tmem_ld_wait();
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) tile_st_chunk(XT, tid, s8, 64, pack8_f16(d + 8 * s8));
+    for (int s8 = 0; s8 < 4; ++s8) tile_st_chunk(XT, r, half * 4 + s8, 64, pack8_f16(d + 8 * s8));
   }
   sync_for_issue();
   if (warp == 0) {
@@ -415,27 +416,29 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
   // still reads the dq-part record that is overwritten below: wait for it before writing anything.
   griddep_wait();
   griddep_launch();
-  if (tid < 64) {
-    const int r = tid;
-    {  // dM, strictly lower -> record
-      float dm[64];
-      tmem_ld32(c3 + lane_base, dm);
-      tmem_ld32(c3 + lane_base + 32, dm + 32);
+  // Results are staged in tiles that are dead by now and leave as bulk copies: dM in the dT tile, the fp32
+  // record of d(beta gamma k) in the 32 KB that start at the [T; A] tile and run over the dv2 tile (and, at
+  // d_v = 64, half of the dw tile); its global layout is its shared-memory image.
+  float* DQs = reinterpret_cast<float*>(TAt);
+  float rv = 0.f, pq = 0.f;
+  if (owner) {
+    {  // dM, strictly lower
+      float dm[32];
+      tmem_ld32(c3 + lane_base + half * 32, dm);
       tmem_ld_wait();
-      unsigned char* dm_g = p.scratch + p.lay.dm + static_cast<size_t>(z) * 8192;
 #pragma unroll
-      for (int s8 = 0; s8 < 8; ++s8) {
+      for (int s8 = 0; s8 < 4; ++s8) {
         float y[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = (s8 * 8 + i < r) ? dm[s8 * 8 + i] : 0.f;
-        *reinterpret_cast<uint4*>(dm_g + sw128_chunk(r, s8, 64)) = pack8_f16(y);
+        for (int i = 0; i < 8; ++i) y[i] = (half * 32 + s8 * 8 + i < r) ? dm[s8 * 8 + i] : 0.f;
+        tile_st_chunk(DTt, r, half * 4 + s8, 64, pack8_f16(y));
       }
     }
     // dv = beta dbv; value part of dbeta
-    float rv = 0.f;
     __nv_bfloat16* dv_g = p.dv + (tok0 + static_cast<size_t>(r) * p.H) * V;
 #pragma unroll
-    for (int jb = 0; jb < V / 32; ++jb) {
+    for (int jj = 0; jj < V / 64; ++jj) {
+      const int jb = half * (V / 64) + jj;
       float d[32];
       tmem_ld32(c4 + lane_base + jb * 32, d);
       tmem_ld_wait();
@@ -454,6 +457,7 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
           }
           st8(p.dwch + at, dwv);
         } else {
+          const float bval = betas[r];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             rv += d[8 * i + e] * vv[e];
@@ -465,10 +469,9 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
     }
     // d(beta gamma k) = T^T dw: fp32 -> record; its direct part of the erase-gate gradient,
     // sum_d d(beta gamma k) gamma k, is closed here
-    float pq = 0.f;
-    float* dqp_g = reinterpret_cast<float*>(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4));
 #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jj = 0; jj < 2; ++jj) {
+      const int jb = half * 2 + jj;
       float d[32];
       tmem_ld32(c4 + V + lane_base + jb * 32, d);
       tmem_ld_wait();
@@ -482,17 +485,31 @@ bwd_cw_wy1_kernel(const Problem p, const __grid_constant__ CUtensorMap mk, const
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<float4*>(dqp_g + ridx(r, jb * 32 + 4 * i)) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+        *reinterpret_cast<float4*>(DQs + ridx(r, jb * 32 + 4 * i)) = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
     }
-    if (full) {
-      // the erase-gate gradient is formed per channel by the pair kernel
-    } else if (p.dbeta_w) {
+    if (half == 1) {
+      part[r] = rv;
+      part[64 + r] = pq;
+    }
+  }
+  fence_proxy_async();
+  __syncthreads();
+  if (tid == 0) {
+    bulk_s2g(p.scratch + p.lay.dm + static_cast<size_t>(z) * 8192, DTt, 8192);
+    bulk_s2g(p.scratch + p.lay.dqp + static_cast<size_t>(z) * (kC * kK * 4), DQs, kC * kK * 4);
+    bulk_commit();
+  }
+  if (owner && half == 0 && !full) {
+    rv += part[r];
+    pq += part[64 + r];
+    if (p.dbeta_w) {
       p.dbeta_w[tok0 + static_cast<size_t>(r) * p.H] = rv;
       p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = pq;
     } else {
       p.dbeta[tok0 + static_cast<size_t>(r) * p.H] = rv + pq;
     }
   }
+  if (tid == 0) bulk_wait_read();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
@@ -843,11 +860,11 @@ static int launch_sb1_t(const Problem& p, const CUtensorMap& mq, const CUtensorM
 }
 template <int V>
 static int launch_wy1_t(const Problem& p, const CUtensorMap& mk, const CUtensorMap& mv, cudaStream_t st) {
-  const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 + 16384 + 32768 + 64 * 4 +
+  const int smem = 32768 + V * 128 * 3 + 16384 * 2 + 8192 + 16384 + 32768 + (64 + 128) * 4 +
                    static_cast<int>(sizeof(CtaShared)) + 1024;
   static SmemAttr attr;
   if (attr.set(bwd_cw_wy1_kernel<V>, smem)) return kErrLaunch;
-  if (launch_dependent(bwd_cw_wy1_kernel<V>, dim3(p.nbh * p.cn), dim3(128), smem, st, p, mk, mv) != cudaSuccess)
+  if (launch_dependent(bwd_cw_wy1_kernel<V>, dim3(p.nbh * p.cn), dim3(kWy1Threads), smem, st, p, mk, mv) != cudaSuccess)
     return kErrLaunch;
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -15,7 +15,8 @@ of the reference, where the tests and the benchmark's CPU arm import ``lethe.*``
 
 This is test infrastructure.  Nothing in the ``lethe_b200`` package imports it.
 
-Usage:  python oracle/make_ref.py [/path/to/reference]        (default /root/reference)
+Usage:  python oracle/make_ref.py [path of the reference checkout]      (default: ``REFERENCE_ROOT`` below,
+or the environment variable ``LETHE_REFERENCE_ROOT``)
 """
 
 from __future__ import annotations
@@ -32,9 +33,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 SUBTREES = ("lethe",)          # everything under src/lethe (a few hundred KB of bytecode)
 EXT = ".lbc"                   # a .pyc by content: 16-byte header, then the marshalled code object
+REFERENCE_ROOT = os.environ.get("LETHE_REFERENCE_ROOT", "/root/reference")
 
 
-def build(reference_root: str = "/root/reference", quiet: bool = False) -> str | None:
+def build(reference_root: str = REFERENCE_ROOT, quiet: bool = False) -> str | None:
     src_root = os.path.join(reference_root, "src")
     if not os.path.isdir(os.path.join(src_root, "lethe")):
         if not quiet:
@@ -119,4 +121,4 @@ def import_reference():
 
 
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    build(sys.argv[1] if len(sys.argv) > 1 else REFERENCE_ROOT)
