@@ -5,7 +5,7 @@
 //
 // (reference gdn_backward.py:45-53, one iteration of its token loop; beta == null drops the delta term).
 // The step is bound by reading and writing the fp32 state once: K x V x 4 bytes each way per pair.
-// One CTA of 2 V threads per pair: two threads share column c of S (64 rows each) and keep their
+// One CTA of 4 V threads per pair: four threads share column c of S (32 rows each) and keep their
 // entries in registers between the two passes over the column (first k^T S, then the update and q^T S), so the state crosses HBM
 // exactly once in each direction and every load of a warp is one contiguous row segment.  No tensor
 // cores: 4 flops per state byte.
@@ -27,12 +27,15 @@ struct DecodeProblem {
   __nv_bfloat16* o;
 };
 
+// kSplit threads share a column of S (kDK / kSplit rows each).
+constexpr int kSplit = 4;
+
 template <int V>
-__global__ void __launch_bounds__(2 * V)
+__global__ void __launch_bounds__(kSplit * V, 1024 / (kSplit * V))
 decode_step_kernel(const DecodeProblem p) {
-  __shared__ float ks[kDK], qs[kDK], as[kDK], part[2][V];
-  const int bh = blockIdx.x, c = threadIdx.x % V, half = threadIdx.x / V;   // rows [64 half, 64 half + 64)
-  for (int d = threadIdx.x; d < kDK; d += 2 * V) {
+  __shared__ float ks[kDK], qs[kDK], as[kDK], part[kSplit][V];
+  const int bh = blockIdx.x, c = threadIdx.x % V, part_id = threadIdx.x / V;   // rows [kRows part_id, + kRows)
+  for (int d = threadIdx.x; d < kDK; d += kSplit * V) {
     ks[d] = __bfloat162float(p.k[static_cast<size_t>(bh) * kDK + d]);
     qs[d] = p.scale * __bfloat162float(p.q[static_cast<size_t>(bh) * kDK + d]);
     float a = 1.f;
@@ -40,24 +43,26 @@ decode_step_kernel(const DecodeProblem p) {
     else if (p.gate == LETHE_GATE_CHANNEL) a = __expf(p.g[static_cast<size_t>(bh) * kDK + d]);
     as[d] = a;
   }
-  constexpr int kRows = kDK / 2;
-  float* S = p.state + (static_cast<size_t>(bh) * kDK + half * kRows) * V + c;
+  constexpr int kRows = kDK / kSplit;
+  float* S = p.state + (static_cast<size_t>(bh) * kDK + part_id * kRows) * V + c;
   float col[kRows];
 #pragma unroll
   for (int d = 0; d < kRows; ++d) col[d] = S[static_cast<size_t>(d) * V];   // all loads in flight at once
   __syncthreads();
-  const float* kh = ks + half * kRows;
-  const float* qh = qs + half * kRows;
-  const float* ah = as + half * kRows;
+  const float* kh = ks + part_id * kRows;
+  const float* qh = qs + part_id * kRows;
+  const float* ah = as + part_id * kRows;
   float ksum = 0.f;
 #pragma unroll
   for (int d = 0; d < kRows; ++d) {
     col[d] *= ah[d];
     ksum += kh[d] * col[d];
   }
-  part[half][c] = ksum;
+  part[part_id][c] = ksum;
   __syncthreads();
-  ksum = part[0][c] + part[1][c];
+  ksum = 0.f;
+#pragma unroll
+  for (int s = 0; s < kSplit; ++s) ksum += part[s][c];
   float vn = __bfloat162float(p.v[static_cast<size_t>(bh) * V + c]);
   if (p.delta) vn = p.beta[bh] * (vn - ksum);
   float o = 0.f;
@@ -68,9 +73,14 @@ decode_step_kernel(const DecodeProblem p) {
     S[static_cast<size_t>(d) * V] = col[d];
   }
   __syncthreads();
-  part[half][c] = o;
+  part[part_id][c] = o;
   __syncthreads();
-  if (half == 0) p.o[static_cast<size_t>(bh) * V + c] = __float2bfloat16_rn(part[0][c] + part[1][c]);
+  if (part_id == 0) {
+    float os = 0.f;
+#pragma unroll
+    for (int s = 0; s < kSplit; ++s) os += part[s][c];
+    p.o[static_cast<size_t>(bh) * V + c] = __float2bfloat16_rn(os);
+  }
 }
 
 }  // namespace lg
@@ -99,7 +109,7 @@ extern "C" int lethe_gdn_decode_step(const LetheGdnDecodeArgs* a, void* stream) 
   p.state = a->state;
   p.o = static_cast<__nv_bfloat16*>(a->o);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (a->V == 64) decode_step_kernel<64><<<p.BH, 128, 0, st>>>(p);
-  else decode_step_kernel<128><<<p.BH, 256, 0, st>>>(p);
+  if (a->V == 64) decode_step_kernel<64><<<p.BH, kSplit * 64, 0, st>>>(p);
+  else decode_step_kernel<128><<<p.BH, kSplit * 128, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
