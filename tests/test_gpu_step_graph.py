@@ -63,3 +63,85 @@ def test_head_ranges_and_groups_give_the_same_bits():
     with pytest.raises(ops.GdnError):
         ops.forward_into(part, *args, K ** -0.5, bh_range=(5, 2))     # beyond B * H = 6
 
+
+
+@pytest.mark.parametrize("gate,delta,V", [("scalar", True, 64), ("channel", True, 128), ("scalar", False, 128),
+                                          ("channel", False, 64)])
+def test_chunk_ranges_and_the_pipelined_graph_give_the_same_bits(gate, delta, V):
+    """Calls restricted to chunk ranges (forward ranges ascending, backward ranges descending: the scans hand
+    their fp32 state on through the workspace) and the graph that overlaps the two halves of every sequence
+    on two streams must reproduce the one-call result bit for bit, final state and initial-state gradient
+    included."""
+    B, L, H, K = 2, 1024, 3, 128
+    NT = L // 64
+    dev = torch.device("cuda")
+    code = {"scalar": ops.GATE_SCALAR, "channel": ops.GATE_CHANNEL}[gate]
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=9)
+    d = {n: (None if t is None else t.to(dev)) for n, t in inp.items()}
+    dhT = 0.1 * torch.randn(B, H, K, V, generator=torch.Generator().manual_seed(10)).to(dev)
+    args = (d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"])
+    sc = K ** -0.5
+    ref = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
+    ops.forward_into(ref, *args, sc)
+    ops.backward_into(ref, *args, d["do"], dhT, sc)
+    names = ["o", "hT", "dq", "dk", "dv", "dg", "dh0"] + (["dbeta"] if delta else [])
+    # three uneven ranges, kernel by kernel
+    part = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
+    for t in (part.o, part.dq, part.dk, part.dv, part.hT, part.dh0):
+        t.fill_(float("nan"))
+    ranges = [(0, 5), (5, 1), (6, NT - 6)]
+    for m in (1, 2, 4):
+        for cr in ranges:
+            ops.forward_into(part, *args, sc, m, c_range=cr)
+    for m in (1, 2, 4, 8) if delta else (1, 2, 4):
+        for cr in reversed(ranges):
+            ops.backward_into(part, *args, d["do"], dhT, sc, m, c_range=cr)
+    pipes = []
+    for cut in (0, NT // 2, 1, NT - 1):
+        pipe = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
+        graph = ops.GdnStepGraph(pipe, *args, d["do"], dhT, sc, pipeline=True, cut=cut)
+        assert graph.pipeline and graph.cut == cut and graph.segments == (2 if cut else 1)
+        for t in (pipe.o, pipe.dq, pipe.dk, pipe.dv, pipe.hT, pipe.dh0):
+            t.fill_(float("nan"))
+        graph.replay()
+        graph.replay()
+        pipes.append(pipe)
+    torch.cuda.synchronize()
+    for b in [part] + pipes:
+        ops.check_status(b.status)
+        for n in names:
+            assert torch.equal(getattr(b, n), getattr(ref, n)), n
+    with pytest.raises(ops.GdnError):
+        ops.forward_into(part, *args, sc, c_range=(NT - 1, 2))          # beyond the last chunk
+
+
+@pytest.mark.parametrize("gate,V,B,L,H", [("scalar", 64, 2, 2048, 8), ("channel", 128, 2, 2048, 8), ("scalar", 128, 4, 4096, 16)])
+def test_step_graph_at_benchmark_shapes_equals_the_plain_chain_on_every_replay(gate, V, B, L, H):
+    """The overlapped schedule at the shapes the benchmark times (the default cut, full grids, every stream of
+    the graph busy): twelve replays, each compared bit for bit with the plain chain - an ordering hole between
+    the graph's streams would show as a difference that comes and goes."""
+    K = 128
+    dev = torch.device("cuda")
+    delta = gate != "scalar" or V != 128           # the third case is SSD: scalar gate, no delta term
+    code = {"scalar": ops.GATE_SCALAR, "channel": ops.GATE_CHANNEL}[gate]
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=delta, seed=5)
+    d = {n: (None if t is None else t.to(dev)) for n, t in inp.items()}
+    sc = K ** -0.5
+    ref = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
+    ops.forward_into(ref, d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"], sc)
+    ops.backward_into(ref, d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"], d["do"], None, sc)
+    buf = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
+    graph = ops.GdnStepGraph(buf, d["q"], d["k"], d["v"], d["g"], d["beta"], d["h0"], d["do"], None, sc)
+    assert graph.pipeline and graph.cut > 0
+    names = ["o", "hT", "dq", "dk", "dv", "dh0", "dg"] + (["dbeta"] if delta else [])
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    for rep in range(12):
+        for n in names:
+            getattr(buf, n).fill_(float("nan"))
+        if rep % 2:
+            flush.zero_()                          # cold and warm L2: different relative timing of the streams
+        graph.replay()
+        torch.cuda.synchronize()
+        ops.check_status(buf.status)
+        for n in names:
+            assert torch.equal(getattr(buf, n), getattr(ref, n)), (rep, n)
