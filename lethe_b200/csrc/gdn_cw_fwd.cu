@@ -204,8 +204,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   // the source rows stream by; the eight pieces of a pair sit in neighbouring lanes and are added by a
   // butterfly (fixed order: deterministic).
   {
-    static_assert(kPrepCwThreads == 256, "4 blocks x 8 row pairs x 8 pieces");
-    const int c = tid & 7, j = (tid >> 3) & 7, blk = tid >> 6;
+    static_assert(kPrepCwThreads == 256, "8 row pairs (one per warp) x 4 blocks x 8 pieces");
+    // (a warp holds one row pair j of all four blocks: which source row comes next, and when the thread moves
+    // on to its second row, is then the same for every lane)
+    const int c = tid & 7, blk = (tid >> 3) & 3, j = tid >> 5;
     float qi[16], ki[16], gi[16];
     auto load_row = [&](int i) {
       unpack8_f16(tile_ld_chunk(KQ, 64 + i, c, 128), qi);
@@ -225,8 +227,10 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
     };
     int i = blk * 16 + j;
     load_row(i);
-    // (unrolled: the loads of a pair and the butterfly of the pair before it overlap this pair's arithmetic;
-    // rolled up, every iteration is one chain of dependent latencies and runs at a quarter of the issue rate)
+    // (unrolled: the loads of a pair overlap the arithmetic of the pair before it; the partial sums of all 17
+    // pairs stay in registers and are added across the eight pieces at the end, 34 independent butterflies
+    // instead of one after every pair)
+    float pa[17], pm[17];
 #pragma unroll
     for (int t = 0; t < 17; ++t) {
       if (t == j + 1) {               // the first row's pairs are done: on to the mirrored row
@@ -250,16 +254,25 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
         mm0 = fmaf(ki[e], k0, mm0);
         mm1 = fmaf(ki[e + 1], k1, mm1);
       }
-      float acc_a = aa0 + aa1, acc_m = mm0 + mm1;
+      pa[t] = aa0 + aa1;
+      pm[t] = mm0 + mm1;
+    }
 #pragma unroll
-      for (int o = 1; o < 8; o <<= 1) {
-        acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
-        acc_m += __shfl_xor_sync(0xffffffffu, acc_m, o);
+    for (int o = 1; o < 8; o <<= 1) {
+#pragma unroll
+      for (int t = 0; t < 17; ++t) {
+        pa[t] += __shfl_xor_sync(0xffffffffu, pa[t], o);
+        pm[t] += __shfl_xor_sync(0xffffffffu, pm[t], o);
       }
-      if (c == 0) {
-        const int ii = i - blk * 16;
-        Adg[i * 16 + ss] = p.scale * acc_a;
-        Mdg[i * 16 + ss] = (DELTA && ss < ii) ? betas[i] * acc_m : 0.f;
+    }
+    if (c == 0) {
+#pragma unroll
+      for (int t = 0; t < 17; ++t) {
+        const int row = (t > j) ? blk * 16 + 15 - j : blk * 16 + j;
+        const int ss = (t > j) ? t - j - 1 : t;
+        const int ii = row - blk * 16;
+        Adg[row * 16 + ss] = p.scale * pa[t];
+        Mdg[row * 16 + ss] = (DELTA && ss < ii) ? betas[row] * pm[t] : 0.f;
       }
     }
   }
