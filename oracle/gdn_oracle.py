@@ -47,7 +47,7 @@ def scale_rel(got: Tensor, ref: Tensor) -> float:
     (``tests/test_gdn2_assemble.py:50-51``; ``results/*.json`` field ``scale_rel``)."""
     ref = ref.double()
     den = float(ref.abs().max())
-    num = float((got.double() - ref).abs().max())
+    num = float((got.detach().double() - ref.detach()).abs().max())
     return num / den if den > 0 else num
 
 
