@@ -574,6 +574,9 @@ def main():
     ap.add_argument("--cut", type=int, default=-1,
                     help="chunk index at which the step graph cuts every sequence into an early and a late segment "
                          "(0: no cut; -1: the library's default, about half of the chunks on a whole number of CTA waves)")
+    ap.add_argument("--bwd-cuts", default="",
+                    help="comma-separated chunk indices at which the backward of the step graph is cut (default: the "
+                         "forward's cut)")
     ap.add_argument("--plain-chain", action="store_true",
                     help="capture the step as one chain of kernels on one stream (no overlap inside the graph)")
     ap.add_argument("--mild-gate", action="store_true",
@@ -674,7 +677,8 @@ def main():
     # the timed step is the CUDA-graph replay of forward + backward (ops.GdnStepGraph: the public call for a
     # training step at fixed shapes); the per-kernel and fwd / bwd timings below are plain launches
     graph = ops.GdnStepGraph(buf, d["q"], d["k"], d["v"], g, beta, h0, d["do"], None, scale, groups=args.groups,
-                             pipeline=not args.plain_chain, cut=None if args.cut < 0 else args.cut, **gates)
+                             pipeline=not args.plain_chain, cut=None if args.cut < 0 else args.cut,
+                             bwd_cuts=[int(x) for x in args.bwd_cuts.split(",")] if args.bwd_cuts else None, **gates)
     ms = timed(graph.replay, args.steps, max(args.warmup, 3))
     ops.check_status(buf.status)
     eager_ms = timed(step, args.steps, 3)
@@ -789,7 +793,7 @@ def main():
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate (bf16 in/out)",
             "data": "synthetic", "config": config,
-            "launch": f"CUDA graph replay (lethe_b200.ops.GdnStepGraph, groups={args.groups}, overlap={graph.pipeline}, cut={graph.cut})",
+            "launch": f"CUDA graph replay (lethe_b200.ops.GdnStepGraph, groups={args.groups}, overlap={graph.pipeline}, cut={graph.cut}, bwd_cuts={list(graph.bwd_cuts)})",
             "eager_ms_per_step": eager_ms,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "kernel_ms": kern,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
@@ -802,8 +806,9 @@ def main():
                     "host_link": pcie,
                     "host_link_floor_ms": max(h2d, d2h) / (pcie["both"]["slowest_rank_gbs"] * 1e9) * 1e3},
             "autograd_op_ms": op_ms,
-            # kernels per replayed step: one chain per segment of the step graph
-            "gpu_launches": args.steps * graph.segments * ((9 if delta else 7) if gate == "channel" else (7 if delta else 6)),
+            # kernels per replayed step: three per forward segment of the step graph, the backward kernels per
+            # backward segment
+            "gpu_launches": args.steps * ((3 * graph.segments + ((6 if delta else 4) if gate == "channel" else (4 if delta else 3)) * (len(graph.bwd_cuts) + 1))),
             "clocks": clocks,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "peak_source": which,

@@ -215,8 +215,9 @@ class GdnStepGraph:
     least 8 chunks; 0 = no cut) splits every sequence into an early and a late segment of chunks (``c_range`` of the C
     ABI): the late segment is prepared under the forward scan of the early one, and its Stage B and WY
     kernels run under the adjoint scan of the early one.  The scans hand their fp32 state from segment to
-    segment through the workspace.  (More than two segments, and a stream per segment, measured slower:
-    every extra segment adds a scan prologue to the serial chain.)
+    segment through the workspace.  ``bwd_cuts`` (default: the forward's cut, plus one at half a wave for
+    problems of at most two waves) cuts the backward at places of its own.  (More segments than that, and a
+    stream per segment, measured slower: every extra segment adds a scan prologue to the serial chain.)
 
     ``groups > 1``: the (batch, head) pairs are cut into that many ranges and every range runs its own
     kernel chain on its own stream inside the graph (the pairs are independent recurrences).
@@ -227,7 +228,7 @@ class GdnStepGraph:
 
     def __init__(self, buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, *, b_gate=None, w_gate=None,
                  groups: int = 1, pipeline: bool | None = None,
-                 cut: int | None = None):
+                 cut: int | None = None, bwd_cuts=None):
         self.buf = buf
         self._keep = (q, k, v, g, beta, h0, do, dhT, b_gate, w_gate)
         dev = q.device
@@ -244,6 +245,11 @@ class GdnStepGraph:
             cut = self._default_cut(buf, NT, BH, dev)
         self.cut = int(cut) if self.pipeline and 0 < int(cut) < NT else 0
         self.segments = 2 if self.cut else 1
+        if bwd_cuts is None or not self.pipeline:
+            bwd_cuts = self._default_bwd_cuts(buf, NT, BH, dev, self.cut)
+        self.bwd_cuts = tuple(sorted(int(c) for c in bwd_cuts))
+        if any(c <= 0 or c >= NT for c in self.bwd_cuts) or len(set(self.bwd_cuts)) != len(self.bwd_cuts):
+            raise GdnError(f"lethe_gdn: backward cuts {self.bwd_cuts} must be distinct chunk indices inside (0, {NT})")
         gates = dict(b_gate=b_gate, w_gate=w_gate)
 
         def chain(rng):
@@ -276,8 +282,14 @@ class GdnStepGraph:
             other, third = self._streams[0], self._streams[1]
             segs = [(0, self.cut), (self.cut, NT - self.cut)] if self.segments == 2 else [(0, NT)]
             S = len(segs)
+            # the backward may be cut at other places than the forward (its ranges only have to be visited in
+            # descending order): boundaries self.bwd_cuts, ascending
+            bb = [0] + list(self.bwd_cuts) + [NT]
+            bsegs = [(bb[i], bb[i + 1] - bb[i]) for i in range(len(bb) - 1)]
+            SB = len(bsegs)
             has_wy = buf.dims.delta != 0
-            e_p, e_f, e_r, e_o, e_a = ([None] * S for _ in range(5))
+            e_p, e_f, e_o = ([None] * S for _ in range(3))
+            e_r, e_a = ([None] * SB for _ in range(2))
             with torch.cuda.stream(side):
                 fwd(1, segs[0])
                 e_p[0] = mark(side)
@@ -286,8 +298,8 @@ class GdnStepGraph:
                 for i in range(1, S):
                     fwd(1, segs[i])                          # prepare of the later segment: under the first scan
                     e_p[i] = mark(other)
-                for i in reversed(range(S)):
-                    bwd(1, segs[i])                          # input of the adjoint scan: needs prepare and do only
+                for i in reversed(range(SB)):
+                    bwd(1, bsegs[i])                         # input of the adjoint scan: needs prepare and do only
                     e_r[i] = mark(other)
             for i in range(S):                               # forward scan, segment after segment
                 if i:
@@ -301,23 +313,26 @@ class GdnStepGraph:
                 with torch.cuda.stream(st):
                     fwd(4, segs[i])
                     e_o[i] = mark(st)
-            for i in reversed(range(S)):                     # adjoint scan straight behind the forward scan
+            for i in reversed(range(SB)):                    # adjoint scan straight behind the forward scan
                 side.wait_event(e_r[i])
                 with torch.cuda.stream(side):
-                    bwd(2, segs[i])
+                    bwd(2, bsegs[i])
                     e_a[i] = mark(side)
-            for i in reversed(range(1, S)):                  # Stage B / WY of the later segment: under the adjoint scan
-                other.wait_event(e_a[i])
-                other.wait_event(e_o[i])
-                with torch.cuda.stream(other):
-                    bwd(4, segs[i])
+            for n, i in enumerate(reversed(range(1, SB))):   # Stage B / WY of the later segments: under the adjoint scan
+                st = other if n % 2 == 0 else third
+                st.wait_event(e_a[i])
+                for e in e_o:
+                    st.wait_event(e)
+                with torch.cuda.stream(st):
+                    bwd(4, bsegs[i])
                     if has_wy:
-                        bwd(8, segs[i])
-            side.wait_event(e_o[0])
+                        bwd(8, bsegs[i])
+            for e in e_o:
+                side.wait_event(e)
             with torch.cuda.stream(side):
-                bwd(4, segs[0])
+                bwd(4, bsegs[0])
                 if has_wy:
-                    bwd(8, segs[0])
+                    bwd(8, bsegs[0])
             side.wait_event(mark(other))
             side.wait_event(mark(third))
 
@@ -371,6 +386,21 @@ class GdnStepGraph:
         if cut >= NT:
             cut -= wave
         return cut if cut > 0 else NT // 2
+
+    @staticmethod
+    def _default_bwd_cuts(buf, NT: int, BH: int, dev, cut: int) -> tuple:
+        """Where the backward is cut: at the forward's cut, and - when the whole problem is at most two waves of
+        two CTAs per SM - once more at half a wave.  The last Stage B and WY launches of a step have nothing to
+        hide behind; with half a wave of chunks their CTAs have an SM each and finish sooner (measured at
+        B=2, H=8, L=2048, d_v=64: 0.1185 -> 0.1125 ms; larger problems and the one-CTA-per-SM kernels lose)."""
+        if not cut:
+            return ()
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        two_per_sm = buf.dims.gate != GATE_CHANNEL and buf.dims.V == 64 and buf.dims.delta != 0
+        wave = (sms * 2) // BH
+        if two_per_sm and wave >= 2 and cut == wave and wave < NT <= 2 * wave:
+            return (wave // 2, cut)
+        return (cut,)
 
     def replay(self) -> None:
         """Enqueue the captured step on the current stream."""

@@ -97,10 +97,12 @@ def test_chunk_ranges_and_the_pipelined_graph_give_the_same_bits(gate, delta, V)
         for cr in reversed(ranges):
             ops.backward_into(part, *args, d["do"], dhT, sc, m, c_range=cr)
     pipes = []
-    for cut in (0, NT // 2, 1, NT - 1):
+    for cut, bcuts in ((0, None), (NT // 2, None), (1, None), (NT - 1, None), (NT // 2, (3, 9)), (5, (2, 7, 11, 14)),
+                       (0, (4,))):
         pipe = ops.GdnBuffers(B, L, H, K, V, code, delta, dev)
-        graph = ops.GdnStepGraph(pipe, *args, d["do"], dhT, sc, pipeline=True, cut=cut)
+        graph = ops.GdnStepGraph(pipe, *args, d["do"], dhT, sc, pipeline=True, cut=cut, bwd_cuts=bcuts)
         assert graph.pipeline and graph.cut == cut and graph.segments == (2 if cut else 1)
+        assert graph.bwd_cuts == (tuple(bcuts) if bcuts else ((cut,) if cut else ()))
         for t in (pipe.o, pipe.dq, pipe.dk, pipe.dv, pipe.hT, pipe.dh0):
             t.fill_(float("nan"))
         graph.replay()
