@@ -17,28 +17,33 @@
 namespace lg {
 
 constexpr int kStages = 3;
-constexpr int kVs = 16;        // columns of the state per CTA
 constexpr int kMmaWarps = 2;   // warps that issue the step's products (each its own accumulator)
+// Columns of the state per CTA (template parameter kVs of the kernel): 16, or 32 when the 16-column CTAs of a
+// launch could not all be resident at once.  With 32 columns the scan needs half the CTAs and reads P half as
+// often, but a step takes about a fifth longer (measured: 39 against 33 us for 32 chunks), so the narrow form
+// is kept wherever it fits in one wave.
 // warps 0-3 hold the state (thread d = key channel d), warp 4 streams P, warps 5.. issue products
 constexpr int kScanThreads = (5 + kMmaWarps) * 32;
 constexpr int kStepBarrier = 128 + kMmaWarps * 32;
-constexpr int kTmemCols = kMmaWarps * 16 < 32 ? 32 : kMmaWarps * 16;
 
 // Step barrier of the delta path: the state-holding warps arrive once the operand is written (and go
 // on to work that does not depend on the product), the issuing warps wait for them.
 __device__ __forceinline__ void step_arrive() { asm volatile("bar.arrive 1, %0;" ::"n"(kStepBarrier) : "memory"); }
 __device__ __forceinline__ void step_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStepBarrier) : "memory"); }
 
-template <bool ADJOINT>
-__global__ void __launch_bounds__(kScanThreads)
+template <bool ADJOINT, int kVs>
+__global__ void __launch_bounds__(kScanThreads, 2)
 scan_kernel(const Problem p) {
+  constexpr int kTmemCols = kMmaWarps * kVs;        // 32 or 64
+  constexpr int kXB = 128 * kVs * 2;                 // bytes of the state operand tile
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = align1024_generic(smem_raw);
   unsigned char* Pst = sm;                          // kStages x 32 KB
-  // 4 KB: x as the B operand, contracted along its rows (row k = key channel k, 16 columns = 32 bytes):
-  // atoms of 8 rows x 32 bytes with the 32-byte swizzle, so that thread k stores its row as two 16-byte pieces
+  // x as the B operand, contracted along its rows (row k = key channel k, kVs columns = 32 or 64 bytes):
+  // atoms of 8 rows x 32 (64) bytes with the 32-byte (64-byte) swizzle, so that thread k stores its row as
+  // two (four) 16-byte pieces
   unsigned char* XB = sm + kStages * 32768;
-  CtaShared* cs = reinterpret_cast<CtaShared*>(XB + 4096);
+  CtaShared* cs = reinterpret_cast<CtaShared*>(XB + kXB);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int v0 = blockIdx.x * kVs, bh = blockIdx.y + p.bh0;
@@ -98,7 +103,7 @@ scan_kernel(const Problem p) {
     const uint32_t leader = elect_leader();
     // A = the P stage (contracted along its columns forward, along its rows for the adjoint),
     // B = the state operand; one 16-element contraction step moves each by a fixed amount
-    const uint64_t b_desc0 = make_desc_sw32(smem_u32(XB), 16u, 256u);
+    const uint64_t b_desc0 = kVs == 16 ? make_desc_sw32(smem_u32(XB), 16u, 256u) : make_desc_sw64(smem_u32(XB), 16u, 512u);
     const uint32_t idesc = make_idesc(128, kVs, ADJOINT, true);
     const uint32_t acc = tmem + static_cast<uint32_t>(m * kVs);
     for (int it = 0; it < n; ++it) {
@@ -114,7 +119,7 @@ scan_kernel(const Problem p) {
         // byte offsets of contraction step j, in the descriptors' 16-byte units
         const uint32_t aoff = ADJOINT ? static_cast<uint32_t>(j * 2048) >> 4
                                       : static_cast<uint32_t>((j >> 2) * 16384 + (j & 3) * 32) >> 4;
-        const uint32_t boff = static_cast<uint32_t>(j * 512) >> 4;     // 16 rows of 32 bytes per step
+        const uint32_t boff = static_cast<uint32_t>(j * 32 * kVs) >> 4;     // 16 rows of 2 kVs bytes per step
         umma_led(leader, acc, a_desc0 + aoff, b_desc0 + boff, idesc, jj > 0 ? 1u : 0u);
       }
       umma_commit_led(leader, bar_mma);
@@ -128,7 +133,7 @@ scan_kernel(const Problem p) {
     unsigned char* Xg = ADJOINT ? p.scratch + p.lay.dh : p.saved + p.lay.hc;
     const size_t szx = p.lay.sz_hc;
     // R / Rb records are [V / 16 column blocks][128 rows][16 columns]: this CTA's block, this thread's row
-    const size_t rofs = (static_cast<size_t>(blockIdx.x) * kK + tid) * kVs;
+    const size_t rofs = (static_cast<size_t>(blockIdx.x) * (kVs / 16) * kK + tid) * 16;
 
     float* carry = reinterpret_cast<float*>(ADJOINT ? p.scratch + p.lay.carry_b : p.saved + p.lay.carry_f);
     float x[kVs];
@@ -137,21 +142,28 @@ scan_kernel(const Problem p) {
 #pragma unroll
       for (int j = 0; j < kVs; ++j) x[j] = x0 ? x0[(static_cast<size_t>(bh) * kK + tid) * V + v0 + j] : 0.f;
     }
-    uint4 rnext[2];
-    {
-      const __half* r = Rg + (static_cast<size_t>(bh) * NT + chunk_of(0)) * kK * V + rofs;
-      rnext[0] = *reinterpret_cast<const uint4*>(r);
-      rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
-    }
+    constexpr int kPieces = kVs / 8;             // 16-byte pieces of this thread's row
+    uint4 rnext[kPieces];
+    auto load_r = [&](int chunk) {
+      // the record is cut into blocks of 16 columns: piece q lies in block q / 2 of this CTA's blocks
+      const __half* r = Rg + (static_cast<size_t>(bh) * NT + chunk) * kK * V + rofs;
+#pragma unroll
+      for (int q = 0; q < kPieces; ++q)
+        rnext[q] = *reinterpret_cast<const uint4*>(r + (q >> 1) * (kK * 16) + (q & 1) * 8);
+    };
+    load_r(chunk_of(0));
     float a_next = ADg[(static_cast<size_t>(bh) * NT + chunk_of(0)) * kK + tid];
 
     for (int it = 0; it < n; ++it) {
       const size_t z = static_cast<size_t>(bh) * NT + chunk_of(it);
       // critical path: the state as a tensor-core operand
       {
-        const int sw = (tid >> 2) & 1;     // 32-byte swizzle: the two 16-byte pieces of rows 4-7 of an atom swap
-        *reinterpret_cast<uint4*>(XB + tid * 32 + (sw << 4)) = pack8_f16(x);
-        *reinterpret_cast<uint4*>(XB + tid * 32 + ((sw ^ 1) << 4)) = pack8_f16(x + 8);
+        // 32-byte swizzle: the two pieces of rows 4-7 of an atom swap; 64-byte swizzle: piece q of row r sits
+        // at q ^ ((r >> 1) & 3)
+        const int sw = kVs == 16 ? (tid >> 2) & 1 : (tid >> 1) & 3;
+#pragma unroll
+        for (int q = 0; q < kPieces; ++q)
+          *reinterpret_cast<uint4*>(XB + tid * (2 * kVs) + ((q ^ sw) << 4)) = pack8_f16(x + 8 * q);
       }
       fence_proxy_async();
       tc_fence_before();
@@ -159,41 +171,44 @@ scan_kernel(const Problem p) {
       // in the shadow of the product: this chunk's input and decay, the next chunk's loads, the record
       const float a = a_next;
       float rr[kVs];
-      unpack8_f16(rnext[0], rr);
-      unpack8_f16(rnext[1], rr + 8);
+#pragma unroll
+      for (int q = 0; q < kPieces; ++q) unpack8_f16(rnext[q], rr + 8 * q);
 #pragma unroll
       for (int j = 0; j < kVs; ++j) rr[j] = fmaf(a, x[j], rr[j]);
       if (it + 1 < n) {
-        const size_t zn = static_cast<size_t>(bh) * NT + chunk_of(it + 1);
-        const __half* r = Rg + zn * kK * V + rofs;
-        rnext[0] = *reinterpret_cast<const uint4*>(r);
-        rnext[1] = *reinterpret_cast<const uint4*>(r + 8);
-        a_next = ADg[zn * kK + tid];
+        const int cn = chunk_of(it + 1);
+        load_r(cn);
+        a_next = ADg[(static_cast<size_t>(bh) * NT + cn) * kK + tid];
       }
       {
         unsigned char* rec = Xg + (ADJOINT ? z : z + bh) * szx;
-        *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
-        *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
+#pragma unroll
+        for (int q = 0; q < kPieces; ++q)
+          *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + q, 128)) = pack8_f16(x + 8 * q);
       }
       mbar_wait_warp(bar_mma, static_cast<uint32_t>(it & 1), ctl, 302);
       tc_fence_after();
-      float acc[kMmaWarps * kVs];
-      if (kMmaWarps == 1) tmem_ld16(tmem + lane_base, acc);
-      if (kMmaWarps >= 2) tmem_ld32(tmem + lane_base, acc);
-      if (kMmaWarps == 4) tmem_ld32(tmem + lane_base + 32, acc + 32);
-      tmem_ld_wait();
+      static_assert(kMmaWarps == 2, "two accumulators of kVs columns, one per half of the contraction");
+      if (kVs == 16) {
+        float acc[32];
+        tmem_ld32(tmem + lane_base, acc);
+        tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < kVs; ++j) {
-        float s = acc[j];
-        if (kMmaWarps >= 2) s += acc[kVs + j];
-        if (kMmaWarps == 4) s += acc[2 * kVs + j] + acc[3 * kVs + j];
-        x[j] = rr[j] - s;
+        for (int j = 0; j < 16; ++j) x[j] = rr[j] - (acc[j] + acc[16 + j]);
+      } else {
+        float a0[32], a1[32];
+        tmem_ld32(tmem + lane_base, a0);
+        tmem_ld32(tmem + lane_base + 32, a1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = rr[j] - (a0[j] + a1[j]);
       }
     }
     if (!ADJOINT && seg_last) {   // the final state as one more record
       unsigned char* rec = Xg + (static_cast<size_t>(bh) * (NT + 1) + NT) * szx;
-      *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8, 128)) = pack8_f16(x);
-      *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + 1, 128)) = pack8_f16(x + 8);
+#pragma unroll
+      for (int q = 0; q < kPieces; ++q)
+        *reinterpret_cast<uint4*>(rec + sw128_chunk(tid, v0 / 8 + q, 128)) = pack8_f16(x + 8 * q);
     }
     float* xT = seg_last ? (ADJOINT ? p.dh0 : p.hT) : carry;
     if (xT) {
@@ -274,6 +289,22 @@ scan_nodelta_kernel(const Problem p) {
   }
 }
 
+template <int kVs>
+static int launch_scan_t(const Problem& p, bool adjoint, cudaStream_t st) {
+  const int smem = kStages * 32768 + 128 * kVs * 2 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  dim3 grid(p.V / kVs, p.nbh);
+  if (adjoint) {
+    static SmemAttr attr;
+    if (attr.set(scan_kernel<true, kVs>, smem)) return kErrLaunch;
+    if (launch_dependent(scan_kernel<true, kVs>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
+  } else {
+    static SmemAttr attr;
+    if (attr.set(scan_kernel<false, kVs>, smem)) return kErrLaunch;
+    if (launch_dependent(scan_kernel<false, kVs>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
+  }
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
 int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
   if (!p.delta) {
     const dim3 g((p.V / 64) * 4, p.nbh);
@@ -281,18 +312,12 @@ int launch_scan(const Problem& p, bool adjoint, cudaStream_t st) {
                                   : launch_dependent(scan_nodelta_kernel<false>, g, dim3(256), 0, st, p);
     return e == cudaSuccess ? kOk : kErrLaunch;
   }
-  const int smem = kStages * 32768 + 4096 + static_cast<int>(sizeof(CtaShared)) + 1024;
-  dim3 grid(p.V / kVs, p.nbh);
-  if (adjoint) {
-    static SmemAttr attr;
-    if (attr.set(scan_kernel<true>, smem)) return kErrLaunch;
-    if (launch_dependent(scan_kernel<true>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
-  } else {
-    static SmemAttr attr;
-    if (attr.set(scan_kernel<false>, smem)) return kErrLaunch;
-    if (launch_dependent(scan_kernel<false>, grid, dim3(kScanThreads), smem, st, p) != cudaSuccess) return kErrLaunch;
-  }
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+  // 32 columns per CTA when the CTAs of the 16-column form could not all be resident at once (two per SM):
+  // the recurrence is serial, so a second wave of CTAs doubles the time of the scan
+  const int sms = sm_count();
+  if (sms <= 0) return kErrDevice;
+  const bool wide = (p.V / 16) * p.nbh > 2 * sms;
+  return wide ? launch_scan_t<32>(p, adjoint, st) : launch_scan_t<16>(p, adjoint, st);
 }
 
 }  // namespace lg

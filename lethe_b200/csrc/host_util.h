@@ -89,6 +89,21 @@ struct DeviceGuard {
   }
 };
 
+// Number of SMs of the current device (looked up once per device ordinal).
+inline int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+  if (dev < 64) {
+    const int c = cached[dev].load(std::memory_order_acquire);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 0;
+  if (dev < 64) cached[dev].store(n, std::memory_order_release);
+  return n;
+}
+
 // Opt-in to more than 48 KB of dynamic shared memory, done once per kernel and device instead of on
 // every launch.  One object per kernel instantiation (a function-local static of its launcher).
 struct SmemAttr {

@@ -210,6 +210,18 @@ __device__ __forceinline__ uint64_t make_desc_sw32(uint32_t saddr, uint32_t lbo,
   return d;
 }
 
+// ... and in the 64-byte swizzle (atoms of 8 rows x 64 bytes; piece c of row r stored at c ^ ((r >> 1) & 3)),
+// for a 32-column operand contracted along its rows.
+__device__ __forceinline__ uint64_t make_desc_sw64(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFF) << 32;
+  d |= 1ull << 46;  // descriptor version of this architecture
+  d |= 4ull << 61;  // 64-byte swizzle
+  return d;
+}
+
 enum : uint32_t { kFmtF16 = 0, kFmtBF16 = 1 };
 
 // Instruction descriptor for kind::f16, fp32 accumulate.  a_mn / b_mn: operand is contracted along

@@ -80,3 +80,20 @@ def test_headline_shapes_bitwise_deterministic(cfg):
     assert set(a) == set(b)
     for n in a:
         assert torch.equal(a[n], b[n]), (cfg, n)
+
+
+@pytest.mark.parametrize("gate,V,B,H", [("scalar", 64, 5, 16), ("channel", 128, 5, 8), ("scalar", 128, 3, 16)])
+def test_many_pairs_take_the_wide_scan_and_stay_exact(gate, V, B, H):
+    """With more (batch, head) pairs than fit the GPU as 16-column scan CTAs (two per SM), the state scans run
+    with 32 columns per CTA (a 64-byte-swizzled state operand).  Parity on the first, a middle and the last
+    pair - with an initial state and a final-state gradient, so both ends of both scans are covered - and two
+    runs must agree bit for bit."""
+    L, K = 256, 128
+    assert (V // 16) * B * H > 2 * torch.cuda.get_device_properties(0).multi_processor_count
+    inp = make_inputs(B, L, H, K, V, gate=gate, delta=True, seed=21)
+    dhT = 0.1 * torch.randn(B, H, K, V, generator=torch.Generator().manual_seed(22))
+    res = run_op(inp, K ** -0.5, dhT)
+    check_pairs(f"wide scan {gate} V={V}", inp, res, [(0, 0), (B // 2, H // 2), (B - 1, H - 1)], dhT=dhT)
+    again = run_op(inp, K ** -0.5, dhT)
+    for n in res:
+        assert torch.equal(res[n], again[n]), n
