@@ -206,18 +206,20 @@ class GdnStepGraph:
 
     A training step at fixed shapes calls the library with the same pointers every time; replaying the
     captured kernels removes the launch gaps between them.  Two ways to fill the SMs the serial state scans
-    leave idle (a scan occupies V / 16 CTAs per (batch, head) pair), both bitwise equal to the plain chain:
+    leave idle (a scan occupies V / 16 CTAs per (batch, head) pair, V / 32 for very many pairs), both bitwise
+    equal to the plain chain:
 
     ``pipeline`` (default): only the serial chain of the step - prepare, forward scan, adjoint scan, Stage B
     and WY - stays on one stream; the output kernel and the kernel that builds the adjoint scan's input run
     on other streams of the graph beside the scans (the adjoint scan needs neither the outputs nor the
-    forward scan).  ``cut`` (default: about half of the chunks, on a whole number of CTA waves, for sequences of at
-    least 8 chunks; 0 = no cut) splits every sequence into an early and a late segment of chunks (``c_range`` of the C
-    ABI): the late segment is prepared under the forward scan of the early one, and its Stage B and WY
-    kernels run under the adjoint scan of the early one.  The scans hand their fp32 state from segment to
-    segment through the workspace.  ``bwd_cuts`` (default: the forward's cut, plus one at half a wave for
-    problems of at most two waves) cuts the backward at places of its own.  (More segments than that, and a
-    stream per segment, measured slower: every extra segment adds a scan prologue to the serial chain.)
+    forward scan).  ``cut`` (default: about half of the chunks, on a whole number of CTA waves, for
+    sequences of at least 8 chunks; 0 = no cut) splits every sequence into an early and a late segment of
+    chunks (``c_range`` of the C ABI): the late segment is prepared under the forward scan of the early one,
+    and its Stage B and WY kernels run under the adjoint scan of the early one.  The scans hand their fp32
+    state from segment to segment through the workspace.  ``bwd_cuts`` (default: the forward's cut, plus one
+    at half a wave for problems of at most two waves) cuts the backward at places of its own.  (More
+    segments than that, and a stream per segment, measured slower: every extra segment adds a scan prologue
+    to the serial chain.)
 
     ``groups > 1``: the (batch, head) pairs are cut into that many ranges and every range runs its own
     kernel chain on its own stream inside the graph (the pairs are independent recurrences).
