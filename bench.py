@@ -261,21 +261,21 @@ def path_fractions(workload: str, fwd_ms: float, bwd_ms: float, step_ms: float, 
 # channel-wise "stageb" and "wy" are two launches each, summed.  Absent combinations report null.
 NCU_DRAM_BYTES_PER_CHUNK = {
     # scalar-gate GDN, B4 H8 L4096 d_v 64 (2048 chunks)
-    ("prepare", "scalar", 64, True): (85.0e6 + 127.4e6) / 2048,
-    ("scan_fwd", "scalar", 64, True): (102.8e6 + 14.2e6) / 2048,
-    ("output", "scalar", 64, True): (151.5e6 + 18.3e6) / 2048,
-    ("bwd_pre", "scalar", 64, True): (118.0e6 + 15.4e6) / 2048,
-    ("scan_bwd", "scalar", 64, True): (101.7e6 + 13.4e6) / 2048,
+    ("prepare", "scalar", 64, True): (85.0e6 + 127.6e6) / 2048,
+    ("scan_fwd", "scalar", 64, True): (102.8e6 + 14.0e6) / 2048,
+    ("output", "scalar", 64, True): (151.5e6 + 18.1e6) / 2048,
+    ("bwd_pre", "scalar", 64, True): (118.0e6 + 14.1e6) / 2048,
+    ("scan_bwd", "scalar", 64, True): (101.7e6 + 14.0e6) / 2048,
     ("stageb", "scalar", 64, True): (185.1e6 + 104.6e6) / 2048,
-    ("wy", "scalar", 64, True): (203.0e6 + 33.3e6) / 2048,
+    ("wy", "scalar", 64, True): (203.0e6 + 35.3e6) / 2048,
     # KDA, B4 H8 L4096 d_v 128 (2048 chunks)
-    ("prepare", "channel", 128, True): (168.5e6 + 278.3e6) / 2048,
-    ("scan_fwd", "channel", 128, True): (137.4e6 + 38.5e6) / 2048,
-    ("output", "channel", 128, True): (201.4e6 + 43.3e6) / 2048,
-    ("bwd_pre", "channel", 128, True): (134.2e6 + 36.1e6) / 2048,
-    ("scan_bwd", "channel", 128, True): (135.3e6 + 38.4e6) / 2048,
-    ("stageb", "channel", 128, True): (369.2e6 + 242.3e6 + 352.4e6 + 131.0e6) / 2048,
-    ("wy", "channel", 128, True): (235.5e6 + 86.6e6 + 319.9e6 + 80.8e6) / 2048,
+    ("prepare", "channel", 128, True): (168.5e6 + 279.8e6) / 2048,
+    ("scan_fwd", "channel", 128, True): (137.4e6 + 38.2e6) / 2048,
+    ("output", "channel", 128, True): (201.4e6 + 43.8e6) / 2048,
+    ("bwd_pre", "channel", 128, True): (134.2e6 + 36.5e6) / 2048,
+    ("scan_bwd", "channel", 128, True): (135.3e6 + 37.6e6) / 2048,
+    ("stageb", "channel", 128, True): (369.3e6 + 241.5e6 + 352.4e6 + 130.4e6) / 2048,
+    ("wy", "channel", 128, True): (235.5e6 + 87.5e6 + 320.0e6 + 81.3e6) / 2048,
     # GLA, B4 H16 L4096 d_v 128 (4096 chunks)
     ("prepare", "channel", 128, False): (335.6e6 + 418.7e6) / 4096,
     ("scan_fwd", "channel", 128, False): (141.0e6 + 93.5e6) / 4096,
