@@ -27,6 +27,48 @@ namespace lg {
 // bank conflicts, and global accesses by 128 threads along d stay coalesced.
 __device__ __forceinline__ int ridx(int i, int d) { return i * kK + (d ^ ((i & 7) << 2)); }
 
+// Four neighbouring channels [4 c4, 4 c4 + 4) of row `row` of an exchange tile (layout exi): they share one
+// aligned 16-byte piece, in which channel e sits at position e ^ (row & 3).
+__device__ __forceinline__ void ex_perm4(float* a, int row) {
+  if (row & 1) {
+    float t = a[0]; a[0] = a[1]; a[1] = t;
+    t = a[2]; a[2] = a[3]; a[3] = t;
+  }
+  if (row & 2) {
+    float t = a[0]; a[0] = a[2]; a[2] = t;
+    t = a[1]; a[1] = a[3]; a[3] = t;
+  }
+}
+__device__ __forceinline__ void ex_ld4(const float* T, int row, int c4, float* out) {
+  const float4 v = *reinterpret_cast<const float4*>(T + row * kK + 4 * (c4 ^ ((row & 31) >> 2)));
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  ex_perm4(out, row);
+}
+__device__ __forceinline__ void ex_st4(float* T, int row, int c4, const float* in) {
+  float a[4] = {in[0], in[1], in[2], in[3]};
+  ex_perm4(a, row);
+  *reinterpret_cast<float4*>(T + row * kK + 4 * (c4 ^ ((row & 31) >> 2))) = make_float4(a[0], a[1], a[2], a[3]);
+}
+__device__ __forceinline__ void unpack4_f16(const uint2& u, float* v) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+  const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+// four 16-bit results (bf16, or fp16 when the call runs with fp16 q, k) as one 8-byte store
+__device__ __forceinline__ void store_out16x4(__nv_bfloat16* dst, const float* x, int f16) {
+  uint2 u;
+  if (f16) {
+    __half2* h = reinterpret_cast<__half2*>(&u);
+    h[0] = __floats2half2_rn(x[0], x[1]);
+    h[1] = __floats2half2_rn(x[2], x[3]);
+  } else {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+    h[0] = __floats2bfloat162_rn(x[0], x[1]);
+    h[1] = __floats2bfloat162_rn(x[2], x[3]);
+  }
+  *reinterpret_cast<uint2*>(dst) = u;
+}
+
 
 // ---------------------------------------------------------------------------------------------
 // Stage B, part 1.  Accumulators: cA [0,128) dv2; cB [128,256) [do; dv2] h^T; cC [256,320) dA;
@@ -781,46 +823,70 @@ bwd_cw_pair_kernel(const Problem p, const __grid_constant__ CUtensorMap mq, cons
   __syncthreads();
   if (MODE == 1 && !full && tid < 64)      // sum_d d(bk)_m k
     p.dbeta[tok0 + static_cast<size_t>(tid) * p.H] += (red[tid] + red[64 + tid]) + (red[128 + tid] + red[192 + tid]);
-  // ---- phase B: column owners (thread (row group, channel d): 16 rows each) combine with the fp32 records:
-  // the dq / dk parts from their shared-memory copies, the gate-gradient part from global memory (all 16
-  // rows requested at once; coalesced along d).
+  // ---- phase B: every (row, group of four channels) combines the two sums with the fp32 records: the dq / dk
+  // parts from their shared-memory copies, the gate-gradient part from global memory.  A warp covers one row
+  // (32 groups), a thread four rows 16 apart; every access is a 16-byte (8-byte for the fp16 tiles and the
+  // 16-bit outputs) piece, coalesced along the channels.
   mbar_wait_warp(bar_rec, 0, ctl, 624);
   {
-    const int d = tid & 127, ibase = 16 * (tid >> 7);
     float* __restrict__ dkb_g = reinterpret_cast<float*>(p.scratch + p.lay.dkb + static_cast<size_t>(z) * p.lay.sz_dkb);
     float* __restrict__ dgb_g = reinterpret_cast<float*>(p.scratch + p.lay.dgb + static_cast<size_t>(z) * p.lay.sz_dgb);
     constexpr bool kFinalK = (MODE == 1) || FINAL_G;     // without the delta term Stage B closes dk
-    float dgb16[16];
+    constexpr int kItems = 64 * 32 / kPairThreads;
+    float4 dgb4[kItems];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) dgb16[j] = dgb_g[ridx(ibase + j, d)];
+    for (int u = 0; u < kItems; ++u) {
+      const int item = tid + u * kPairThreads;
+      dgb4[u] = *reinterpret_cast<const float4*>(dgb_g + ridx(item >> 5, (item & 31) * 4));
+    }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const int i = ibase + j;
-      const float part = RQ[ridx(i, d)], dgb = dgb16[j], dkb = RK[ridx(i, d)];
-      const float o1 = EX1[exi(i, d)], o2 = EX2[exi(i, d)];
-      const float kv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(i, d, 128)));
-      const float xv = __half2float(*reinterpret_cast<const __half*>(KX + sw128_off(64 + i, d, 128)));
-      const size_t tok = (tok0 + static_cast<size_t>(i) * p.H) * kK + d;
-      float dk, dG;
+    for (int u = 0; u < kItems; ++u) {
+      const int item = tid + u * kPairThreads, i = item >> 5, c4 = item & 31, d0 = c4 * 4;
+      const float4 part4 = *reinterpret_cast<const float4*>(RQ + ridx(i, d0));
+      const float4 dkb4 = *reinterpret_cast<const float4*>(RK + ridx(i, d0));
+      const float part[4] = {part4.x, part4.y, part4.z, part4.w}, dkb[4] = {dkb4.x, dkb4.y, dkb4.z, dkb4.w};
+      const float dgb[4] = {dgb4[u].x, dgb4[u].y, dgb4[u].z, dgb4[u].w};
+      float o1[4], o2[4], kv[4], xv[4];
+      ex_ld4(EX1, i, c4, o1);
+      ex_ld4(EX2, i, c4, o2);
+      unpack4_f16(*reinterpret_cast<const uint2*>(KX + sw128_chunk(i, c4 >> 1, 128) + (c4 & 1) * 8), kv);
+      unpack4_f16(*reinterpret_cast<const uint2*>(KX + sw128_chunk(64 + i, c4 >> 1, 128) + (c4 & 1) * 8), xv);
+      const size_t tok = (tok0 + static_cast<size_t>(i) * p.H) * kK + d0;
+      float dk[4], dG[4];
       if (MODE == 0) {
-        store_out16(p.dq + tok, part + o1, p.qk16);
-        dk = dkb + o2;
-        dG = dgb + xv * o1 - kv * o2;                  // q~ . dq_intra - k . dk_intra (the scale sits in C)
-      } else {
-        const float eg = exp2f(Gt[gidx(i, d)]);
-        const float dbk = part * eg + o1;              // d(beta k), or d(b k) of the full op
-        if (full) {
-          dk = dkb + dbk * p.bch[tok] + o2;
-          p.dbch[tok] = dbk * kv;
-        } else {
-          dk = dkb + dbk * betas[i] + o2;
+        float dq[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          dq[e] = part[e] + o1[e];
+          dk[e] = dkb[e] + o2[e];
+          dG[e] = dgb[e] + xv[e] * o1[e] - kv[e] * o2[e];          // q~ . dq_intra - k . dk_intra (the scale sits in C)
         }
-        dG = dgb + part * xv * eg + xv * o1 - kv * o2; // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
+        store_out16x4(p.dq + tok, dq, p.qk16);
+      } else {
+        const float4 g4 = gt4(Gt, i, d0);
+        const float gg[4] = {g4.x, g4.y, g4.z, g4.w};
+        float bb[4];
+        if (full) {
+          const float4 b4 = *reinterpret_cast<const float4*>(p.bch + tok);
+          bb[0] = b4.x; bb[1] = b4.y; bb[2] = b4.z; bb[3] = b4.w;
+        } else {
+          bb[0] = bb[1] = bb[2] = bb[3] = betas[i];
+        }
+        float dbkk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float eg = exp2f(gg[e]);
+          const float dbk = part[e] * eg + o1[e];                  // d(beta k), or d(b k) of the full op
+          dk[e] = dkb[e] + dbk * bb[e] + o2[e];
+          dbkk[e] = dbk * kv[e];
+          dG[e] = dgb[e] + part[e] * xv[e] * eg + xv[e] * o1[e] - kv[e] * o2[e];   // dq_wy (b gamma k) + (b k) dbk_m - k dk_m
+        }
+        if (full) *reinterpret_cast<float4*>(p.dbch + tok) = make_float4(dbkk[0], dbkk[1], dbkk[2], dbkk[3]);
       }
-      if (kFinalK) store_out16(p.dk + tok, dk, p.qk16);
-      else dkb_g[ridx(i, d)] = dk;
-      if (FINAL_G) EX1[exi(i, d)] = dG;                // closed below by the reverse cumulative sum
-      else dgb_g[ridx(i, d)] = dG;
+      if (kFinalK) store_out16x4(p.dk + tok, dk, p.qk16);
+      else *reinterpret_cast<float4*>(dkb_g + ridx(i, d0)) = make_float4(dk[0], dk[1], dk[2], dk[3]);
+      if (FINAL_G) ex_st4(EX1, i, c4, dG);                         // closed below by the reverse cumulative sum
+      else *reinterpret_cast<float4*>(dgb_g + ridx(i, d0)) = make_float4(dG[0], dG[1], dG[2], dG[3]);
     }
   }
   if (FINAL_G) {
