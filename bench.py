@@ -274,8 +274,8 @@ NCU_DRAM_BYTES_PER_CHUNK = {
     ("output", "channel", 128, True): (201.4e6 + 43.8e6) / 2048,
     ("bwd_pre", "channel", 128, True): (134.2e6 + 36.5e6) / 2048,
     ("scan_bwd", "channel", 128, True): (135.3e6 + 37.6e6) / 2048,
-    ("stageb", "channel", 128, True): (369.3e6 + 241.5e6 + 352.4e6 + 130.4e6) / 2048,
-    ("wy", "channel", 128, True): (235.5e6 + 87.5e6 + 320.0e6 + 81.3e6) / 2048,
+    ("stageb", "channel", 128, True): (369.2e6 + 240.3e6 + 352.4e6 + 129.5e6) / 2048,
+    ("wy", "channel", 128, True): (235.5e6 + 87.9e6 + 319.9e6 + 81.0e6) / 2048,
     # GLA, B4 H16 L4096 d_v 128 (4096 chunks)
     ("prepare", "channel", 128, False): (335.6e6 + 418.7e6) / 4096,
     ("scan_fwd", "channel", 128, False): (141.0e6 + 93.5e6) / 4096,
