@@ -20,6 +20,7 @@ namespace lg {
 
 constexpr int kMsC = 68;
 constexpr int kPrepCwThreads = 256;
+constexpr int kDg = 17;                               // row stride (floats) of the diagonal-block buffers
 constexpr int kGateSegs = kPrepCwThreads / 128;       // row segments of the cumulative sum (thread = segment x channel)
 constexpr int kGateRows = kC / kGateSegs;
 
@@ -38,10 +39,12 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
   unsigned char* KD = BV + V * 128;            // 16 KB
   unsigned char* TA = KD + 16384;              // 16 KB
   float* fs = reinterpret_cast<float*>(TA + 16384);
-  float* Adg = fs;              // [64][16] diagonal blocks of A
-  float* Mdg = fs + 1024;       // [64][16] diagonal blocks of M
-  float* betas = fs + 2048;     // [64]
-  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 2112);
+  // diagonal blocks of A and of M, [64][16] with rows kDg floats apart: an odd stride keeps both the epilogue's
+  // reads (thread r reads row r) and the diagonal phase's stores off each other's banks
+  float* Adg = fs;
+  float* Mdg = fs + 64 * kDg;
+  float* betas = fs + 128 * kDg;     // [64]
+  CtaShared* cs = reinterpret_cast<CtaShared*>(fs + 128 * kDg + 64);
   float* Msm = reinterpret_cast<float*>(KQ);
   unsigned char* WU = KQ;
 
@@ -271,8 +274,8 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
         const int row = (t > j) ? blk * 16 + 15 - j : blk * 16 + j;
         const int ss = (t > j) ? t - j - 1 : t;
         const int ii = row - blk * 16;
-        Adg[row * 16 + ss] = p.scale * pa[t];
-        Mdg[row * 16 + ss] = (DELTA && ss < ii) ? betas[row] * pm[t] : 0.f;
+        Adg[row * kDg + ss] = p.scale * pa[t];
+        Mdg[row * kDg + ss] = (DELTA && ss < ii) ? betas[row] * pm[t] : 0.f;
       }
     }
   }
@@ -315,7 +318,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
         for (int j = 0; j < 32; ++j) {
           const int s = half * 32 + j;
           float m = row[j] * be;                               // off-diagonal blocks (zero beyond 16 I)
-          if ((s >> 4) == I) m = (s < r) ? Mdg[r * 16 + (s & 15)] : 0.f;
+          if ((s >> 4) == I) m = (s < r) ? Mdg[r * kDg + (s & 15)] : 0.f;
           Msm[r * kMsC + s] = m;
         }
       }
@@ -328,7 +331,7 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
         for (int e = 0; e < 8; ++e) {
           const int s = s8 * 8 + e;
           float x = row[q * 8 + e] * p.scale;
-          if ((s >> 4) == I) x = (s <= r) ? Adg[r * 16 + (s & 15)] : 0.f;
+          if ((s >> 4) == I) x = (s <= r) ? Adg[r * kDg + (s & 15)] : 0.f;
           a[e] = x;
         }
         tile_st_chunk(TA, 64 + r, s8, 128, pack8_f16(a));
@@ -432,7 +435,8 @@ prepare_cw_kernel(const Problem p, const __grid_constant__ CUtensorMap mq,
 template <int V, bool DELTA>
 static int launch_prepare_cw_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
                                const CUtensorMap& mv, cudaStream_t st) {
-  const int smem = 32768 * 4 + 16384 + V * 128 + 16384 + 16384 + 2112 * 4 + static_cast<int>(sizeof(CtaShared)) + 1024;
+  const int smem = 32768 * 4 + 16384 + V * 128 + 16384 + 16384 + (128 * kDg + 64) * 4 +
+                   static_cast<int>(sizeof(CtaShared)) + 1024;
   auto kern = prepare_cw_kernel<V, DELTA>;
   static SmemAttr attr;
   if (attr.set(kern, smem)) return kErrLaunch;
