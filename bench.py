@@ -269,7 +269,7 @@ NCU_DRAM_BYTES_PER_CHUNK = {
     ("stageb", "scalar", 64, True): (185.1e6 + 104.6e6) / 2048,
     ("wy", "scalar", 64, True): (203.0e6 + 35.3e6) / 2048,
     # KDA, B4 H8 L4096 d_v 128 (2048 chunks)
-    ("prepare", "channel", 128, True): (168.5e6 + 279.8e6) / 2048,
+    ("prepare", "channel", 128, True): (168.5e6 + 279.2e6) / 2048,
     ("scan_fwd", "channel", 128, True): (137.4e6 + 38.2e6) / 2048,
     ("output", "channel", 128, True): (201.4e6 + 43.8e6) / 2048,
     ("bwd_pre", "channel", 128, True): (134.2e6 + 36.5e6) / 2048,
