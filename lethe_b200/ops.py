@@ -201,6 +201,38 @@ def backward_into(buf: GdnBuffers, q, k, v, g, beta, h0, do, dhT, scale: float, 
     _check(native.lib().lethe_gdn_backward(ctypes.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
 
 
+def default_cut(gate: int, V: int, NT: int, BH: int, sms: int) -> int:
+    """Chunk index at which ``GdnStepGraph`` cuts every sequence: the whole number of CTA waves of the chunk
+    kernels nearest to half of the sequence.  A chunk kernel runs one CTA per chunk, two per SM for the scalar
+    gate at d_v = 64 and one otherwise; when the early segment fills whole waves, the kernels on the serial
+    chain (its prepare, its Stage B and WY) do not end on a nearly empty wave, which is worth 7 % of the step
+    at B=2, H=8, L=2048.  ``NT`` chunks per sequence, ``BH`` (batch, head) pairs, ``sms`` SMs."""
+    if NT < 8:
+        return 0
+    per_sm = 2 if (gate != GATE_CHANNEL and V == 64) else 1
+    wave = (sms * per_sm) // BH                  # chunks of every (batch, head) pair in one wave
+    if wave == 0 or wave >= NT:
+        return NT // 2
+    cut = max(1, int(NT / 2 / wave + 0.5)) * wave
+    if cut >= NT:
+        cut -= wave
+    return cut if cut > 0 else NT // 2
+
+
+def default_bwd_cuts(gate: int, V: int, delta: bool, NT: int, BH: int, sms: int, cut: int) -> tuple:
+    """Where the backward is cut: at the forward's cut, and - when the whole problem is at most two waves of
+    two CTAs per SM - once more at half a wave.  The last Stage B and WY launches of a step have nothing to
+    hide behind; with half a wave of chunks their CTAs have an SM each and finish sooner (measured at
+    B=2, H=8, L=2048, d_v=64: 0.1185 -> 0.1125 ms; larger problems and the one-CTA-per-SM kernels lose)."""
+    if not cut:
+        return ()
+    two_per_sm = gate != GATE_CHANNEL and V == 64 and delta
+    wave = (sms * 2) // BH
+    if two_per_sm and wave >= 2 and cut == wave and wave < NT <= 2 * wave:
+        return (wave // 2, cut)
+    return (cut,)
+
+
 class GdnStepGraph:
     """Forward + backward of one fixed problem, captured once into a CUDA graph and replayed.
 
@@ -373,36 +405,13 @@ class GdnStepGraph:
 
     @staticmethod
     def _default_cut(buf, NT: int, BH: int, dev) -> int:
-        """Chunk index of the cut: the whole number of CTA waves of the chunk kernels nearest to half of the
-        sequence.  A chunk kernel runs one CTA per chunk, two per SM for the scalar gate at d_v = 64 and one
-        otherwise; when the early segment fills whole waves, the kernels on the serial chain (its prepare, its
-        Stage B and WY) do not end on a nearly empty wave, which is worth 7 % of the step at B=2, H=8, L=2048."""
-        if NT < 8:
-            return 0
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        per_sm = 2 if (buf.dims.gate != GATE_CHANNEL and buf.dims.V == 64) else 1
-        wave = (sms * per_sm) // BH                  # chunks of every (batch, head) pair in one wave
-        if wave == 0 or wave >= NT:
-            return NT // 2
-        cut = max(1, int(NT / 2 / wave + 0.5)) * wave
-        if cut >= NT:
-            cut -= wave
-        return cut if cut > 0 else NT // 2
+        return default_cut(buf.dims.gate, buf.dims.V, NT, BH, sms)
 
     @staticmethod
     def _default_bwd_cuts(buf, NT: int, BH: int, dev, cut: int) -> tuple:
-        """Where the backward is cut: at the forward's cut, and - when the whole problem is at most two waves of
-        two CTAs per SM - once more at half a wave.  The last Stage B and WY launches of a step have nothing to
-        hide behind; with half a wave of chunks their CTAs have an SM each and finish sooner (measured at
-        B=2, H=8, L=2048, d_v=64: 0.1185 -> 0.1125 ms; larger problems and the one-CTA-per-SM kernels lose)."""
-        if not cut:
-            return ()
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        two_per_sm = buf.dims.gate != GATE_CHANNEL and buf.dims.V == 64 and buf.dims.delta != 0
-        wave = (sms * 2) // BH
-        if two_per_sm and wave >= 2 and cut == wave and wave < NT <= 2 * wave:
-            return (wave // 2, cut)
-        return (cut,)
+        return default_bwd_cuts(buf.dims.gate, buf.dims.V, buf.dims.delta != 0, NT, BH, sms, cut)
 
     def replay(self) -> None:
         """Enqueue the captured step on the current stream."""
